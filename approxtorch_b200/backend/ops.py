@@ -1,0 +1,647 @@
+"""Operator boundary: the reference's ``torch.ops.approxtorch.*`` schemas, implemented by calling the
+hand-written sm_100a kernels through the C ABI (ctypes, raw device pointers, the current stream).
+
+The schema strings are the ones the reference registers
+(approxtorch/backend/csrc/claude/bgemm_float_claude.cu:281-288, gemm.cu:292-299,
+bgemm_lre_backward_claude.cu:892-899, quantization.cu:313-318,
+approxtorch/backend/csrc/cuda/bgemm_custom_grad_optimize.cu:590-595, dwconv_claude.cu:279-281) and
+the Python wrappers at the bottom keep the names and argument order of
+approxtorch/backend/ops.py:166-273, so callers written against the reference run unchanged.
+
+Conventions kept from the reference operators: inputs are normalised with ``.contiguous()`` and never
+mutated; outputs are fresh tensors on the input's device; every kernel is enqueued on the current
+stream without host synchronisation; wrong device / dtype / rank raises ``RuntimeError`` before any
+launch.  CUDA tensors only: there is no CPU implementation.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import weakref
+
+import torch
+from torch import Tensor
+from torch.nn.modules.utils import _pair
+
+from . import _C
+from ._C import lib as _lib, check as _check
+
+F32, I8, U8 = 0, 1, 2
+_DTYPE_CODE = {torch.float32: F32, torch.int8: I8, torch.uint8: U8}
+
+
+# --------------------------------------------------------------------------- helpers
+def _ptr(t: Tensor | None):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(t: Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _require_cuda(*named):
+    for name, t in named:
+        _require(isinstance(t, Tensor) and t.is_cuda, f"{name} must be a CUDA tensor")
+
+
+def _qcode(t: Tensor, name: str) -> int:
+    _require(t.dtype in _DTYPE_CODE, f"{name} must be float32, int8 or uint8")
+    return _DTYPE_CODE[t.dtype]
+
+
+class _Guard:
+    """Make the tensor's device current for the duration of a launch sequence."""
+
+    def __init__(self, t: Tensor):
+        self._ctx = torch.cuda.device(t.device)
+
+    def __enter__(self):
+        self._ctx.__enter__()
+
+    def __exit__(self, *exc):
+        return self._ctx.__exit__(*exc)
+
+
+# --------------------------------------------------------------------------- LUT images
+_IMAGE_BYTES = int(_lib.atb_lut_image_bytes())
+_images: "weakref.WeakKeyDictionary[Tensor, tuple[int, Tensor]]" = weakref.WeakKeyDictionary()
+
+
+def lut_image(lut: Tensor) -> Tensor:
+    """Device image of a 256x256 table (16-bit + fp32, natural + transposed, validity flags).
+
+    Built once per (tensor object, version) and cached; the reference rebuilds its image and makes
+    three allocations on every call (approxtorch/backend/csrc/claude/bgemm_float_claude.cu:163-192).
+    The cache is a derived object keyed on the tensor, never a state_dict entry."""
+    _require(lut.is_cuda, "lut must be a CUDA tensor")
+    _require(lut.dtype == torch.float32, "lut must be float32")
+    _require(lut.numel() == 65536, "lut must have 65536 elements")
+    hit = _images.get(lut)
+    if hit is not None and hit[0] == lut._version and hit[1].device == lut.device:
+        return hit[1]
+    src = lut.detach().contiguous()
+    img = torch.empty(_IMAGE_BYTES, dtype=torch.uint8, device=lut.device)
+    with _Guard(lut):
+        _check(_lib.atb_lut_prepare(_ptr(src), _ptr(img), _stream(lut)), "atb_lut_prepare")
+    _images[lut] = (lut._version, img)
+    return img
+
+
+# --------------------------------------------------------------------------- raw launch helpers
+def quantize_u8(x: Tensor, offset: int) -> Tensor:
+    x = x.contiguous()
+    out = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    with _Guard(x):
+        _check(_lib.atb_quantize_u8(_ptr(x), _ptr(out), x.numel(), offset, _stream(x)), "atb_quantize_u8")
+    return out
+
+
+def _normalise_cfg(cfg: int) -> int:
+    """cfg < 0: automatic.  Otherwise bits 0-15 = pixel rows per block (multiple of 32, up to 512) and
+    bits 16-23 = split-K factor; the reference's tile ids (0..18, 100..118) do not name a tiling of
+    this kernel and select the automatic plan."""
+    if cfg < 0:
+        return -1
+    rows = cfg & 0xFFFF
+    if rows != 0 and (rows % 32 != 0 or rows > 512):
+        return -1
+    return cfg
+
+
+def lut_gemm_launch(x_idx: Tensor, w_idx: Tensor, image: Tensor, y: Tensor, N: int, K: int, L: int, O: int,
+                    wb_rows: int = 0, w_batch_stride: int = 0, alpha: Tensor | None = None,
+                    beta: Tensor | None = None, zero_x: Tensor | None = None, zero_w: Tensor | None = None,
+                    wsum: Tensor | None = None, cfg: int = -1) -> None:
+    cfg = _normalise_cfg(int(cfg))
+    plan = _C.GemmPlan()
+    with _Guard(y):
+        _check(_lib.atb_lut_gemm_plan(N * L, K, O, wb_rows, cfg, ctypes.byref(plan)), "atb_lut_gemm_plan")
+        scratch = None
+        if plan.scratch_bytes:
+            scratch = torch.empty(plan.scratch_bytes, dtype=torch.uint8, device=y.device)
+        _check(_lib.atb_lut_bgemm_fwd(_ptr(x_idx), _ptr(w_idx), _ptr(image), _ptr(y), N, K, L, O, wb_rows,
+                                      w_batch_stride, _ptr(alpha), _ptr(beta), _ptr(zero_x), _ptr(zero_w),
+                                      _ptr(wsum), cfg, _ptr(scratch), plan.scratch_bytes, _stream(y)),
+               "atb_lut_bgemm_fwd")
+
+
+def conv_out_hw(H, W, kh, kw, sh, sw, ph, pw, dh, dw):
+    return ((H + 2 * ph - dh * (kh - 1) - 1) // sh + 1, (W + 2 * pw - dw * (kw - 1) - 1) // sw + 1)
+
+
+def lut_conv2d_launch(img8: Tensor, w_idx: Tensor, image: Tensor, geom, pad_index: int,
+                      alpha: Tensor | None = None, beta: Tensor | None = None, zero_x: Tensor | None = None,
+                      zero_w: Tensor | None = None, wsum: Tensor | None = None, cfg: int = -1) -> Tensor:
+    """im2col-free LUT conv on a quantised 8-bit image [B,C,H,W]; returns y [B,O,OH,OW] fp32."""
+    (kh, kw), (sh, sw), (ph, pw), (dh, dw) = geom
+    B, C, H, W = img8.shape
+    O = w_idx.shape[0]
+    OH, OW = conv_out_hw(H, W, kh, kw, sh, sw, ph, pw, dh, dw)
+    _require(OH >= 1 and OW >= 1, "conv geometry yields empty output")
+    y = torch.empty((B, O, OH, OW), dtype=torch.float32, device=img8.device)
+    cfg = _normalise_cfg(int(cfg))
+    plan = _C.GemmPlan()
+    with _Guard(y):
+        _check(_lib.atb_lut_gemm_plan(B * OH * OW, C * kh * kw, O, 0, cfg, ctypes.byref(plan)), "atb_lut_gemm_plan")
+        scratch = None
+        if plan.scratch_bytes:
+            scratch = torch.empty(plan.scratch_bytes, dtype=torch.uint8, device=y.device)
+        _check(_lib.atb_lut_conv2d_fwd(_ptr(img8), _DTYPE_CODE[img8.dtype], _ptr(w_idx), _ptr(image), _ptr(y),
+                                       B, C, H, W, O, kh, kw, sh, sw, ph, pw, dh, dw, pad_index,
+                                       _ptr(alpha), _ptr(beta), _ptr(zero_x), _ptr(zero_w), _ptr(wsum),
+                                       cfg, _ptr(scratch), plan.scratch_bytes, _stream(y)),
+               "atb_lut_conv2d_fwd")
+    return y
+
+
+def absmax(x: Tensor, want_minmax: bool = False) -> Tensor:
+    """[max|x|, min x, max x] as a 3-element device tensor (min/max only when asked)."""
+    x = x.detach().contiguous()
+    _require(x.is_cuda and x.dtype == torch.float32, "absmax needs a float32 CUDA tensor")
+    out = torch.empty(3, dtype=torch.float32, device=x.device)
+    with _Guard(x):
+        _check(_lib.atb_absmax(_ptr(x), x.numel(), int(want_minmax), _ptr(out), _stream(x)), "atb_absmax")
+    return out
+
+
+def quantize_image(x: Tensor, scale: Tensor, zero_point: Tensor | None, qmin: int, qmax: int,
+                   want_mask: bool = True):
+    """Fused fake-quant to a 1-byte image: int8 values (symmetric) or uint8 indices (asymmetric)."""
+    x = x.contiguous()
+    q8 = torch.empty(x.shape, dtype=torch.int8 if zero_point is None else torch.uint8, device=x.device)
+    mask = torch.empty(x.shape, dtype=torch.bool, device=x.device) if want_mask else None
+    with _Guard(x):
+        _check(_lib.atb_quantize_image(_ptr(x), _ptr(scale), _ptr(zero_point), qmin, qmax, _ptr(q8), _ptr(mask),
+                                       x.numel(), _stream(x)), "atb_quantize_image")
+    return q8, mask
+
+
+def quantize_weight(w: Tensor, scale: Tensor, zero_point: Tensor | None, qmin: int, qmax: int, index_offset: int,
+                    want_mask: bool = True, want_q: bool = False, want_sum: bool = False):
+    """Per-output-channel weight fake-quant -> (uint8 indices [O, inner], mask, fp32 q, int32 index sums)."""
+    w = w.contiguous()
+    O = w.shape[0]
+    inner = w.numel() // O if O else 0
+    widx = torch.empty((O, inner), dtype=torch.uint8, device=w.device)
+    mask = torch.empty(w.shape, dtype=torch.bool, device=w.device) if want_mask else None
+    q = torch.empty(w.shape, dtype=torch.float32, device=w.device) if want_q else None
+    wsum = torch.empty(O, dtype=torch.int32, device=w.device) if want_sum else None
+    with _Guard(w):
+        _check(_lib.atb_quantize_weight(_ptr(w), _ptr(scale.contiguous()),
+                                        _ptr(None if zero_point is None else zero_point.contiguous()),
+                                        qmin, qmax, index_offset, O, inner, _ptr(widx), _ptr(mask), _ptr(q),
+                                        _ptr(wsum), _stream(w)), "atb_quantize_weight")
+    return widx, mask, q, wsum
+
+
+def lre_conv_backward(go: Tensor, x8: Tensor, w_idx: Tensor | None, dx: Tensor | None, dw: Tensor | None,
+                      geom, pad_index: int, go_scale: Tensor | None = None, need_x: bool = True, need_w: bool = True):
+    """Image-space STE/LRE backward: (grad wrt the quantised image [B,C,H,W], grad_w [O,K])."""
+    (kh, kw), (sh, sw), (ph, pw), (dh, dw_) = geom
+    B, C, H, W = x8.shape
+    go = go.contiguous()
+    O = go.shape[1]
+    gx = torch.empty((B, C, H, W), dtype=torch.float32, device=go.device) if need_x else None
+    gw = torch.empty((O, C * kh * kw), dtype=torch.float32, device=go.device) if need_w else None
+    with _Guard(go):
+        _check(_lib.atb_lre_conv_bwd(_ptr(go), _ptr(x8), _DTYPE_CODE[x8.dtype], _ptr(w_idx), _ptr(dx), _ptr(dw),
+                                     _ptr(go_scale), _ptr(gx), _ptr(gw), B, C, H, W, O, kh, kw, sh, sw, ph, pw,
+                                     dh, dw_, pad_index, _stream(go)), "atb_lre_conv_bwd")
+    return gx, gw
+
+
+_decode_tables: dict = {}
+
+
+def decode_table(device, offset: int) -> Tensor:
+    """arange(256) - offset: turns saved LUT indices back into quantised values, so the STE backward
+    is the LRE backward with this table (approxtorch/nn/bgemm_int8.py:220-226)."""
+    key = (device, offset)
+    t = _decode_tables.get(key)
+    if t is None:
+        t = torch.arange(256, device=device, dtype=torch.float32) - float(offset)
+        _decode_tables[key] = t
+    return t
+
+
+# --------------------------------------------------------------------------- operator implementations
+def _check_lut(lut: Tensor):
+    _require(lut.is_cuda, "lut must be a CUDA tensor")
+    _require(lut.dtype == torch.float32, "lut must be float32")
+    _require(lut.numel() == 256 * 256, "lut must have 65536 elements")
+
+
+def _bgemm_save(x: Tensor, w: Tensor, lut: Tensor, cfg: int, offset: int):
+    _require_cuda(("x", x), ("w", w))
+    _check_lut(lut)
+    _require(x.dtype in (torch.float32, torch.uint8), "x must be float32 or uint8 (LUT indices)")
+    _require(w.dtype == torch.float32, "w must be float32")
+    _require(x.dim() == 3, "x must have shape [N, CKK, L]")
+    _require(w.dim() == 2, "w must have shape [O, CKK]")
+    _require(x.size(1) == w.size(1), "x.size(1) must equal w.size(1)")
+    N, K, L = x.shape
+    O = w.shape[0]
+    _require(N * L <= 2**31 - 1, "N * L too large")
+    xq = x.contiguous() if x.dtype == torch.uint8 else quantize_u8(x, offset)
+    wq = quantize_u8(w, offset)
+    y = torch.empty((N, O, L), dtype=torch.float32, device=x.device)
+    if y.numel():
+        lut_gemm_launch(xq, wq, lut_image(lut), y, N, K, L, O, cfg=cfg)
+    return y, xq, wq
+
+
+def _gemm_save(A: Tensor, B: Tensor, lut: Tensor, cfg: int, offset: int):
+    _require_cuda(("A", A), ("B", B))
+    _check_lut(lut)
+    _require(A.dtype in (torch.float32, torch.uint8), "A must be float32 or uint8 (LUT indices)")
+    _require(B.dtype in (torch.float32, torch.uint8), "B must be float32 or uint8 (LUT indices)")
+    _require(A.dim() == 2, "A must have shape [M, K]")
+    _require(B.dim() == 2, "B must have shape [K, N]")
+    _require(A.size(1) == B.size(0), f"A.size(1) must equal B.size(0), got {A.size(1)} vs {B.size(0)}")
+    M, K = A.shape
+    Ncol = B.shape[1]
+    aq = A.contiguous() if A.dtype == torch.uint8 else quantize_u8(A, offset)
+    bq = torch.empty((Ncol, K), dtype=torch.uint8, device=A.device)
+    if bq.numel():
+        with _Guard(A):
+            _check(_lib.atb_quantize_transpose_u8(_ptr(B), _DTYPE_CODE[B.dtype], K, Ncol, B.stride(0), B.stride(1),
+                                                  offset, _ptr(bq), _stream(A)), "atb_quantize_transpose_u8")
+    y = torch.empty((M, Ncol), dtype=torch.float32, device=A.device)
+    if y.numel():
+        lut_gemm_launch(aq, bq, lut_image(lut), y, M, K, 1, Ncol, cfg=cfg)
+    return y, aq, bq
+
+
+def _fakequant(x: Tensor, scale: Tensor, zero_point: Tensor | None, qmin: int, qmax: int):
+    _require(x.is_cuda and scale.is_cuda, "x and scale must be CUDA")
+    _require(x.dtype == torch.float32, "x must be float32")
+    _require(scale.dtype == torch.float32, "scale must be float32")
+    _require(scale.numel() == 1, "scale must be a scalar tensor")
+    if zero_point is not None:
+        _require(zero_point.is_cuda and zero_point.dtype == torch.float32, "zero_point must be a float32 CUDA tensor")
+        _require(zero_point.numel() == 1, "zero_point must be a scalar tensor")
+    xc = x.contiguous()
+    q = torch.empty_like(xc)
+    mask = torch.empty(xc.shape, dtype=torch.bool, device=x.device)
+    with _Guard(x):
+        _check(_lib.atb_fakequant_fwd(_ptr(xc), _ptr(scale.contiguous()),
+                                      _ptr(None if zero_point is None else zero_point.contiguous()),
+                                      int(qmin), int(qmax), _ptr(q), _ptr(mask), xc.numel(), _stream(x)),
+               "atb_fakequant_fwd")
+    return q, mask
+
+
+def _fakequant_backward(grad_output: Tensor, mask: Tensor, scale: Tensor) -> Tensor:
+    _require(grad_output.is_cuda and mask.is_cuda and scale.is_cuda, "all tensors must be CUDA")
+    _require(grad_output.dtype == torch.float32, "grad_output must be float32")
+    _require(mask.dtype == torch.bool, "mask must be bool")
+    _require(scale.dtype == torch.float32 and scale.numel() == 1, "scale must be a float32 scalar tensor")
+    _require(grad_output.shape == mask.shape, "grad_output/mask shape mismatch")
+    go = grad_output.contiguous()
+    mc = mask.contiguous()
+    gx = torch.empty_like(go)
+    with _Guard(go):
+        _check(_lib.atb_fakequant_bwd(_ptr(go), _ptr(mc), _ptr(scale.contiguous()), _ptr(gx), go.numel(), _stream(go)),
+               "atb_fakequant_bwd")
+    return gx
+
+
+def _geometry_ok(kh, kw, sh, sw, ph, pw, dh, dw):
+    _require(kh >= 1 and kw >= 1 and sh >= 1 and sw >= 1 and ph >= 0 and pw >= 0 and dh >= 1 and dw >= 1,
+             "invalid conv geometry")
+
+
+def _im2col_u8(x: Tensor, kh, kw, sh, sw, ph, pw, dh, dw, pad_index: int = 128) -> Tensor:
+    _require(x.is_cuda, "x must be a CUDA tensor")
+    code = _qcode(x, "x")
+    _require(x.dim() == 4, "x must have shape [N, C, H, W]")
+    _geometry_ok(kh, kw, sh, sw, ph, pw, dh, dw)
+    xc = x.contiguous()
+    N, C, H, W = xc.shape
+    OH, OW = conv_out_hw(H, W, kh, kw, sh, sw, ph, pw, dh, dw)
+    _require(OH >= 1 and OW >= 1, "conv geometry yields empty output")
+    out = torch.empty((N, C * kh * kw, OH * OW), dtype=torch.uint8, device=x.device)
+    if out.numel():
+        with _Guard(x):
+            _check(_lib.atb_im2col_u8(_ptr(xc), code, N, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, pad_index,
+                                      _ptr(out), _stream(x)), "atb_im2col_u8")
+    return out
+
+
+def _lut_map(x: Tensor, lut: Tensor) -> Tensor:
+    _require(x.is_cuda and lut.is_cuda, "tensors must be CUDA")
+    code = _qcode(x, "x")
+    _require(lut.dtype == torch.float32, "lut must be float32")
+    _require(lut.numel() == 256, "lut must have 256 elements")
+    xc = x.contiguous()
+    out = torch.empty(xc.shape, dtype=torch.float32, device=x.device)
+    if out.numel():
+        with _Guard(x):
+            _check(_lib.atb_lut_map(_ptr(xc), code, _ptr(lut.contiguous()), _ptr(out), xc.numel(), _stream(x)),
+                   "atb_lut_map")
+    return out
+
+
+def _lut_map_pad(x: Tensor, lut: Tensor, ph: int, pw: int) -> Tensor:
+    _require(x.is_cuda and lut.is_cuda, "tensors must be CUDA")
+    code = _qcode(x, "x")
+    _require(lut.dtype == torch.float32, "lut must be float32")
+    _require(lut.numel() == 256, "lut must have 256 elements")
+    _require(x.dim() == 4, "x must have shape [N, C, H, W]")
+    _require(ph >= 0 and pw >= 0, "padding must be non-negative")
+    xc = x.contiguous()
+    N, C, H, W = xc.shape
+    out = torch.empty((N, C, H + 2 * ph, W + 2 * pw), dtype=torch.float32, device=x.device)
+    if out.numel():
+        with _Guard(x):
+            _check(_lib.atb_lut_map_pad(_ptr(xc), code, _ptr(lut.contiguous()), _ptr(out), N, C, H, W, ph, pw,
+                                        _stream(x)), "atb_lut_map_pad")
+    return out
+
+
+def _lre_checks(go, x, w, dx, dw, x_rank):
+    _require(go.is_cuda and x.is_cuda and w.is_cuda and dx.is_cuda and dw.is_cuda, "all tensors must be CUDA")
+    _require(go.dtype == torch.float32 and dx.dtype == torch.float32 and dw.dtype == torch.float32,
+             "grad_output/dx/dw must be float32")
+    _qcode(x, "x")
+    _qcode(w, "w")
+    _require(go.dim() == 3, "grad_output must have shape [N, O, L]")
+    _require(x.dim() == x_rank, "x must have shape [N, K, L]" if x_rank == 3 else "x must have shape [N, C, H, W]")
+    _require(w.dim() == 2, "w must have shape [K, O]")
+    _require(dx.numel() == 256, "dx must have 256 elements")
+    _require(dw.numel() == 256, "dw must have 256 elements")
+
+
+def lre_backward_launch(go: Tensor, x: Tensor, w: Tensor, w_ok_layout: bool, dx: Tensor, dw: Tensor,
+                        need_x: bool = True, need_w: bool = True):
+    """Column-space STE/LRE backward; w and grad_w are [O,K] when w_ok_layout else [K,O]."""
+    N, K, L = x.shape
+    O = w.shape[0] if w_ok_layout else w.shape[1]
+    gx = torch.empty((N, K, L), dtype=torch.float32, device=go.device) if need_x else None
+    gw = torch.empty(w.shape, dtype=torch.float32, device=go.device) if need_w else None
+    with _Guard(go):
+        _check(_lib.atb_lre_bwd(_ptr(go), _ptr(x), _DTYPE_CODE[x.dtype], _ptr(w), _DTYPE_CODE[w.dtype],
+                                int(w_ok_layout), _ptr(dx), _ptr(dw), _ptr(gx), _ptr(gw), N, K, L, O, _stream(go)),
+               "atb_lre_bwd")
+    return gx, gw
+
+
+def _lre_backward(grad_output: Tensor, x: Tensor, w: Tensor, dx: Tensor, dw: Tensor, cfg: int = -1):
+    _lre_checks(grad_output, x, w, dx, dw, 3)
+    go, xc, wc = grad_output.contiguous(), x.contiguous(), w.contiguous()
+    N, K, L = xc.shape
+    O = wc.shape[1]
+    _require(wc.shape[0] == K, "w.shape[0] must equal K")
+    _require(tuple(go.shape) == (N, O, L), "grad_output shape must be [N, O, L]")
+    if N == 0 or K == 0 or L == 0 or O == 0:
+        return (torch.zeros((N, K, L), dtype=torch.float32, device=x.device),
+                torch.zeros((K, O), dtype=torch.float32, device=x.device))
+    return lre_backward_launch(go, xc, wc, False, dx.contiguous(), dw.contiguous())
+
+
+def _lre_backward_im2col(grad_output, x, w, dx, dw, kh, kw, sh, sw, ph, pw, dh, dw_):
+    _lre_checks(grad_output, x, w, dx, dw, 4)
+    _geometry_ok(kh, kw, sh, sw, ph, pw, dh, dw_)
+    go, xc, wc = grad_output.contiguous(), x.contiguous(), w.contiguous()
+    N, C, H, W = xc.shape
+    K = C * kh * kw
+    O = wc.shape[1]
+    _require(wc.shape[0] == K, "w.shape[0] must equal C*kh*kw")
+    OH, OW = conv_out_hw(H, W, kh, kw, sh, sw, ph, pw, dh, dw_)
+    _require(OH >= 1 and OW >= 1, "conv geometry yields empty output")
+    L = OH * OW
+    _require(tuple(go.shape) == (N, O, L), f"grad_output shape must be [N, O, OH*OW] for this geometry, expected L={L}")
+    if N == 0 or K == 0 or L == 0 or O == 0:
+        return (torch.zeros((N, K, L), dtype=torch.float32, device=x.device),
+                torch.zeros((K, O), dtype=torch.float32, device=x.device))
+    dxc, dwc = dx.contiguous(), dw.contiguous()
+    # grad_x stays in column space [N,K,L] (it never reads x); grad_w gathers the image taps on the fly
+    gx = torch.empty((N, K, L), dtype=torch.float32, device=go.device)
+    with _Guard(go):
+        _check(_lib.atb_lre_bwd(_ptr(go), None, U8, _ptr(wc), _DTYPE_CODE[wc.dtype], 0, _ptr(dxc), None, _ptr(gx),
+                                None, N, K, L, O, _stream(go)), "atb_lre_bwd")
+    geom = ((kh, kw), (sh, sw), (ph, pw), (dh, dw_))
+    _, gw_ok = lre_conv_backward(go.view(N, O, OH, OW), xc, None, None, dwc, geom, 128, need_x=False)
+    return gx, gw_ok.t().contiguous()
+
+
+def _custom_grad(X: Tensor, W: Tensor, dY: Tensor, table: Tensor, want: str, expect: torch.dtype):
+    _require(X.is_cuda and W.is_cuda and dY.is_cuda and table.is_cuda, "all tensors must be CUDA")
+    _require(X.dtype == expect and W.dtype == expect, f"X and W must have dtype {expect}")
+    _require(dY.dtype == torch.float32 and table.dtype == torch.float32, "dY and the gradient LUT must be float32")
+    _require(X.dim() == 3 and W.dim() == 2 and dY.dim() == 3, "expected X [N,K,L], W [O,K], dY [N,O,L]")
+    Xc, Wc, dYc = X.contiguous(), W.contiguous(), dY.contiguous()
+    tab = table.contiguous().view(-1)
+    N, K, L = Xc.shape
+    O = Wc.shape[0]
+    _require(Wc.shape[1] == K, "W.size(1) must equal X.size(1)")
+    _require(tuple(dYc.shape) == (N, O, L), "dY shape must be [N, O, L]")
+    _require(tab.numel() == 65536, "gradient LUT must have 65536 elements")
+    if expect == torch.int8:     # signed values -> LUT indices
+        Xc = (Xc.view(torch.uint8) ^ 0x80)
+        Wc = (Wc.view(torch.uint8) ^ 0x80)
+    with _Guard(X):
+        if want == "dx":
+            out = torch.empty((N, K, L), dtype=torch.float32, device=X.device)
+            if out.numel():
+                _check(_lib.atb_custom_bwd_dx(_ptr(Xc), _ptr(Wc), _ptr(dYc), _ptr(tab), _ptr(out), N, K, L, O,
+                                              _stream(X)), "atb_custom_bwd_dx")
+        else:
+            out = torch.empty((O, K), dtype=torch.float32, device=X.device)
+            if out.numel():
+                _check(_lib.atb_custom_bwd_dw(_ptr(Xc), _ptr(Wc), _ptr(dYc), _ptr(tab), _ptr(out), N, K, L, O,
+                                              _stream(X)), "atb_custom_bwd_dw")
+    return out
+
+
+def _dwconv(x: Tensor, w: Tensor, lut: Tensor, kh, kw, sh, sw, ph, pw, dh, dw):
+    _require(x.is_cuda and w.is_cuda, "x and w must be CUDA tensors")
+    _check_lut(lut)
+    code = _qcode(x, "x")
+    _require(w.dtype == torch.float32, "w must be float32")
+    _require(x.dim() == 4, "x must have shape [N, C, H, W]")
+    _geometry_ok(kh, kw, sh, sw, ph, pw, dh, dw)
+    xc = x.contiguous()
+    N, C, H, W = xc.shape
+    _require(w.dim() == 2 and w.shape[0] == C and w.shape[1] == kh * kw, "w must have shape [C, kh*kw]")
+    OH, OW = conv_out_hw(H, W, kh, kw, sh, sw, ph, pw, dh, dw)
+    _require(OH >= 1 and OW >= 1, "conv geometry yields empty output")
+    wq = quantize_u8(w, 128)
+    y = torch.empty((N, C, OH, OW), dtype=torch.float32, device=x.device)
+    if y.numel():
+        with _Guard(x):
+            _check(_lib.atb_lut_dwconv_fwd(_ptr(xc), code, _ptr(wq), _ptr(lut_image(lut)), _ptr(y), N, C, H, W,
+                                           kh, kw, sh, sw, ph, pw, dh, dw, 128, _stream(x)), "atb_lut_dwconv_fwd")
+    return y, wq
+
+
+# --------------------------------------------------------------------------- torch.ops.approxtorch registration
+_SCHEMAS = {
+    "bgemm_fake_int8_forward_cuda_claude": "(Tensor x, Tensor w, Tensor lut) -> Tensor",
+    "bgemm_fake_int8_forward_cuda_claude_cfg": "(Tensor x, Tensor w, Tensor lut, int cfg) -> Tensor",
+    "bgemm_fake_int8_forward_cuda_claude_save": "(Tensor x, Tensor w, Tensor lut) -> (Tensor, Tensor, Tensor)",
+    "bgemm_fake_uint8_forward_cuda_claude": "(Tensor x, Tensor w, Tensor lut) -> Tensor",
+    "bgemm_fake_uint8_forward_cuda_claude_cfg": "(Tensor x, Tensor w, Tensor lut, int cfg) -> Tensor",
+    "bgemm_fake_uint8_forward_cuda_claude_save": "(Tensor x, Tensor w, Tensor lut) -> (Tensor, Tensor, Tensor)",
+    "gemm_fake_int8_forward_cuda_claude": "(Tensor A, Tensor B, Tensor lut) -> Tensor",
+    "gemm_fake_int8_forward_cuda_claude_cfg": "(Tensor A, Tensor B, Tensor lut, int cfg) -> Tensor",
+    "gemm_fake_int8_forward_cuda_claude_save": "(Tensor A, Tensor B, Tensor lut) -> (Tensor, Tensor, Tensor)",
+    "gemm_fake_uint8_forward_cuda_claude": "(Tensor A, Tensor B, Tensor lut) -> Tensor",
+    "gemm_fake_uint8_forward_cuda_claude_cfg": "(Tensor A, Tensor B, Tensor lut, int cfg) -> Tensor",
+    "gemm_fake_uint8_forward_cuda_claude_save": "(Tensor A, Tensor B, Tensor lut) -> (Tensor, Tensor, Tensor)",
+    "bgemm_lre_backward_claude": "(Tensor grad_output, Tensor x, Tensor w, Tensor dx, Tensor dw) -> (Tensor, Tensor)",
+    "bgemm_lre_backward_claude_cfg": "(Tensor grad_output, Tensor x, Tensor w, Tensor dx, Tensor dw, int cfg) -> (Tensor, Tensor)",
+    "bgemm_lre_backward_claude_im2col": "(Tensor grad_output, Tensor x, Tensor w, Tensor dx, Tensor dw, int kh, int kw, int sh, int sw, int ph, int pw, int dilh, int dilw) -> (Tensor, Tensor)",
+    "im2col_u8": "(Tensor x, int kh, int kw, int sh, int sw, int ph, int pw, int dilh, int dilw) -> Tensor",
+    "lut_map": "(Tensor x, Tensor lut) -> Tensor",
+    "lut_map_pad": "(Tensor x, Tensor lut, int ph, int pw) -> Tensor",
+    "fakequant_per_tensor_claude": "(Tensor x, Tensor scale, int qmin, int qmax) -> (Tensor, Tensor)",
+    "fakequant_per_tensor_backward_claude": "(Tensor grad_output, Tensor mask, Tensor scale) -> Tensor",
+    "fakequant_per_tensor_asymmetric_claude": "(Tensor x, Tensor scale, Tensor zero_point, int qmin, int qmax) -> (Tensor, Tensor)",
+    "fakequant_per_tensor_asymmetric_backward_claude": "(Tensor grad_output, Tensor mask, Tensor scale) -> Tensor",
+    "bgemm_custom_grad_uint8_dx": "(Tensor X, Tensor W, Tensor dY, Tensor dx_lut) -> Tensor",
+    "bgemm_custom_grad_uint8_dw": "(Tensor X, Tensor W, Tensor dY, Tensor dw_lut) -> Tensor",
+    "bgemm_custom_grad_int8_dx": "(Tensor X, Tensor W, Tensor dY, Tensor dx_lut) -> Tensor",
+    "bgemm_custom_grad_int8_dw": "(Tensor X, Tensor W, Tensor dY, Tensor dw_lut) -> Tensor",
+    "dwconv_fake_int8_claude": "(Tensor x, Tensor w, Tensor lut, int kh, int kw, int sh, int sw, int ph, int pw, int dilh, int dilw) -> (Tensor, Tensor)",
+}
+
+_IMPLS = {
+    "bgemm_fake_int8_forward_cuda_claude": lambda x, w, lut: _bgemm_save(x, w, lut, -1, 128)[0],
+    "bgemm_fake_int8_forward_cuda_claude_cfg": lambda x, w, lut, cfg: _bgemm_save(x, w, lut, cfg, 128)[0],
+    "bgemm_fake_int8_forward_cuda_claude_save": lambda x, w, lut: _bgemm_save(x, w, lut, -1, 128),
+    "bgemm_fake_uint8_forward_cuda_claude": lambda x, w, lut: _bgemm_save(x, w, lut, -1, 0)[0],
+    "bgemm_fake_uint8_forward_cuda_claude_cfg": lambda x, w, lut, cfg: _bgemm_save(x, w, lut, cfg, 0)[0],
+    "bgemm_fake_uint8_forward_cuda_claude_save": lambda x, w, lut: _bgemm_save(x, w, lut, -1, 0),
+    "gemm_fake_int8_forward_cuda_claude": lambda A, B, lut: _gemm_save(A, B, lut, -1, 128)[0],
+    "gemm_fake_int8_forward_cuda_claude_cfg": lambda A, B, lut, cfg: _gemm_save(A, B, lut, cfg, 128)[0],
+    "gemm_fake_int8_forward_cuda_claude_save": lambda A, B, lut: _gemm_save(A, B, lut, -1, 128),
+    "gemm_fake_uint8_forward_cuda_claude": lambda A, B, lut: _gemm_save(A, B, lut, -1, 0)[0],
+    "gemm_fake_uint8_forward_cuda_claude_cfg": lambda A, B, lut, cfg: _gemm_save(A, B, lut, cfg, 0)[0],
+    "gemm_fake_uint8_forward_cuda_claude_save": lambda A, B, lut: _gemm_save(A, B, lut, -1, 0),
+    "bgemm_lre_backward_claude": lambda go, x, w, dx, dw: _lre_backward(go, x, w, dx, dw),
+    "bgemm_lre_backward_claude_cfg": lambda go, x, w, dx, dw, cfg: _lre_backward(go, x, w, dx, dw, cfg),
+    "bgemm_lre_backward_claude_im2col": _lre_backward_im2col,
+    "im2col_u8": lambda x, kh, kw, sh, sw, ph, pw, dilh, dilw: _im2col_u8(x, kh, kw, sh, sw, ph, pw, dilh, dilw),
+    "lut_map": _lut_map,
+    "lut_map_pad": _lut_map_pad,
+    "fakequant_per_tensor_claude": lambda x, scale, qmin, qmax: _fakequant(x, scale, None, qmin, qmax),
+    "fakequant_per_tensor_backward_claude": _fakequant_backward,
+    "fakequant_per_tensor_asymmetric_claude": _fakequant,
+    "fakequant_per_tensor_asymmetric_backward_claude": _fakequant_backward,
+    "bgemm_custom_grad_uint8_dx": lambda X, W, dY, t: _custom_grad(X, W, dY, t, "dx", torch.uint8),
+    "bgemm_custom_grad_uint8_dw": lambda X, W, dY, t: _custom_grad(X, W, dY, t, "dw", torch.uint8),
+    "bgemm_custom_grad_int8_dx": lambda X, W, dY, t: _custom_grad(X, W, dY, t, "dx", torch.int8),
+    "bgemm_custom_grad_int8_dw": lambda X, W, dY, t: _custom_grad(X, W, dY, t, "dw", torch.int8),
+    "dwconv_fake_int8_claude": _dwconv,
+}
+
+_library = torch.library.Library("approxtorch", "FRAGMENT")
+for _name, _schema in _SCHEMAS.items():
+    _library.define(_name + _schema)
+    _library.impl(_name, _IMPLS[_name], "CUDA")
+
+OPERATOR_NAMES = tuple(_SCHEMAS)
+
+
+# --------------------------------------------------------------------------- reference-named Python wrappers
+def bgemm_fake_int8_claude(X: Tensor, W: Tensor, lut: Tensor) -> Tensor:
+    """y[n,o,l] = sum_k lut[(X[n,k,l]+128)*256 + (W[o,k]+128)]; X fp32 integer values or uint8 indices."""
+    return torch.ops.approxtorch.bgemm_fake_int8_forward_cuda_claude.default(X, W, lut)
+
+
+def bgemm_fake_int8_claude_save(X: Tensor, W: Tensor, lut: Tensor):
+    """Same forward; also returns the uint8 index images (xq [N,K,L], wq [O,K]) for a backward to keep."""
+    return torch.ops.approxtorch.bgemm_fake_int8_forward_cuda_claude_save.default(X, W, lut)
+
+
+def bgemm_fake_uint8_claude(X: Tensor, W: Tensor, lut: Tensor) -> Tensor:
+    """uint8 x uint8 table: y[n,o,l] = sum_k lut[X[n,k,l]*256 + W[o,k]]; zero-point terms are the caller's."""
+    return torch.ops.approxtorch.bgemm_fake_uint8_forward_cuda_claude.default(X, W, lut)
+
+
+def bgemm_fake_uint8_claude_save(X: Tensor, W: Tensor, lut: Tensor):
+    return torch.ops.approxtorch.bgemm_fake_uint8_forward_cuda_claude_save.default(X, W, lut)
+
+
+def gemm_fake_int8_claude(A: Tensor, B: Tensor, lut: Tensor) -> Tensor:
+    """torch.mm layout: A [M,K] @ B [K,N] -> y [M,N] through the table; B may have any strides."""
+    return torch.ops.approxtorch.gemm_fake_int8_forward_cuda_claude.default(A, B, lut)
+
+
+def gemm_fake_int8_claude_save(A: Tensor, B: Tensor, lut: Tensor):
+    """Also returns aq [M,K] and bq [N,K] (bq is the TRANSPOSED index image of B)."""
+    return torch.ops.approxtorch.gemm_fake_int8_forward_cuda_claude_save.default(A, B, lut)
+
+
+def gemm_fake_uint8_claude(A: Tensor, B: Tensor, lut: Tensor) -> Tensor:
+    return torch.ops.approxtorch.gemm_fake_uint8_forward_cuda_claude.default(A, B, lut)
+
+
+def gemm_fake_uint8_claude_save(A: Tensor, B: Tensor, lut: Tensor):
+    return torch.ops.approxtorch.gemm_fake_uint8_forward_cuda_claude_save.default(A, B, lut)
+
+
+def bgemm_lre_backward_claude(grad_output: Tensor, x: Tensor, w: Tensor, dx: Tensor, dw: Tensor):
+    """(grad_x [N,K,L], grad_w [K,O]) for x [N,K,L], w [K,O] (fp32 / int8 / uint8) and 256-entry slopes."""
+    return torch.ops.approxtorch.bgemm_lre_backward_claude.default(grad_output, x, w, dx, dw)
+
+
+def bgemm_lre_backward_claude_im2col(grad_output, x, w, dx, dw, kernel_size, stride, padding, dilation):
+    """x is the pre-unfold quantised image [N,C,H,W]; grad_x is still returned in column space."""
+    kh, kw = _pair(kernel_size)
+    sh, sw = _pair(stride)
+    ph, pw = _pair(padding)
+    dilh, dilw = _pair(dilation)
+    return torch.ops.approxtorch.bgemm_lre_backward_claude_im2col.default(
+        grad_output, x, w, dx, dw, kh, kw, sh, sw, ph, pw, dilh, dilw)
+
+
+def im2col_u8(feature: Tensor, kernel_size, stride=1, padding=0, dilation=1) -> Tensor:
+    """Quantised image [N,C,H,W] -> uint8 LUT indices [N, C*kh*kw, L]; padding maps to index 128."""
+    kh, kw = _pair(kernel_size)
+    sh, sw = _pair(stride)
+    ph, pw = _pair(padding)
+    dilh, dilw = _pair(dilation)
+    return torch.ops.approxtorch.im2col_u8.default(feature, kh, kw, sh, sw, ph, pw, dilh, dilw)
+
+
+def lut_map(x: Tensor, lut: Tensor) -> Tensor:
+    """out[i] = lut[idx(x[i])] for a 256-entry table."""
+    return torch.ops.approxtorch.lut_map.default(x, lut)
+
+
+def lut_map_pad(x: Tensor, lut: Tensor, padding) -> Tensor:
+    """lut_map of an image with a constant border lut[128]."""
+    ph, pw = _pair(padding)
+    return torch.ops.approxtorch.lut_map_pad.default(x, lut, ph, pw)
+
+
+def bgemm_custom_grad_uint8_dx(X, W, dY, dx_lut):
+    return torch.ops.approxtorch.bgemm_custom_grad_uint8_dx.default(X, W, dY, dx_lut)
+
+
+def bgemm_custom_grad_uint8_dw(X, W, dY, dW_lut):
+    return torch.ops.approxtorch.bgemm_custom_grad_uint8_dw.default(X, W, dY, dW_lut)
+
+
+def bgemm_custom_grad_int8_dx(X, W, dY, dx_lut):
+    return torch.ops.approxtorch.bgemm_custom_grad_int8_dx.default(X, W, dY, dx_lut)
+
+
+def bgemm_custom_grad_int8_dw(X, W, dY, dW_lut):
+    return torch.ops.approxtorch.bgemm_custom_grad_int8_dw.default(X, W, dY, dW_lut)
+
+
+def dwconv_fake_int8_claude(x, w, lut, kernel_size, stride=1, padding=0, dilation=1):
+    """Depthwise LUT conv forward (groups == C): returns (y [N,C,OH,OW], wq [C, kh*kw] uint8 indices)."""
+    kh, kw = _pair(kernel_size)
+    sh, sw = _pair(stride)
+    ph, pw = _pair(padding)
+    dilh, dilw = _pair(dilation)
+    return torch.ops.approxtorch.dwconv_fake_int8_claude.default(x, w, lut, kh, kw, sh, sw, ph, pw, dilh, dilw)

@@ -1,0 +1,389 @@
+// STE / LRE backward: dense fp32 contractions whose operands are 256-entry table maps of the saved
+// 8-bit tensors.  The maps, the im2col gather and the fold are fused into the operand fetch of one
+// tiled fp32 GEMM kernel (128 x 128 x 8 tiles, 8 x 8 outputs per thread), so neither the mapped
+// operand X' = dw[idx(x)] nor the column matrix is ever written to memory
+// (approxtorch/backend/csrc/claude/bgemm_lre_backward_claude.cu:443-524 materialises X' for cuBLAS;
+// approxtorch/nn/bgemm_int8.py:165-212, 259-295 hands the image form to cuDNN).
+//
+//   grad_x[n,k,l] = sum_o go[n,o,l] * dx[idx(w[o,k])]        grad_w[o,k] = sum_{n,l} go[n,o,l] * dw[idx(x[n,k,l])]
+//
+// fp32 FMA throughout (no TF32): these gradients carry a rel-1e-5 bar.  grad_w reduces over all
+// pixels, so its launch is split over the pixel axis and the partial tiles are added with fp32
+// atomics into a zeroed output.
+#include "common.cuh"
+
+namespace atb {
+
+struct FastDiv {
+    unsigned d, mul, shift;
+};
+
+static FastDiv make_fastdiv(unsigned d)
+{
+    FastDiv f;
+    f.d = d < 1 ? 1 : d;
+    unsigned s = 0;
+    while ((1ull << s) < f.d) ++s;
+    f.shift = s;
+    f.mul = static_cast<unsigned>((((1ull << s) - f.d) << 32) / f.d + 1);
+    return f;
+}
+
+// valid for n < 2^31
+__device__ __forceinline__ unsigned fdiv(unsigned n, const FastDiv& f)
+{
+    return (__umulhi(n, f.mul) + n) >> f.shift;
+}
+
+__device__ __forceinline__ int index_rt(const void* base, long long i, int dtype)
+{
+    if (dtype == ATB_U8) return index_of<ATB_U8>(base, i);
+    if (dtype == ATB_I8) return index_of<ATB_I8>(base, i);
+    return index_of<ATB_F32>(base, i);
+}
+
+constexpr int TM = 128, TN = 128, TK = 8, PITCH = 132;
+
+// ------------------------------------------------------------------------------------------------
+// problem descriptions: a(m, r), b(r, n), store(m, n, v)
+// ------------------------------------------------------------------------------------------------
+
+// column space, grad_x of batch item z:  C[k, l] = sum_o dx[idx(w[o,k])] * go[z, o, l]
+struct ColGradX {
+    const float* go; const void* w; int w_dtype; int w_ok; const float* dx; float* gx;
+    int K, L, O;
+    long long z;
+    static constexpr bool kAtomic = false, kARFast = false, kBRFast = false;
+    __device__ int M() const { return K; }
+    __device__ int N() const { return L; }
+    __device__ void setup(int zz, int nz, int& rbeg, int& rend) { z = zz; rbeg = 0; rend = O; }
+    __device__ float a(int k, int o) const
+    {
+        const long long i = w_ok ? static_cast<long long>(o) * K + k : static_cast<long long>(k) * O + o;
+        return __ldg(dx + index_rt(w, i, w_dtype));
+    }
+    __device__ float b(int o, int l) const { return __ldg(go + (z * O + o) * L + l); }
+    __device__ void store(int k, int l, float v) const { gx[(z * K + k) * L + l] = v; }
+};
+
+// column space, grad_w:  C[o, k] = sum_{p=(n,l)} go[n,o,l] * dw[idx(x[n,k,l])]
+struct ColGradW {
+    const float* go; const void* x; int x_dtype; const float* dw; float* gw; int w_ok;
+    int K, L, O; long long P;
+    FastDiv divL;
+    static constexpr bool kAtomic = true, kARFast = true, kBRFast = true;
+    __device__ int M() const { return O; }
+    __device__ int N() const { return K; }
+    __device__ void setup(int zz, int nz, int& rbeg, int& rend)
+    {
+        const long long per = ((P + nz - 1) / nz + TK - 1) / TK * TK;
+        const long long b0 = per * zz;
+        rbeg = static_cast<int>(b0 < P ? b0 : P);
+        rend = static_cast<int>(b0 + per < P ? b0 + per : P);
+    }
+    __device__ float a(int o, int p) const
+    {
+        const unsigned n = fdiv(p, divL);
+        const unsigned l = p - n * L;
+        return __ldg(go + (static_cast<long long>(n) * O + o) * L + l);
+    }
+    __device__ float b(int p, int k) const
+    {
+        const unsigned n = fdiv(p, divL);
+        const unsigned l = p - n * L;
+        return __ldg(dw + index_rt(x, (static_cast<long long>(n) * K + k) * L + l, x_dtype));
+    }
+    __device__ void store(int o, int k, float v) const
+    {
+        atomicAdd(gw + (w_ok ? static_cast<long long>(o) * K + k : static_cast<long long>(k) * O + o), v);
+    }
+};
+
+// image space, grad_x:  C[m=(n,h,w), c] = sum_{r=(o,i,j)} go[n,o,oh,ow] * gs[o] * dx[widx[o,(c,i,j)]]
+struct ConvGradX {
+    const float* go; const uint8_t* widx; const float* dx; const float* gs; float* gx;
+    int Nb, O, K; ConvGeom g;
+    FastDiv divHW, divW, divKK, divKW, divSH, divSW;
+    static constexpr bool kAtomic = false, kARFast = false, kBRFast = false;
+    __device__ int M() const { return Nb * g.H * g.W; }
+    __device__ int N() const { return g.C; }
+    __device__ void setup(int zz, int nz, int& rbeg, int& rend) { rbeg = 0; rend = O * g.KH * g.KW; }
+    __device__ float a(int m, int r) const
+    {
+        const unsigned n = fdiv(m, divHW);
+        const unsigned hw = m - n * (g.H * g.W);
+        const unsigned h = fdiv(hw, divW);
+        const unsigned w = hw - h * g.W;
+        const unsigned o = fdiv(r, divKK);
+        const unsigned ij = r - o * (g.KH * g.KW);
+        const unsigned i = fdiv(ij, divKW);
+        const unsigned j = ij - i * g.KW;
+        const int th = static_cast<int>(h) + g.PH - static_cast<int>(i) * g.DH;
+        const int tw = static_cast<int>(w) + g.PW - static_cast<int>(j) * g.DW;
+        if (th < 0 || tw < 0) return 0.0f;
+        const unsigned oh = fdiv(th, divSH), ow = fdiv(tw, divSW);
+        if (oh * g.SH != static_cast<unsigned>(th) || ow * g.SW != static_cast<unsigned>(tw)) return 0.0f;
+        if (oh >= static_cast<unsigned>(g.OH) || ow >= static_cast<unsigned>(g.OW)) return 0.0f;
+        return __ldg(go + ((static_cast<long long>(n) * O + o) * g.OH + oh) * g.OW + ow);
+    }
+    __device__ float b(int r, int c) const
+    {
+        const unsigned o = fdiv(r, divKK);
+        const unsigned ij = r - o * (g.KH * g.KW);
+        float v = __ldg(dx + __ldg(widx + static_cast<long long>(o) * K + c * (g.KH * g.KW) + ij));
+        if (gs != nullptr) v *= __ldg(gs + o);
+        return v;
+    }
+    __device__ void store(int m, int c, float v) const
+    {
+        const unsigned n = fdiv(m, divHW);
+        const unsigned hw = m - n * (g.H * g.W);
+        gx[(static_cast<long long>(n) * g.C + c) * (g.H * g.W) + hw] = v;
+    }
+};
+
+// image space, grad_w:  C[o, k=(c,i,j)] = gs[o] * sum_{p=(n,oh,ow)} go[n,o,oh,ow] * dw[idx(x[n,c,ih,iw]) or pad]
+struct ConvGradW {
+    const float* go; const void* x; int x_dtype; const float* dw; const float* gs; float* gw;
+    int O, K, pad_index; long long P; ConvGeom g;
+    FastDiv divL, divOW, divKK, divKW;
+    static constexpr bool kAtomic = true, kARFast = true, kBRFast = true;
+    __device__ int M() const { return O; }
+    __device__ int N() const { return K; }
+    __device__ void setup(int zz, int nz, int& rbeg, int& rend)
+    {
+        const long long per = ((P + nz - 1) / nz + TK - 1) / TK * TK;
+        const long long b0 = per * zz;
+        rbeg = static_cast<int>(b0 < P ? b0 : P);
+        rend = static_cast<int>(b0 + per < P ? b0 + per : P);
+    }
+    __device__ float a(int o, int p) const
+    {
+        const unsigned n = fdiv(p, divL);
+        const unsigned l = p - n * (g.OH * g.OW);
+        return __ldg(go + (static_cast<long long>(n) * O + o) * (g.OH * g.OW) + l);
+    }
+    __device__ float b(int p, int k) const
+    {
+        const unsigned n = fdiv(p, divL);
+        const unsigned l = p - n * (g.OH * g.OW);
+        const unsigned oh = fdiv(l, divOW);
+        const unsigned ow = l - oh * g.OW;
+        const unsigned c = fdiv(k, divKK);
+        const unsigned ij = k - c * (g.KH * g.KW);
+        const unsigned i = fdiv(ij, divKW);
+        const unsigned j = ij - i * g.KW;
+        const int ih = static_cast<int>(oh) * g.SH - g.PH + static_cast<int>(i) * g.DH;
+        const int iw = static_cast<int>(ow) * g.SW - g.PW + static_cast<int>(j) * g.DW;
+        int idx = pad_index;
+        if (static_cast<unsigned>(ih) < static_cast<unsigned>(g.H) && static_cast<unsigned>(iw) < static_cast<unsigned>(g.W))
+            idx = index_rt(x, ((static_cast<long long>(n) * g.C + c) * g.H + ih) * g.W + iw, x_dtype);
+        return __ldg(dw + idx);
+    }
+    __device__ void store(int o, int k, float v) const
+    {
+        if (gs != nullptr) v *= __ldg(gs + o);
+        atomicAdd(gw + static_cast<long long>(o) * K + k, v);
+    }
+};
+
+// ------------------------------------------------------------------------------------------------
+// the tiled kernel
+// ------------------------------------------------------------------------------------------------
+template <class Prob>
+__global__ void __launch_bounds__(256) fused_sgemm_kernel(const Prob prob_in)
+{
+    __shared__ float As[2][TK][PITCH];
+    __shared__ float Bs[2][TK][PITCH];
+    Prob p = prob_in;
+    int rbeg, rend;
+    p.setup(blockIdx.z, gridDim.z, rbeg, rend);
+    const int M = p.M(), N = p.N();
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
+    const int tx = tid & 15, ty = tid >> 4;
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+    if (rbeg >= rend) {
+        if (Prob::kAtomic) return;     // nothing to add
+    }
+
+    float ra[4], rb[4];
+    auto fetch = [&](int r0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int e = tid + 256 * q;
+            const int ml = Prob::kARFast ? (e >> 3) : (e & 127);
+            const int rl = Prob::kARFast ? (e & 7) : (e >> 7);
+            const int m = m0 + ml, r = r0 + rl;
+            ra[q] = (m < M && r < rend) ? p.a(m, r) : 0.0f;
+            const int nl = Prob::kBRFast ? (e >> 3) : (e & 127);
+            const int sl = Prob::kBRFast ? (e & 7) : (e >> 7);
+            const int n = n0 + nl, s = r0 + sl;
+            rb[q] = (n < N && s < rend) ? p.b(s, n) : 0.0f;
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int e = tid + 256 * q;
+            const int ml = Prob::kARFast ? (e >> 3) : (e & 127);
+            const int rl = Prob::kARFast ? (e & 7) : (e >> 7);
+            As[buf][rl][ml] = ra[q];
+            const int nl = Prob::kBRFast ? (e >> 3) : (e & 127);
+            const int sl = Prob::kBRFast ? (e & 7) : (e >> 7);
+            Bs[buf][sl][nl] = rb[q];
+        }
+    };
+
+    const int ntiles = (rend - rbeg + TK - 1) / TK;
+    if (ntiles > 0) { fetch(rbeg); stash(0); }
+    __syncthreads();
+    for (int t = 0; t < ntiles; ++t) {
+        const int buf = t & 1;
+        if (t + 1 < ntiles) fetch(rbeg + (t + 1) * TK);
+#pragma unroll
+        for (int kk = 0; kk < TK; ++kk) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
+            const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        if (t + 1 < ntiles) stash(buf ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+            if (n < N) p.store(m, n, acc[i][j]);
+        }
+    }
+}
+
+__global__ void zero_kernel(float* p, long long n)
+{
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) p[i] = 0.0f;
+}
+
+static int split_factor(long long tiles, long long P)
+{
+    const int target = 3 * sm_count();
+    long long s = tiles >= target ? 1 : (target + tiles - 1) / tiles;
+    const long long maxs = (P + 4 * TK - 1) / (4 * TK);
+    if (s > maxs) s = maxs;
+    if (s > 1024) s = 1024;
+    if (s < 1) s = 1;
+    return static_cast<int>(s);
+}
+
+}  // namespace atb
+
+using namespace atb;
+
+extern "C" int atb_lre_bwd(const float* go, const void* x, int x_dtype, const void* w, int w_dtype, int w_ok_layout,
+                           const float* dx, const float* dw, float* grad_x, float* grad_w,
+                           int N, int K, int L, int O, void* stream)
+{
+    ATB_REQUIRE(N >= 0 && K >= 0 && L >= 0 && O >= 0, "negative dimension");
+    ATB_REQUIRE(x_dtype >= 0 && x_dtype <= 2 && w_dtype >= 0 && w_dtype <= 2, "bad dtype");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const long long P = static_cast<long long>(N) * L;
+    ATB_REQUIRE(P < 2147483647LL, "N*L too large");
+    int rc = ATB_OK;
+    if (grad_x != nullptr && P * K > 0) {
+        if (O == 0) {
+            zero_kernel<<<grid_for(P * K, 256, 4096), 256, 0, s>>>(grad_x, P * K);
+        } else {
+            ATB_REQUIRE(go && w && dx, "null pointer");
+            ATB_REQUIRE(N <= 65535, "batch above 65535 is not supported");
+            ColGradX p{go, w, w_dtype, w_ok_layout, dx, grad_x, K, L, O, 0};
+            dim3 grid(ceil_div(K, TM), ceil_div(L, TN), N);
+            ATB_REQUIRE(grid.y <= 65535, "L too large");
+            fused_sgemm_kernel<ColGradX><<<grid, 256, 0, s>>>(p);
+        }
+        rc = check_launch("lre grad_x");
+        if (rc != ATB_OK) return rc;
+    }
+    if (grad_w != nullptr && static_cast<long long>(O) * K > 0) {
+        zero_kernel<<<grid_for(static_cast<long long>(O) * K, 256, 4096), 256, 0, s>>>(grad_w, static_cast<long long>(O) * K);
+        rc = check_launch("zero_kernel");
+        if (rc != ATB_OK) return rc;
+        if (P > 0) {
+            ATB_REQUIRE(go && x && dw, "null pointer");
+            ColGradW p{go, x, x_dtype, dw, grad_w, w_ok_layout, K, L, O, P, make_fastdiv(L)};
+            dim3 grid(ceil_div(O, TM), ceil_div(K, TN), 1);
+            ATB_REQUIRE(grid.y <= 65535, "K too large");
+            grid.z = split_factor(static_cast<long long>(grid.x) * grid.y, P);
+            fused_sgemm_kernel<ColGradW><<<grid, 256, 0, s>>>(p);
+            rc = check_launch("lre grad_w");
+        }
+    }
+    return rc;
+}
+
+extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t* widx,
+                                const float* dx, const float* dw, const float* go_scale,
+                                float* grad_x, float* grad_w,
+                                int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
+                                int dh, int dw_, int pad_index, void* stream)
+{
+    ATB_REQUIRE(N >= 0 && C >= 0 && H >= 0 && W >= 0 && O >= 0, "negative dimension");
+    ATB_REQUIRE(x_dtype >= 0 && x_dtype <= 2, "bad dtype");
+    ATB_REQUIRE(pad_index >= 0 && pad_index <= 255, "pad_index out of range");
+    int OH = 0, OW = 0;
+    ATB_REQUIRE(conv_out_shape(H, W, kh, kw, sh, sw, ph, pw, dh, dw_, &OH, &OW), "conv geometry yields empty output");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const ConvGeom g{C, H, W, kh, kw, sh, sw, ph, pw, dh, dw_, OH, OW};
+    const long long K = static_cast<long long>(C) * kh * kw;
+    const long long Mx = static_cast<long long>(N) * H * W;
+    const long long P = static_cast<long long>(N) * OH * OW;
+    ATB_REQUIRE(Mx < 2147483647LL && P < 2147483647LL && K < 2147483647LL &&
+                static_cast<long long>(O) * kh * kw < 2147483647LL, "dimensions too large");
+    int rc = ATB_OK;
+    if (grad_x != nullptr && Mx * C > 0) {
+        if (O == 0) {
+            zero_kernel<<<grid_for(Mx * C, 256, 4096), 256, 0, s>>>(grad_x, Mx * C);
+        } else {
+            ATB_REQUIRE(go && widx && dx, "null pointer");
+            ConvGradX p{go, widx, dx, go_scale, grad_x, N, O, static_cast<int>(K), g,
+                        make_fastdiv(H * W), make_fastdiv(W), make_fastdiv(kh * kw), make_fastdiv(kw),
+                        make_fastdiv(sh), make_fastdiv(sw)};
+            dim3 grid(ceil_div(Mx, TM), ceil_div(C, TN), 1);
+            ATB_REQUIRE(grid.y <= 65535, "C too large");
+            fused_sgemm_kernel<ConvGradX><<<grid, 256, 0, s>>>(p);
+        }
+        rc = check_launch("conv grad_x");
+        if (rc != ATB_OK) return rc;
+    }
+    if (grad_w != nullptr && O * K > 0) {
+        zero_kernel<<<grid_for(O * K, 256, 4096), 256, 0, s>>>(grad_w, O * K);
+        rc = check_launch("zero_kernel");
+        if (rc != ATB_OK) return rc;
+        if (P > 0) {
+            ATB_REQUIRE(go && x && dw, "null pointer");
+            ConvGradW p{go, x, x_dtype, dw, go_scale, grad_w, O, static_cast<int>(K), pad_index, P, g,
+                        make_fastdiv(OH * OW), make_fastdiv(OW), make_fastdiv(kh * kw), make_fastdiv(kw)};
+            dim3 grid(ceil_div(O, TM), ceil_div(K, TN), 1);
+            ATB_REQUIRE(grid.y <= 65535, "K too large");
+            grid.z = split_factor(static_cast<long long>(grid.x) * grid.y, P);
+            fused_sgemm_kernel<ConvGradW><<<grid, 256, 0, s>>>(p);
+            rc = check_launch("conv grad_w");
+        }
+    }
+    return rc;
+}

@@ -1,0 +1,555 @@
+// LUT GEMM / approximate Conv2d forward for sm_100a.
+//
+//   acc[r, o] = sum_k lut[x_idx(r, k)][w_idx(o, k)]          r = pixel row (n, l), o = output channel
+//
+// A table lookup is not a dense contraction, so this kernel does not use the tensor cores; its
+// roofline is the shared-memory load pipe (32 four-byte bank reads per clock per SM).  A plain
+// gather from a 128 KB table in shared memory would spend ~3.4 bank wavefronts per 32 lookups on
+// uniformly distributed operands, because 32 data-dependent addresses collide in the 32 banks.
+// The kernel removes those collisions by construction:
+//
+//  * The whole transposed 16-bit table (tabT[w][x], 128 KB) is resident in shared memory.
+//  * For every k-step the block STAGES the 64 table columns its 64 output channels need:
+//    staged row c = tabT[w_idx(c, k)][0..255], copied (conflict-free, 512 contiguous bytes) to a
+//    row pitch of 516 bytes.  516/4 = 129 is odd, so for one activation value x the 32 lanes of a
+//    warp, each owning one staged row, hit 32 different banks: bank = (lane + x/2) mod 32.
+//  * The lookups of the step then read stage[lane][x] with a warp-uniform x (the activation of the
+//    pixel row a warp works on) and lane-dependent rows: one wavefront per 32 lookups.
+//  * Each thread keeps 32 pixel rows x 2 output channels of int32 accumulators in registers, so
+//    staging one column (8 wavefronts) is amortised over `block_rows` (up to 512) lookups.
+//
+// Integer-valued tables (the int16 / uint16 images) accumulate exactly in int32.  Tables that are
+// not 16-bit exact take the fp32 path: lookups go to the transposed fp32 table in global memory
+// (L1/L2 resident) and are summed in fp32 in ascending k, as the reference does
+// (approxtorch/backend/csrc/claude/bgemm_lut_kernels.cuh:278-281).
+//
+// The pixel operand is either a column matrix x[N,K,L] (L == 1: row-major A[M,K]) or the quantised
+// image itself with the im2col gather done in the tile loader, so the conv never materialises the
+// K/C-times larger column matrix (approxtorch/backend/csrc/claude/bgemm_lre_backward_claude.cu:216-269
+// is what it replaces).
+#include "common.cuh"
+
+namespace atb {
+
+constexpr int kStagedCols = 64;                          // output channels per thread block
+constexpr int kChunk = 16;                               // k-steps per operand tile
+constexpr int kRowPitch = 516;                           // bytes per staged row (256 x int16 + 4 B skew)
+constexpr int kStageBytes = kStagedCols * kRowPitch;     // 33024
+constexpr int kMaxBlockRows = 512;
+constexpr int kTableBytes = 65536 * 2;
+constexpr int kSmemStage = kTableBytes;
+constexpr int kSmemX = kSmemStage + 2 * kStageBytes;
+constexpr int kSmemW = kSmemX + 2 * kChunk * kMaxBlockRows;
+constexpr int kSmemTotal = kSmemW + 2 * kChunk * kStagedCols;   // 215552 bytes
+
+struct GemmArgs {
+    const uint8_t* x;
+    const uint8_t* w;
+    const LutImage* img;
+    float* y;
+    int* scratch;          // split-K partials [S][R][O] followed by row sums [S][R]
+    long long R;           // pixel rows
+    int K, L, O;
+    int wb_rows;           // pixel rows per weight matrix (0: one matrix for all rows)
+    long long w_batch_stride;
+    int tiles_per_batch;   // row tiles per weight batch (wb_rows != 0)
+    int chunks_per_split, splits;
+    int image_mode;        // 1: x is the quantised image, gather taps in the loader
+    int x_xor;             // 0x80 when the image holds int8 values (idx = v + 128), else 0
+    int pad_index;
+    ConvGeom g;
+    const float* alpha;
+    const float* beta;
+    const float* zero_x;
+    const float* zero_w;
+    const int* wsum;
+};
+
+__device__ __forceinline__ float finalize_output(double total, long long xsum, int o, const GemmArgs& a)
+{
+    if (a.zero_x != nullptr) {
+        const long long zx = llrintf(__ldg(a.zero_x));
+        const long long zw = llrintf(__ldg(a.zero_w + o));
+        const long long ws = __ldg(a.wsum + o);
+        total += static_cast<double>(-zw * xsum - zx * ws + static_cast<long long>(a.K) * zx * zw);
+    }
+    float v = static_cast<float>(total);
+    if (a.alpha != nullptr) v = v * __ldg(a.alpha + o);
+    if (a.beta != nullptr) v = v + __ldg(a.beta + o);
+    return v;
+}
+
+__device__ __forceinline__ long long output_offset(long long r, int o, const GemmArgs& a)
+{
+    const long long n = r / a.L;
+    const long long l = r - n * a.L;
+    return (n * a.O + o) * a.L + l;
+}
+
+// One k-step of staging: every warp copies its share of the 64 table columns into `stage`.
+__device__ __forceinline__ void stage_columns(uint8_t* stage, const uint8_t* s_tab, const uint8_t* wstep,
+                                              int warp, int lane, int nwarps)
+{
+    const uint32_t* tab = reinterpret_cast<const uint32_t*>(s_tab);
+    for (int c = warp; c < kStagedCols; c += nwarps) {
+        const uint32_t* src = tab + static_cast<uint32_t>(wstep[c]) * 128u;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(stage + c * kRowPitch);
+        const uint32_t v0 = src[lane], v1 = src[lane + 32], v2 = src[lane + 64], v3 = src[lane + 96];
+        dst[lane] = v0;
+        dst[lane + 32] = v1;
+        dst[lane + 64] = v2;
+        dst[lane + 96] = v3;
+    }
+}
+
+template <int CLS>
+__device__ __forceinline__ void lookup_step(const uint8_t* stage, const uint8_t* xrow, int lane,
+                                            int (&acc)[32][2])
+{
+    const uint4 xa = *reinterpret_cast<const uint4*>(xrow);
+    const uint4 xb = *reinterpret_cast<const uint4*>(xrow + 16);
+    const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+    const uint8_t* base = stage + lane * kRowPitch;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const uint32_t xv = (xw[j >> 2] >> (8 * (j & 3))) & 0xffu;
+        const uint8_t* p = base + 2u * xv;
+        if constexpr (CLS == LUT_I16) {
+            acc[j][0] += static_cast<int>(*reinterpret_cast<const int16_t*>(p));
+            acc[j][1] += static_cast<int>(*reinterpret_cast<const int16_t*>(p + 32 * kRowPitch));
+        } else {
+            acc[j][0] += static_cast<int>(*reinterpret_cast<const uint16_t*>(p));
+            acc[j][1] += static_cast<int>(*reinterpret_cast<const uint16_t*>(p + 32 * kRowPitch));
+        }
+    }
+}
+
+__device__ __forceinline__ void lookup_step_f32(const float* tabT, const uint8_t* wstep, const uint8_t* xrow,
+                                                int lane, float (&acc)[32][2])
+{
+    const uint4 xa = *reinterpret_cast<const uint4*>(xrow);
+    const uint4 xb = *reinterpret_cast<const uint4*>(xrow + 16);
+    const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+    const float* c0 = tabT + (static_cast<uint32_t>(wstep[lane]) << 8);
+    const float* c1 = tabT + (static_cast<uint32_t>(wstep[lane + 32]) << 8);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const uint32_t xv = (xw[j >> 2] >> (8 * (j & 3))) & 0xffu;
+        acc[j][0] += __ldg(c0 + xv);
+        acc[j][1] += __ldg(c1 + xv);
+    }
+}
+
+// Per-thread view of the pixel operand: thread t of the block loads row r0 + t of every k-step.
+struct RowCursor {
+    const uint8_t* base;   // column mode: &x[n, 0, l]; image mode: &x[n, 0, 0, 0]
+    int ih0, iw0;          // image mode: top-left tap of the output pixel
+};
+
+__device__ __forceinline__ void load_chunk(const GemmArgs& a, const RowCursor& rc, const uint8_t* wcol,
+                                           bool vec_x, bool vec_w, int k0, int kend, int tid, int pad,
+                                           uint32_t (&xr)[4], uint32_t (&wr)[4])
+{
+    if (a.image_mode) {
+        const int khw = a.g.KH * a.g.KW;
+        int c = k0 / khw;
+        int rem = k0 - c * khw;
+        int i = rem / a.g.KW;
+        int j = rem - i * a.g.KW;
+        xr[0] = xr[1] = xr[2] = xr[3] = 0u;
+#pragma unroll
+        for (int kk = 0; kk < kChunk; ++kk) {
+            if (k0 + kk < kend) {
+                const int ih = rc.ih0 + i * a.g.DH;
+                const int iw = rc.iw0 + j * a.g.DW;
+                uint32_t v = static_cast<uint32_t>(pad);
+                if (static_cast<unsigned>(ih) < static_cast<unsigned>(a.g.H) &&
+                    static_cast<unsigned>(iw) < static_cast<unsigned>(a.g.W)) {
+                    v = static_cast<uint32_t>(__ldg(rc.base + (static_cast<long long>(c) * a.g.H + ih) * a.g.W + iw))
+                        ^ static_cast<uint32_t>(a.x_xor);
+                }
+                xr[kk >> 2] |= v << (8 * (kk & 3));
+            }
+            if (++j == a.g.KW) { j = 0; if (++i == a.g.KH) { i = 0; ++c; } }
+        }
+    } else if (vec_x) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(rc.base + k0));
+        xr[0] = v.x; xr[1] = v.y; xr[2] = v.z; xr[3] = v.w;
+    } else {
+        xr[0] = xr[1] = xr[2] = xr[3] = 0u;
+#pragma unroll
+        for (int kk = 0; kk < kChunk; ++kk) {
+            if (k0 + kk < kend) {
+                const uint32_t v = __ldg(rc.base + static_cast<long long>(k0 + kk) * a.L);
+                xr[kk >> 2] |= v << (8 * (kk & 3));
+            }
+        }
+    }
+    if (tid < kStagedCols) {
+        if (vec_w) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(wcol + k0));
+            wr[0] = v.x; wr[1] = v.y; wr[2] = v.z; wr[3] = v.w;
+        } else {
+            wr[0] = wr[1] = wr[2] = wr[3] = 0u;
+#pragma unroll
+            for (int kk = 0; kk < kChunk; ++kk) {
+                if (k0 + kk < kend) {
+                    const uint32_t v = __ldg(wcol + k0 + kk);
+                    wr[kk >> 2] |= v << (8 * (kk & 3));
+                }
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void store_chunk(uint8_t* s_x, uint8_t* s_w, int buf, int tid,
+                                            const uint32_t (&xr)[4], const uint32_t (&wr)[4])
+{
+    uint8_t* xd = s_x + buf * kChunk * kMaxBlockRows + tid;
+#pragma unroll
+    for (int kk = 0; kk < kChunk; ++kk)
+        xd[kk * kMaxBlockRows] = static_cast<uint8_t>(xr[kk >> 2] >> (8 * (kk & 3)));
+    if (tid < kStagedCols) {
+        uint8_t* wd = s_w + buf * kChunk * kStagedCols + tid;
+#pragma unroll
+        for (int kk = 0; kk < kChunk; ++kk)
+            wd[kk * kStagedCols] = static_cast<uint8_t>(wr[kk >> 2] >> (8 * (kk & 3)));
+    }
+}
+
+template <int CLS>
+__device__ __forceinline__ void gemm_body(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
+                                          const uint8_t* wcol, bool vec_x, bool vec_w, int pad,
+                                          long long r0, long long r_end, int c0, int kbeg, int kend)
+{
+    uint8_t* s_tab = smem;
+    uint8_t* s_stage = smem + kSmemStage;
+    uint8_t* s_x = smem + kSmemX;
+    uint8_t* s_w = smem + kSmemW;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int nwarps = blockDim.x >> 5;
+    const int nch = (kend - kbeg + kChunk - 1) / kChunk;
+
+    using acc_t = typename std::conditional<CLS == LUT_F32, float, int>::type;
+    acc_t acc[32][2];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { acc[j][0] = 0; acc[j][1] = 0; }
+    int xsum = 0;
+    const bool want_xsum = a.zero_x != nullptr;
+
+    uint32_t xr[4], wr[4];
+    if (nch > 0) {
+        load_chunk(a, rc, wcol, vec_x, vec_w, kbeg, kend, tid, pad, xr, wr);
+        store_chunk(s_x, s_w, 0, tid, xr, wr);
+    }
+    __syncthreads();
+    if (CLS != LUT_F32 && nch > 0) {
+        stage_columns(s_stage, s_tab, s_w, warp, lane, nwarps);
+        __syncthreads();
+    }
+
+    int step = 0;
+    for (int ci = 0; ci < nch; ++ci) {
+        const int k0 = kbeg + ci * kChunk;
+        const int kc = min(kChunk, kend - k0);
+        const int cur = ci & 1;
+        const bool has_next = ci + 1 < nch;
+        if (has_next) load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr);
+        for (int kk = 0; kk < kc; ++kk) {
+            if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr);
+            const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * 32;
+            const uint8_t* wstep = s_w + (cur * kChunk + kk) * kStagedCols;
+            if (want_xsum) xsum += static_cast<int>(xrow[lane]);
+            if constexpr (CLS == LUT_F32) {
+                lookup_step_f32(a.img->tabT32, wstep, xrow, lane, acc);
+                if (kk == kc - 1) __syncthreads();
+            } else {
+                const uint8_t* wnext = nullptr;
+                if (kk + 1 < kc) wnext = wstep + kStagedCols;
+                else if (has_next) wnext = s_w + ((cur ^ 1) * kChunk) * kStagedCols;
+                if (wnext != nullptr)
+                    stage_columns(s_stage + ((step + 1) & 1) * kStageBytes, s_tab, wnext, warp, lane, nwarps);
+                lookup_step<CLS>(s_stage + (step & 1) * kStageBytes, xrow, lane, acc);
+                __syncthreads();
+            }
+            ++step;
+        }
+    }
+
+    // ---- epilogue ----
+    const int split = blockIdx.z;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const long long r = r0 + warp * 32 + j;
+        const int xs = __shfl_sync(0xffffffffu, xsum, j);
+        if (r >= r_end) continue;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const int o = c0 + lane + 32 * t;
+            if (o >= a.O) continue;
+            if (a.splits > 1) {
+                int bits;
+                if constexpr (CLS == LUT_F32) bits = __float_as_int(acc[j][t]);
+                else bits = acc[j][t];
+                a.scratch[(static_cast<long long>(split) * a.R + r) * a.O + o] = bits;
+            } else {
+                a.y[output_offset(r, o, a)] = finalize_output(static_cast<double>(acc[j][t]), xs, o, a);
+            }
+        }
+        if (a.splits > 1 && want_xsum && blockIdx.y == 0 && lane == 0)
+            a.scratch[static_cast<long long>(a.splits) * a.R * a.O + static_cast<long long>(split) * a.R + r] = xs;
+    }
+}
+
+__global__ void __launch_bounds__(kMaxBlockRows, 1) lut_gemm_kernel(const GemmArgs a)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int tid = threadIdx.x;
+    const int bm = blockDim.x;
+
+    long long r0, r_end;
+    long long wbatch = 0;
+    if (a.wb_rows > 0) {
+        wbatch = blockIdx.x / a.tiles_per_batch;
+        const int t = blockIdx.x - static_cast<int>(wbatch) * a.tiles_per_batch;
+        r0 = wbatch * a.wb_rows + static_cast<long long>(t) * bm;
+        r_end = min(a.R, (wbatch + 1) * a.wb_rows);
+    } else {
+        r0 = static_cast<long long>(blockIdx.x) * bm;
+        r_end = a.R;
+    }
+    const int c0 = blockIdx.y * kStagedCols;
+    const int nchunks = (a.K + kChunk - 1) / kChunk;
+    const int ch_beg = blockIdx.z * a.chunks_per_split;
+    const int ch_end = min(nchunks, ch_beg + a.chunks_per_split);
+    const int kbeg = ch_beg * kChunk;
+    const int kend = min(a.K, ch_end * kChunk);
+
+    // this thread's pixel row for the tile loads (clamped: rows past the end are never stored)
+    const long long r = min(r0 + tid, r_end - 1);
+    RowCursor rc;
+    bool vec_x = false;
+    if (a.image_mode) {
+        const long long hw = static_cast<long long>(a.g.OH) * a.g.OW;
+        const long long n = r / hw;
+        const int rem = static_cast<int>(r - n * hw);
+        const int oh = rem / a.g.OW;
+        const int ow = rem - oh * a.g.OW;
+        rc.base = a.x + n * a.g.C * a.g.H * a.g.W;
+        rc.ih0 = oh * a.g.SH - a.g.PH;
+        rc.iw0 = ow * a.g.SW - a.g.PW;
+    } else {
+        const long long n = r / a.L;
+        const long long l = r - n * a.L;
+        rc.base = a.x + n * a.K * a.L + l;
+        rc.ih0 = rc.iw0 = 0;
+        vec_x = (a.L == 1) && (a.K % kChunk == 0) && ((reinterpret_cast<uintptr_t>(a.x) & 15) == 0);
+    }
+    const int ocol = min(c0 + tid, a.O - 1);
+    const uint8_t* wcol = a.w + wbatch * a.w_batch_stride + static_cast<long long>(ocol) * a.K;
+    const bool vec_w = (a.K % kChunk == 0) && ((reinterpret_cast<uintptr_t>(a.w) & 15) == 0) &&
+                       ((a.w_batch_stride & 15) == 0);
+
+    const int cls = lut_class_of(a.img);
+    if (cls != LUT_F32) {
+        const uint4* src = reinterpret_cast<const uint4*>(a.img->tabT16);
+        uint4* dst = reinterpret_cast<uint4*>(smem);
+        for (int i = tid; i < kTableBytes / 16; i += bm) dst[i] = __ldg(src + i);
+    }
+    // pad_index < 0: taps outside the image take the activation zero point (an integer-valued device scalar)
+    const int pad = a.pad_index >= 0 ? a.pad_index : min(255, max(0, static_cast<int>(llrintf(__ldg(a.zero_x)))));
+    if (cls == LUT_I16) gemm_body<LUT_I16>(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend);
+    else if (cls == LUT_U16) gemm_body<LUT_U16>(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend);
+    else gemm_body<LUT_F32>(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend);
+}
+
+// Split-K: y = finalize(sum_s partial[s]) in ascending split order.
+__global__ void lut_gemm_reduce_kernel(const GemmArgs a)
+{
+    const long long total = a.R * a.O;
+    const int cls = lut_class_of(a.img);
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long r = i / a.O;
+        const int o = static_cast<int>(i - r * a.O);
+        double sum = 0.0;
+        if (cls == LUT_F32) {
+            float f = 0.0f;
+            for (int s = 0; s < a.splits; ++s) f += __int_as_float(a.scratch[static_cast<long long>(s) * total + i]);
+            sum = f;
+        } else {
+            long long t = 0;
+            for (int s = 0; s < a.splits; ++s) t += a.scratch[static_cast<long long>(s) * total + i];
+            sum = static_cast<double>(t);
+        }
+        long long xs = 0;
+        if (a.zero_x != nullptr)
+            for (int s = 0; s < a.splits; ++s) xs += a.scratch[a.splits * total + static_cast<long long>(s) * a.R + r];
+        a.y[output_offset(r, o, a)] = finalize_output(sum, xs, o, a);
+    }
+}
+
+// K == 0: exact zeros through the same epilogue (approxtorch/backend/csrc/claude/gemm.cu:30-32)
+__global__ void lut_gemm_empty_k_kernel(const GemmArgs a)
+{
+    const long long total = a.R * a.O;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long r = i / a.O;
+        const int o = static_cast<int>(i - r * a.O);
+        a.y[output_offset(r, o, a)] = finalize_output(0.0, 0, o, a);
+    }
+}
+
+static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_plan* p,
+                     int* tiles_per_batch, long long* row_tiles)
+{
+    ATB_REQUIRE(p != nullptr, "plan is null");
+    ATB_REQUIRE(R >= 0 && K >= 0 && O >= 0 && wb_rows >= 0, "negative dimension");
+    const int sms = sm_count();
+    const long long span = wb_rows > 0 ? wb_rows : R;
+    int bm = 0, splits = 0;
+    if (cfg >= 0) { bm = cfg & 0xffff; splits = (cfg >> 16) & 0xff; }
+    if (bm != 0) {
+        ATB_REQUIRE(bm % 32 == 0 && bm >= 32 && bm <= kMaxBlockRows, "cfg: block rows must be a multiple of 32 in [32, 512]");
+    } else {
+        long long want = ((span + 31) / 32) * 32;
+        if (want > kMaxBlockRows) want = kMaxBlockRows;
+        if (want < 32) want = 32;
+        bm = static_cast<int>(want);
+    }
+    const int tpb = wb_rows > 0 ? ceil_div(wb_rows, bm) : 0;
+    const long long rt = wb_rows > 0 ? (R / (wb_rows > 0 ? wb_rows : 1)) * tpb : (R + bm - 1) / bm;
+    const long long tiles = rt * ceil_div(O > 0 ? O : 1, kStagedCols);
+    const int nchunks = K > 0 ? ceil_div(K, kChunk) : 1;
+    if (splits == 0) {
+        splits = 1;
+        if (tiles > 0 && tiles < sms && nchunks > 1) {
+            long long s = (sms + tiles - 1) / tiles;
+            if (s > 32) s = 32;
+            if (s > nchunks) s = nchunks;
+            splits = static_cast<int>(s);
+        }
+    }
+    if (splits > nchunks) splits = nchunks;
+    const int cps = ceil_div(nchunks, splits);
+    splits = ceil_div(nchunks, cps);
+    p->block_rows = bm;
+    p->splits = splits;
+    p->scratch_bytes = splits > 1 ? static_cast<size_t>(splits) * static_cast<size_t>(R) * (static_cast<size_t>(O) + 1) * 4u : 0u;
+    if (tiles_per_batch) *tiles_per_batch = tpb;
+    if (row_tiles) *row_tiles = rt;
+    return ATB_OK;
+}
+
+static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes, cudaStream_t stream)
+{
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(lut_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+        if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
+        attr_set = true;
+    }
+    if (a.R == 0 || a.O == 0) return ATB_OK;
+    ATB_REQUIRE(a.K <= 32768, "K above 32768 is not supported (int32 accumulators)");
+    ATB_REQUIRE(a.wb_rows == 0 || a.R % a.wb_rows == 0, "rows must be a multiple of wb_rows");
+    if (a.K == 0) {
+        lut_gemm_empty_k_kernel<<<grid_for(a.R * a.O, 256, 4096), 256, 0, stream>>>(a);
+        return check_launch("lut_gemm_empty_k_kernel");
+    }
+    atb_gemm_plan plan;
+    int tpb = 0;
+    long long row_tiles = 0;
+    int rc = make_plan(a.R, a.K, a.O, a.wb_rows, cfg, &plan, &tpb, &row_tiles);
+    if (rc != ATB_OK) return rc;
+    ATB_REQUIRE(row_tiles <= 2147483647LL, "too many row tiles");
+    const int col_tiles = ceil_div(a.O, kStagedCols);
+    ATB_REQUIRE(col_tiles <= 65535, "too many output channels");
+    if (plan.splits > 1) {
+        if (scratch == nullptr || scratch_bytes < plan.scratch_bytes) {
+            set_error("split-K needs %zu bytes of scratch, got %zu", plan.scratch_bytes, scratch_bytes);
+            return ATB_ERR_SCRATCH;
+        }
+    }
+    a.scratch = static_cast<int*>(scratch);
+    a.tiles_per_batch = tpb;
+    a.splits = plan.splits;
+    a.chunks_per_split = ceil_div(ceil_div(a.K, kChunk), plan.splits);
+    dim3 grid(static_cast<unsigned>(row_tiles), static_cast<unsigned>(col_tiles), static_cast<unsigned>(plan.splits));
+    lut_gemm_kernel<<<grid, plan.block_rows, kSmemTotal, stream>>>(a);
+    rc = check_launch("lut_gemm_kernel");
+    if (rc != ATB_OK) return rc;
+    if (plan.splits > 1) {
+        lut_gemm_reduce_kernel<<<grid_for(a.R * a.O, 256, 8 * sm_count()), 256, 0, stream>>>(a);
+        rc = check_launch("lut_gemm_reduce_kernel");
+    }
+    return rc;
+}
+
+}  // namespace atb
+
+using namespace atb;
+
+extern "C" int atb_lut_gemm_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_plan* plan)
+{
+    return make_plan(R, K, O, wb_rows, cfg, plan, nullptr, nullptr);
+}
+
+static int check_epilogue(const float* zero_x, const float* zero_w, const int* wsum)
+{
+    if (zero_x != nullptr) ATB_REQUIRE(zero_w != nullptr && wsum != nullptr, "zero_x needs zero_w and wsum");
+    return ATB_OK;
+}
+
+extern "C" int atb_lut_bgemm_fwd(const uint8_t* x, const uint8_t* w, const void* lut_image, float* y,
+                                 int N, int K, int L, int O, int wb_rows, long long w_batch_stride,
+                                 const float* alpha, const float* beta, const float* zero_x,
+                                 const float* zero_w, const int* wsum,
+                                 int cfg, void* scratch, size_t scratch_bytes, void* stream)
+{
+    ATB_REQUIRE(N >= 0 && K >= 0 && L >= 0 && O >= 0, "negative dimension");
+    ATB_REQUIRE(lut_image != nullptr, "lut_image is null");
+    if (static_cast<long long>(N) * L == 0 || O == 0) return ATB_OK;
+    ATB_REQUIRE(y != nullptr && (K == 0 || (x != nullptr && w != nullptr)), "null operand");
+    int rc = check_epilogue(zero_x, zero_w, wsum);
+    if (rc != ATB_OK) return rc;
+    GemmArgs a{};
+    a.x = x; a.w = w; a.img = static_cast<const LutImage*>(lut_image); a.y = y;
+    a.R = static_cast<long long>(N) * L; a.K = K; a.L = L; a.O = O;
+    a.wb_rows = wb_rows; a.w_batch_stride = w_batch_stride;
+    a.image_mode = 0; a.x_xor = 0; a.pad_index = 0;
+    a.alpha = alpha; a.beta = beta; a.zero_x = zero_x; a.zero_w = zero_w; a.wsum = wsum;
+    return launch_gemm(a, cfg, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int atb_lut_conv2d_fwd(const void* x, int dtype, const uint8_t* w, const void* lut_image, float* y,
+                                  int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw,
+                                  int ph, int pw, int dh, int dw, int pad_index,
+                                  const float* alpha, const float* beta, const float* zero_x,
+                                  const float* zero_w, const int* wsum,
+                                  int cfg, void* scratch, size_t scratch_bytes, void* stream)
+{
+    ATB_REQUIRE(N >= 0 && C >= 0 && H >= 0 && W >= 0 && O >= 0, "negative dimension");
+    ATB_REQUIRE(dtype == ATB_I8 || dtype == ATB_U8, "image must be int8 values or uint8 indices");
+    ATB_REQUIRE(pad_index >= -1 && pad_index <= 255, "pad_index out of range");
+    ATB_REQUIRE(pad_index >= 0 || zero_x != nullptr, "pad_index -1 takes the pad value from zero_x, which is null");
+    ATB_REQUIRE(lut_image != nullptr, "lut_image is null");
+    int OH = 0, OW = 0;
+    ATB_REQUIRE(conv_out_shape(H, W, kh, kw, sh, sw, ph, pw, dh, dw, &OH, &OW), "conv geometry yields empty output");
+    if (N == 0 || O == 0) return ATB_OK;
+    const long long K = static_cast<long long>(C) * kh * kw;
+    ATB_REQUIRE(K <= 32768, "C*kh*kw above 32768 is not supported");
+    ATB_REQUIRE(y != nullptr && (K == 0 || (x != nullptr && w != nullptr)), "null operand");
+    int rc = check_epilogue(zero_x, zero_w, wsum);
+    if (rc != ATB_OK) return rc;
+    GemmArgs a{};
+    a.x = static_cast<const uint8_t*>(x); a.w = w; a.img = static_cast<const LutImage*>(lut_image); a.y = y;
+    a.L = OH * OW; a.R = static_cast<long long>(N) * a.L; a.K = static_cast<int>(K); a.O = O;
+    a.wb_rows = 0; a.w_batch_stride = 0;
+    a.image_mode = 1; a.x_xor = (dtype == ATB_I8) ? 0x80 : 0; a.pad_index = pad_index;
+    a.g = ConvGeom{C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, OH, OW};
+    a.alpha = alpha; a.beta = beta; a.zero_x = zero_x; a.zero_w = zero_w; a.wsum = wsum;
+    return launch_gemm(a, cfg, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+}

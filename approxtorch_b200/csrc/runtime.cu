@@ -1,0 +1,69 @@
+// Library-wide runtime helpers: per-thread error text, device properties, LUT image preparation.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+namespace atb {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+}
+
+int sm_count()
+{
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+// One thread per table entry.  Writes all four images and raises the two "not exact" flags
+// (the flags were zeroed by the memset that precedes the launch).  Eligibility rules:
+// approxtorch/backend/csrc/claude/bgemm_lut_kernels.cuh:116-142.
+__global__ void lut_prepare_kernel(const float* __restrict__ lut, LutImage* __restrict__ img)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;   // i = x * 256 + w
+    const float v = lut[i];
+    const float r = rintf(v);
+    const bool is_int = (v == r);
+    const bool i16_ok = is_int && (fabsf(v) <= 32767.0f);
+    const bool u16_ok = is_int && (v >= 0.0f) && (v <= 65535.0f);
+    if (!i16_ok) img->flags[0] = 1;
+    if (!u16_ok) img->flags[1] = 1;
+    const int16_t v16 = (i16_ok || u16_ok)
+        ? static_cast<int16_t>(static_cast<uint16_t>(static_cast<int>(r))) : static_cast<int16_t>(0);
+    const int t = ((i & 255) << 8) | (i >> 8);
+    img->tab16[i] = v16;
+    img->tab32[i] = v;
+    img->tabT16[t] = v16;
+    img->tabT32[t] = v;
+}
+
+}  // namespace atb
+
+using namespace atb;
+
+extern "C" const char* atb_last_error(void) { return g_error; }
+extern "C" int atb_version(void) { return 100; }
+extern "C" size_t atb_lut_image_bytes(void) { return sizeof(LutImage); }
+
+extern "C" int atb_lut_prepare(const float* lut, void* image, void* stream)
+{
+    ATB_REQUIRE(lut != nullptr && image != nullptr, "null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemsetAsync(image, 0, sizeof(int) * 4, s);
+    if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
+    lut_prepare_kernel<<<256, 256, 0, s>>>(lut, static_cast<LutImage*>(image));
+    return check_launch("lut_prepare_kernel");
+}

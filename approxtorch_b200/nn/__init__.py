@@ -1,0 +1,7 @@
+"""Approximate convolution layers and their autograd Functions (same exports as approxtorch/nn/__init__.py:4-9,
+minus the naive comparison operators)."""
+from .Conv2d_int8 import Conv2d_int8
+from .Conv2d_uint8 import Conv2d_uint8
+from . import bgemm_int8
+from . import bgemm_uint8
+from . import quantization

@@ -1,0 +1,172 @@
+/* C ABI of libapproxtorch_b200.so — the drop-in boundary of the approximate-multiplier hot path.
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer unless a comment says
+ * "host"; `stream` is a cudaStream_t passed as void*.  Every entry point enqueues work on
+ * `stream` and returns without synchronising.  Return value: 0 = success, otherwise one of
+ * the ATB_ERR_* codes; atb_last_error() gives the message of the calling thread's last
+ * failure.  No entry point allocates device memory unless its comment says so: outputs and
+ * scratch buffers are supplied by the caller (the Python binding uses torch tensors).
+ *
+ * Each declaration names the reference interface it replaces; paths are relative to the
+ * reference project root.
+ *
+ * Shape letters: N batch, K = C*kh*kw reduction, L = OH*OW output pixels, O output channels,
+ * R = N*L pixel rows.  LUT index rule: table row = activation index, column = weight index,
+ * flat = idx(x)*256 + idx(w); idx_int8(v) = v+128, idx_uint8(v) = v.
+ */
+#ifndef APPROXTORCH_B200_H
+#define APPROXTORCH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ATB_OK 0
+#define ATB_ERR_INVALID 1   /* bad argument (shape, null pointer, unsupported size) */
+#define ATB_ERR_CUDA 2      /* a CUDA runtime call or launch failed */
+#define ATB_ERR_SCRATCH 3   /* caller-supplied scratch buffer too small */
+
+/* element types accepted where an operand may be fp32 integer values, int8 values or uint8 LUT indices
+ * (approxtorch/backend/csrc/claude/bgemm_lre_backward_claude.cu:69-80, 353-355) */
+#define ATB_F32 0
+#define ATB_I8 1
+#define ATB_U8 2
+
+const char* atb_last_error(void);
+int atb_version(void);
+
+/* ---- LUT image --------------------------------------------------------------------------
+ * Device-side image of a 256x256 fp32 table: 16-bit and fp32 copies, natural and transposed,
+ * plus two validity flags the kernels branch on (int16-exact, uint16-exact).  Replaces
+ * prepare_lut_kernel and the per-call allocations around it
+ * (approxtorch/backend/csrc/claude/bgemm_lut_kernels.cuh:116-142,
+ *  approxtorch/backend/csrc/claude/bgemm_float_claude.cu:163-192); built once per table, not per call. */
+size_t atb_lut_image_bytes(void);
+int atb_lut_prepare(const float* lut /*[65536]*/, void* image /*atb_lut_image_bytes()*/, void* stream);
+
+/* ---- operand prepasses ------------------------------------------------------------------ */
+/* fp32 integer-valued operand -> uint8 LUT index, clamp(rn(v)+offset, 0, 255)
+ * (quantize_to_u8_kernel, approxtorch/backend/csrc/claude/bgemm_lut_kernels.cuh:62-97). */
+int atb_quantize_u8(const float* in, uint8_t* out, long long numel, int offset, void* stream);
+/* B[K,N] with arbitrary element strides (fp32 values or uint8 indices) -> uint8 [N,K]
+ * (quantize_transpose_u8_kernel, approxtorch/backend/csrc/claude/gemm.cu:68-95). */
+int atb_quantize_transpose_u8(const void* b, int dtype, int K, int N, long long stride_k,
+                              long long stride_n, int offset, uint8_t* out, void* stream);
+/* quantised image [N,C,H,W] (fp32 / int8 / uint8) -> uint8 LUT-index columns [N, C*kh*kw, OH*OW];
+ * taps outside the image get `pad_index` (128 = quantised zero of the signed path)
+ * (im2col_u8, approxtorch/backend/csrc/claude/bgemm_lre_backward_claude.cu:216-269, 737-791). */
+int atb_im2col_u8(const void* x, int dtype, int N, int C, int H, int W, int kh, int kw, int sh, int sw,
+                  int ph, int pw, int dh, int dw, int pad_index, uint8_t* out, void* stream);
+
+/* ---- LUT GEMM / conv forward --------------------------------------------------------------
+ * y[n,o,l] = alpha[o] * t + beta[o],
+ * t = sum_k lut[x_idx][w_idx] - zw[o]*xsum[n,l] - zx*wsum[o] + K*zx*zw[o]
+ * alpha/beta are optional (NULL = 1 / 0).  The zero-point terms are formed only when zero_x != NULL:
+ * zx = *zero_x and zw = zero_w[o] are integer-valued fp32, wsum[o] = sum_k w_idx[o,k] (int32),
+ * xsum = sum_k x_idx of the row; they are combined in integer arithmetic before the single
+ * conversion to fp32.  Integer tables accumulate in int32 (exact), other tables in fp32 in ascending k.
+ *
+ * The plan says how the launch will be tiled and how much scratch (bytes) a split-K launch needs. */
+typedef struct {
+    int block_rows;      /* pixel rows per thread block (a multiple of 32, 64..512) */
+    int splits;          /* split-K factor; > 1 needs scratch */
+    size_t scratch_bytes;
+} atb_gemm_plan;
+
+int atb_lut_gemm_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_plan* plan /*host*/);
+
+/* Batched LUT GEMM on uint8 index operands.  x is [N,K,L] (l fastest; L == 1 gives the torch.mm
+ * layout A[M,K]); w is [O,K] shared by all rows (wb_rows == 0) or one [O,K] matrix per `wb_rows`
+ * consecutive pixel rows, `w_batch_stride` bytes apart.  Replaces bgemm_forward_save_cfg_impl and
+ * gemm_forward_save_cfg_impl (approxtorch/backend/csrc/claude/bgemm_float_claude.cu:70-205,
+ * approxtorch/backend/csrc/claude/gemm.cu:97-232) and the dequantisation of
+ * approxtorch/nn/Conv2d_int8.py:213-218 when alpha/beta are given. */
+int atb_lut_bgemm_fwd(const uint8_t* x, const uint8_t* w, const void* lut_image, float* y,
+                      int N, int K, int L, int O, int wb_rows, long long w_batch_stride,
+                      const float* alpha, const float* beta, const float* zero_x, const float* zero_w, const int* wsum,
+                      int cfg, void* scratch, size_t scratch_bytes, void* stream);
+
+/* im2col-free approximate Conv2d forward on the quantised image (int8 values or uint8 indices):
+ * the column matrix is never materialised; taps outside the image look up `pad_index`
+ * (pad_index == -1: the rounded value of *zero_x, read on the device, so no host copy is needed).
+ * Replaces im2col_u8 + bgemm_fake_int8_claude_save + dequant
+ * (approxtorch/nn/bgemm_int8.py:244-256, approxtorch/nn/Conv2d_int8.py:207-218) and, with zw/cterm,
+ * the zero-point correction of approxtorch/nn/Conv2d_uint8.py:283-323 when zero_x is given. */
+int atb_lut_conv2d_fwd(const void* x, int dtype, const uint8_t* w /*[O, C*kh*kw]*/, const void* lut_image,
+                       float* y /*[N,O,OH,OW]*/, int N, int C, int H, int W, int O, int kh, int kw,
+                       int sh, int sw, int ph, int pw, int dh, int dw, int pad_index,
+                       const float* alpha, const float* beta, const float* zero_x, const float* zero_w, const int* wsum,
+                       int cfg, void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- fake quantisation -------------------------------------------------------------------- */
+/* result[0] = max|x| (result[1] = min x, result[2] = max x when want_minmax).  `result` must hold 3 floats;
+ * it is initialised by the call.  Replaces x.abs().max() / amin / amax of
+ * approxtorch/nn/Conv2d_int8.py:139 and approxtorch/nn/Conv2d_uint8.py:229-230. */
+int atb_absmax(const float* x, long long numel, int want_minmax, float* result, void* stream);
+/* (q fp32, mask bool) = fake-quant of x with a 1-element device scale (zero_point NULL = symmetric)
+ * (approxtorch/backend/csrc/claude/quantization.cu:54-110, 149-183). */
+int atb_fakequant_fwd(const float* x, const float* scale, const float* zero_point, int qmin, int qmax,
+                      float* q, uint8_t* mask, long long numel, void* stream);
+/* gx = (mask ? go : 0) / max(scale, 1e-12) (approxtorch/backend/csrc/claude/quantization.cu:113-143). */
+int atb_fakequant_bwd(const float* go, const uint8_t* mask, const float* scale, float* gx,
+                      long long numel, void* stream);
+/* Fused form used by the layers: same arithmetic, but writes the 1-byte quantised image (int8 value,
+ * or uint8 index when zero_point != NULL) and the mask instead of an fp32 tensor; `mask` may be NULL. */
+int atb_quantize_image(const float* x, const float* scale, const float* zero_point, int qmin, int qmax,
+                       void* q8, uint8_t* mask, long long numel, void* stream);
+/* per-output-channel weight fake-quant: w [O, inner] fp32, scale[O] (zero_point[O] or NULL) ->
+ * uint8 LUT index (value + index_offset), mask, optional fp32 q and optional per-channel index sum
+ * (approxtorch/nn/quantization.py:98-133). */
+int atb_quantize_weight(const float* w, const float* scale, const float* zero_point, int qmin, int qmax,
+                        int index_offset, int O, int inner, uint8_t* widx, uint8_t* mask, float* q,
+                        int* wsum, void* stream);
+
+/* ---- 256-entry table maps ------------------------------------------------------------------- */
+/* out[i] = table[idx(x[i])] (lut_map, approxtorch/backend/csrc/claude/bgemm_lre_backward_claude.cu:96-130, 793-807). */
+int atb_lut_map(const void* x, int dtype, const float* table, float* out, long long numel, void* stream);
+/* mapped image with constant border table[128]
+ * (lut_map_pad, approxtorch/backend/csrc/claude/bgemm_lre_backward_claude.cu:277-311, 809-850). */
+int atb_lut_map_pad(const void* x, int dtype, const float* table, float* out, int N, int C, int H, int W,
+                    int ph, int pw, void* stream);
+
+/* ---- backward: STE / LRE (256-entry slope tables) ------------------------------------------------
+ * Column-space (unfolded) operands, the contract of bgemm_lre_backward_claude
+ * (approxtorch/backend/csrc/claude/bgemm_lre_backward_claude.cu:539-647):
+ *   grad_x[n,k,l] = sum_o go[n,o,l] * dx[idx(w[o,k])]      grad_w[o,k] = sum_{n,l} go[n,o,l] * dw[idx(x[n,k,l])]
+ * w is given as [O,K] (w_ok_layout = 1) or [K,O] (0); grad_w is written in the same layout.
+ * STE is the same call with the decode table dx = dw = arange(256) - 128. */
+int atb_lre_bwd(const float* go, const void* x, int x_dtype, const void* w, int w_dtype, int w_ok_layout,
+                const float* dx, const float* dw, float* grad_x, float* grad_w,
+                int N, int K, int L, int O, void* stream);
+/* Image-space form used by the conv Functions: x is the quantised image [N,C,H,W]; grad_x is the
+ * gradient w.r.t. that image (the fold is fused), grad_w is [O, C*kh*kw]; taps outside the image
+ * contribute dw[pad_index] to grad_w.  `go_scale` (optional, [O]) multiplies go per output channel.
+ * Replaces the cuDNN convolution_backward calls of approxtorch/nn/bgemm_int8.py:165-212, 259-295. */
+int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t* widx /*[O,K]*/,
+                     const float* dx, const float* dw, const float* go_scale,
+                     float* grad_x /*[N,C,H,W]*/, float* grad_w /*[O,K]*/,
+                     int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
+                     int dh, int dw_, int pad_index, void* stream);
+
+/* ---- backward: custom pair tables (256x256) --------------------------------------------------------
+ * grad_x[n,k,l] = sum_o dY[n,o,l] * dx_lut[x][w[o,k]]   (approxtorch/backend/csrc/cuda/bgemm_custom_grad_optimize.cu:30-116, 212-257)
+ * grad_w[o,k]   = sum_{n,l} dY[n,o,l] * dw_lut[x][w]    (same file :136-205, 259-301)
+ * x, w are uint8 LUT indices. */
+int atb_custom_bwd_dx(const uint8_t* x, const uint8_t* w, const float* dy, const float* dx_lut,
+                      float* grad_x, int N, int K, int L, int O, void* stream);
+int atb_custom_bwd_dw(const uint8_t* x, const uint8_t* w, const float* dy, const float* dw_lut,
+                      float* grad_w, int N, int K, int L, int O, void* stream);
+
+/* ---- depthwise LUT conv forward (groups == C, channel multiplier 1) ------------------------------
+ * (dwconv_fake_int8_claude, approxtorch/backend/csrc/claude/dwconv_claude.cu:78-266). */
+int atb_lut_dwconv_fwd(const void* x, int dtype, const uint8_t* widx /*[C, kh*kw]*/, const void* lut_image,
+                       float* y, int N, int C, int H, int W, int kh, int kw, int sh, int sw, int ph, int pw,
+                       int dh, int dw, int pad_index, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* APPROXTORCH_B200_H */

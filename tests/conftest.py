@@ -22,3 +22,19 @@ def load_golden(name):
 @pytest.fixture(scope="session")
 def golden():
     return load_golden
+
+
+def pytest_sessionstart(session):
+    """Make sure the in-tree CUDA library and the C oracle exist (both build without a GPU)."""
+    from approxtorch_b200.build import build_library
+    build_library()
+    from oracle import c_oracle
+    c_oracle.build()
+
+
+@pytest.fixture(scope="session")
+def dev():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda:0")

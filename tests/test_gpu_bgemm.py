@@ -1,0 +1,207 @@
+"""GPU parity of the LUT-BGEMM / GEMM forward operators (through the C ABI) against the CPU oracle and
+the fixtures recorded from the reference's CPU operator.  Integer tables: bit-exact."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import c_oracle, lut_oracle as lo
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops():
+    from approxtorch_b200.backend import ops
+    return ops
+
+
+def _t(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+@pytest.mark.parametrize("name", ["affine", "noisy", "trunc4", "utrunc6"])
+def test_matches_reference_cpu_operator_fixture(golden, dev, name):
+    ops = _ops()
+    g = golden("bgemm_ref_cpu")
+    lut = _t(g[f"lut_{name}"], dev)
+    for si in range(4):
+        x, w, y = g[f"{name}_{si}_x"], g[f"{name}_{si}_w"], g[f"{name}_{si}_y"]
+        # uint8 operator on raw indices (fp32 weights, uint8-dtype x = indices)
+        out = ops.bgemm_fake_uint8_claude(_t(x, dev), _t(w.astype(np.float32), dev), lut)
+        np.testing.assert_array_equal(out.cpu().numpy(), y.astype(np.float32))
+        # fp32 x takes the rounding prepass and must agree bit for bit
+        out2 = ops.bgemm_fake_uint8_claude(_t(x.astype(np.float32), dev), _t(w.astype(np.float32), dev), lut)
+        assert torch.equal(out, out2)
+        # int8 operator on shifted values: uint8_op(x, w) == int8_op(x - 128, w - 128)
+        out3 = ops.bgemm_fake_int8_claude(_t(x.astype(np.float32) - 128, dev), _t(w.astype(np.float32) - 128, dev), lut)
+        assert torch.equal(out, out3)
+
+
+# (N, K, L, O): tails in every dimension, K below/above one operand chunk, L == 1, tiny and wide O
+SHAPES = [(1, 1, 1, 1), (2, 17, 33, 5), (3, 64, 100, 64), (1, 130, 513, 65), (4, 48, 1, 200),
+          (2, 576, 96, 64), (1, 31, 700, 129), (5, 16, 7, 3), (64, 512, 1, 100)]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_shape_sweep_against_oracle(dev, shape):
+    ops = _ops()
+    N, K, L, O = shape
+    rng = np.random.default_rng(hash(shape) & 0xffff)
+    x = rng.integers(0, 256, (N, K, L), dtype=np.uint8)
+    w = rng.integers(-128, 128, (O, K)).astype(np.float32)
+    lut = lo.lut_signed_noisy(64, seed=2)
+    ref = c_oracle.bgemm_u8(x, lo.to_lut_index(w, 128), lut)
+    y, xq, wq = ops.bgemm_fake_int8_claude_save(_t(x, dev), _t(w, dev), _t(lut.reshape(-1), dev))
+    np.testing.assert_array_equal(y.cpu().numpy().astype(np.float64), ref)
+    assert xq.dtype == torch.uint8 and wq.dtype == torch.uint8 and tuple(wq.shape) == (O, K)
+    np.testing.assert_array_equal(wq.cpu().numpy(), lo.to_lut_index(w, 128))
+
+
+@pytest.mark.parametrize("cfg", [-1, 0, 7, 100, 32, 64, 128, 256, 480, 512, (3 << 16) | 128, (2 << 16) | 512,
+                                 (5 << 16)])
+def test_forced_tilings_and_split_k_are_bit_identical(dev, cfg):
+    ops = _ops()
+    rng = np.random.default_rng(5)
+    N, K, L, O = 2, 200, 300, 70
+    x = rng.integers(0, 256, (N, K, L), dtype=np.uint8)
+    w = rng.integers(-128, 128, (O, K)).astype(np.float32)
+    lut = lo.lut_affine_asymmetric()
+    ref = c_oracle.bgemm_u8(x, lo.to_lut_index(w, 128), lut)
+    y = torch.ops.approxtorch.bgemm_fake_int8_forward_cuda_claude_cfg(_t(x, dev), _t(w, dev), _t(lut.reshape(-1), dev), cfg)
+    np.testing.assert_array_equal(y.cpu().numpy().astype(np.float64), ref)
+
+
+def test_rounding_prepass_and_save_contract(dev):
+    ops = _ops()
+    rng = np.random.default_rng(9)
+    x = (rng.integers(-300, 300, (2, 23, 40)) * 0.5).astype(np.float32)      # ties and out-of-range values
+    w = (rng.integers(-300, 300, (6, 23)) * 0.5).astype(np.float32)
+    lut = lo.lut_signed_noisy(64, seed=3)
+    y, xq, wq = ops.bgemm_fake_int8_claude_save(_t(x, dev), _t(w, dev), _t(lut.reshape(-1), dev))
+    np.testing.assert_array_equal(xq.cpu().numpy(), lo.to_lut_index(x, 128))
+    np.testing.assert_array_equal(wq.cpu().numpy(), lo.to_lut_index(w, 128))
+    ref = lo.bgemm_exact(lo.to_lut_index(x, 128), lo.to_lut_index(w, 128), lut)
+    np.testing.assert_array_equal(y.cpu().numpy().astype(np.int64), ref)
+    # uint8-dtype x: the returned index image aliases the input
+    xi = _t(lo.to_lut_index(x, 128), dev)
+    y2, xq2, _ = ops.bgemm_fake_int8_claude_save(xi, _t(w, dev), _t(lut.reshape(-1), dev))
+    assert xq2.data_ptr() == xi.data_ptr() and torch.equal(y, y2)
+    # misaligned storage offsets take the scalar paths
+    big = torch.zeros(x.size + 3, dtype=torch.float32, device=dev)
+    big[3:] = _t(x, dev).flatten()
+    y3 = ops.bgemm_fake_int8_claude(big[3:].view(x.shape), _t(w, dev), _t(lut.reshape(-1), dev))
+    assert torch.equal(y, y3)
+
+
+def test_lut_classes(dev):
+    """int16-exact, uint16-exact (incl. 0 / 32768 / 65535), beyond-int16 mixed sign and non-integer
+    tables: 16-bit classes are bit-exact; fp32-class tables follow the ascending-k fp32 sum."""
+    ops = _ops()
+    rng = np.random.default_rng(21)
+    N, K, L, O = 2, 75, 50, 40
+    x = rng.integers(0, 256, (N, K, L), dtype=np.uint8)
+    w = rng.integers(0, 256, (O, K)).astype(np.float32)
+    wi = w.astype(np.uint8)
+    edge16 = rng.integers(-32767, 32768, (256, 256)).astype(np.float32)
+    edge16[0, 0], edge16[1, 1] = 32767, -32767
+    u16 = rng.integers(0, 65536, (256, 256)).astype(np.float32)
+    u16[0, 0], u16[0, 1], u16[0, 2] = 0, 65535, 32768
+    for tab in (edge16, u16, lo.lut_exact_unsigned()):
+        assert lo.lut_class(tab) in ("i16", "u16")
+        y = ops.bgemm_fake_uint8_claude(_t(x, dev), _t(w, dev), _t(tab.reshape(-1), dev))
+        np.testing.assert_array_equal(y.cpu().numpy().astype(np.float64), c_oracle.bgemm_u8(x, wi, tab))
+    mixed = edge16.copy(); mixed[5, 5] = 40000.0; mixed[6, 6] = -40000.0
+    half = (rng.integers(-2000, 2000, (256, 256)) * 0.5).astype(np.float32)
+    for tab in (mixed, half):
+        assert lo.lut_class(tab) == "f32"
+        y = ops.bgemm_fake_uint8_claude(_t(x, dev), _t(w, dev), _t(tab.reshape(-1), dev))
+        np.testing.assert_array_equal(y.cpu().numpy(), lo.bgemm_f32_ascending(x, wi, tab))
+    # exact product table == integer einsum
+    y = ops.bgemm_fake_uint8_claude(_t(x, dev), _t(w, dev), _t(lo.lut_exact_unsigned().reshape(-1), dev))
+    ref = np.einsum("nkl,ok->nol", x.astype(np.int64), wi.astype(np.int64))
+    np.testing.assert_array_equal(y.cpu().numpy().astype(np.int64), ref)
+
+
+def test_lut_image_cache_follows_in_place_updates(dev):
+    ops = _ops()
+    rng = np.random.default_rng(2)
+    x = rng.integers(0, 256, (1, 9, 10), dtype=np.uint8)
+    w = rng.integers(0, 256, (3, 9)).astype(np.float32)
+    lut = _t(lo.lut_exact_unsigned().reshape(-1), dev)
+    y1 = ops.bgemm_fake_uint8_claude(_t(x, dev), _t(w, dev), lut)
+    lut.mul_(2.0)                                   # version bump must invalidate the cached image
+    y2 = ops.bgemm_fake_uint8_claude(_t(x, dev), _t(w, dev), lut)
+    assert torch.equal(y2, 2.0 * y1)
+
+
+def test_gemm_operators(dev):
+    ops = _ops()
+    rng = np.random.default_rng(33)
+    M, K, Nc = 70, 45, 130
+    A = rng.integers(-128, 128, (M, K)).astype(np.float32)
+    B = rng.integers(-128, 128, (K, Nc)).astype(np.float32)
+    lut = lo.lut_affine_asymmetric()
+    ref = lo.gemm_exact(lo.to_lut_index(A, 128), lo.to_lut_index(B, 128), lut)
+    lt = _t(lut.reshape(-1), dev)
+    y, aq, bq = ops.gemm_fake_int8_claude_save(_t(A, dev), _t(B, dev), lt)
+    np.testing.assert_array_equal(y.cpu().numpy().astype(np.int64), ref)
+    assert tuple(aq.shape) == (M, K) and tuple(bq.shape) == (Nc, K)      # bq is transposed
+    np.testing.assert_array_equal(bq.cpu().numpy(), lo.to_lut_index(B, 128).T)
+    # transposed-view B costs nothing extra and gives the same numbers
+    Wt = _t(np.ascontiguousarray(B.T), dev)
+    assert torch.equal(ops.gemm_fake_int8_claude(_t(A, dev), Wt.t(), lt), y)
+    # orientation matters: A and B swapped through an asymmetric table differ
+    yu = ops.gemm_fake_uint8_claude(_t(lo.to_lut_index(A, 128), dev), _t(lo.to_lut_index(B, 128), dev), lt)
+    assert torch.equal(yu, y)
+    # degenerate shapes
+    assert ops.gemm_fake_int8_claude(torch.zeros(0, K, device=dev), _t(B, dev), lt).shape == (0, Nc)
+    assert ops.gemm_fake_int8_claude(_t(A, dev), torch.zeros(K, 0, device=dev), lt).shape == (M, 0)
+    z = ops.gemm_fake_int8_claude(torch.zeros(M, 0, device=dev), torch.zeros(0, Nc, device=dev), lt)
+    assert z.shape == (M, Nc) and not z.any()
+    with pytest.raises(RuntimeError):
+        ops.gemm_fake_int8_claude(_t(A, dev), _t(B[:-1], dev), lt)
+    with pytest.raises(RuntimeError):
+        ops.gemm_fake_int8_claude(_t(A, dev), _t(B, dev), lt[:100])
+    with pytest.raises(RuntimeError):
+        ops.bgemm_fake_int8_claude(_t(A, dev), _t(B, dev), lt)              # wrong rank
+
+
+def test_per_batch_weights_match_oracle(dev):
+    """The benchmark's raw LUT-BGEMM shape family: one weight matrix per batch item, A k-contiguous."""
+    ops = _ops()
+    rng = np.random.default_rng(44)
+    Bt, M, K, Nc = 3, 640, 96, 128
+    A = rng.integers(0, 256, (Bt, M, K), dtype=np.uint8)
+    Bm = rng.integers(0, 256, (Bt, Nc, K), dtype=np.uint8)                   # already [N,K] per batch
+    lut = lo.lut_signed_noisy(64, seed=0)
+    y = torch.empty((Bt, M, Nc), dtype=torch.float32, device=dev)
+    ops.lut_gemm_launch(_t(A, dev), _t(Bm, dev), ops.lut_image(_t(lut.reshape(-1), dev)), y,
+                        Bt * M, K, 1, Nc, wb_rows=M, w_batch_stride=Nc * K)
+    for b in range(Bt):
+        ref = lo.gemm_exact(A[b], Bm[b].T, lut)
+        np.testing.assert_array_equal(y[b].cpu().numpy().astype(np.int64), ref)
+
+
+def test_benchmark_size_rows_against_oracle(dev):
+    """Full benchmark size (16 x [4096 x 576] . [576 x 256]): a random sample of output rows is checked
+    bit-exactly against the C oracle, and the whole output against a column checksum identity:
+    sum over rows of y[:, o] equals sum_k sum_a count_k[a] * lut[a][w[o,k]]."""
+    ops = _ops()
+    rng = np.random.default_rng(0)
+    Bt, M, K, Nc = 16, 4096, 576, 256
+    A = rng.integers(0, 256, (Bt, M, K), dtype=np.uint8)
+    Bm = rng.integers(0, 256, (Bt, Nc, K), dtype=np.uint8)
+    lut = lo.lut_signed_noisy(64, seed=0)
+    y = torch.empty((Bt, M, Nc), dtype=torch.float32, device=dev)
+    ops.lut_gemm_launch(_t(A, dev), _t(Bm, dev), ops.lut_image(_t(lut.reshape(-1), dev)), y,
+                        Bt * M, K, 1, Nc, wb_rows=M, w_batch_stride=Nc * K)
+    yh = y.cpu().numpy().astype(np.int64)
+    rows = rng.integers(0, M, 24)
+    for b in (0, 7, 15):
+        ref = lo.gemm_exact(A[b][rows], Bm[b].T, lut)
+        np.testing.assert_array_equal(yh[b][rows], ref)
+    tab = lut.reshape(256, 256).astype(np.int64)
+    for b in (3, 12):
+        counts = np.stack([np.bincount(A[b][:, k], minlength=256) for k in range(K)])      # [K, 256]
+        expect = np.array([(counts * tab[:, Bm[b][o]].T).sum() for o in range(Nc)])
+        np.testing.assert_array_equal(yh[b].sum(axis=0), expect)

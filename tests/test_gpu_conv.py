@@ -1,0 +1,351 @@
+"""GPU parity of the approximate Conv2d path: im2col-free forward, fused dequantisation, STE / LRE /
+custom backward, the uint8 layer and the depthwise operator, against the oracle and the fixture
+composed from reference pieces.  Integer accumulators bit-exact; fp32 outputs / gradients rel 1e-5."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import lut_oracle as lo
+
+pytestmark = pytest.mark.gpu
+RTOL = 1e-5
+
+
+def _t(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def _close(got, ref, rtol=RTOL):
+    got = got.detach().cpu().numpy().astype(np.float64) if isinstance(got, torch.Tensor) else got
+    scale = max(np.abs(ref).max(), 1e-30)
+    assert np.abs(got - ref).max() <= rtol * scale, (np.abs(got - ref).max(), scale)
+
+
+GEOMS = [  # (B, C, H, W, O, k, s, p, d)
+    (2, 3, 8, 8, 4, 3, 1, 1, 1), (1, 16, 12, 10, 24, 3, 2, 1, 1), (2, 8, 9, 9, 5, 1, 1, 0, 1),
+    (2, 8, 9, 9, 70, 1, 2, 0, 1), (1, 4, 11, 13, 6, (3, 2), (2, 1), (1, 2), (1, 2)), (3, 5, 7, 7, 9, 5, 1, 2, 1),
+    (1, 2, 6, 6, 3, 3, 1, 0, 2), (8, 64, 8, 8, 64, 3, 1, 1, 1),
+]
+
+
+def _pair(v):
+    return (v, v) if isinstance(v, int) else tuple(v)
+
+
+@pytest.mark.parametrize("geom", GEOMS)
+def test_conv_forward_is_bit_exact(dev, geom):
+    from approxtorch_b200.backend import ops
+    B, C, H, W, O, k, s, p, d = geom
+    (kh, kw), (sh, sw), (ph, pw), (dh, dw) = _pair(k), _pair(s), _pair(p), _pair(d)
+    rng = np.random.default_rng(abs(hash(geom)) & 0xffff)
+    x8 = rng.integers(-127, 128, (B, C, H, W)).astype(np.int8)
+    widx = rng.integers(0, 256, (O, C * kh * kw), dtype=np.uint8)
+    lut = lo.lut_signed_noisy(64, seed=5)
+    cols = lo.im2col_index(lo.index_of(x8, True), kh, kw, sh, sw, ph, pw, dh, dw, 128)
+    ref = lo.bgemm_exact(cols, widx, lut)
+    img = ops.lut_image(_t(lut.reshape(-1), dev))
+    g4 = ((kh, kw), (sh, sw), (ph, pw), (dh, dw))
+    y = ops.lut_conv2d_launch(_t(x8, dev), _t(widx, dev), img, g4, 128)
+    np.testing.assert_array_equal(y.flatten(2).cpu().numpy().astype(np.int64), ref)
+    # uint8 index image input and a forced split-K give the same integers
+    y2 = ops.lut_conv2d_launch(_t(lo.index_of(x8, True), dev), _t(widx, dev), img, g4, 128, cfg=(3 << 16) | 64)
+    assert torch.equal(y, y2)
+    # identical to the materialised route im2col_u8 -> LUT-BGEMM
+    cols_gpu = ops.im2col_u8(_t(x8, dev), (kh, kw), (sh, sw), (ph, pw), (dh, dw))
+    y3 = torch.empty_like(y.flatten(2))
+    ops.lut_gemm_launch(cols_gpu, _t(widx, dev), img, y3, B, C * kh * kw, cols.shape[2], O)
+    assert torch.equal(y.flatten(2), y3)
+
+
+def test_layer_matches_fixture_composed_from_reference_pieces(golden, dev):
+    import approxtorch_b200 as at
+    g = golden("conv_layer")
+    x = _t(g["x"], dev)
+    lut = _t(g["lut"], dev)
+    for bits in (8, 4):
+        for s, p in ((1, 1), (2, 0)):
+            layer = at.nn.Conv2d_int8(16, 24, 3, lut, bias=True, stride=s, padding=p, weight_bits=bits,
+                                      update_scale=False).to(dev)
+            with torch.no_grad():
+                layer.weight.copy_(_t(g["w"], dev))
+                layer.bias.copy_(_t(g["bias"], dev))
+                layer.scale_x.copy_(_t(g["scale_x"], dev))
+            layer._reset_scale_w_from_weight()
+            np.testing.assert_array_equal(layer.scale_w.cpu().numpy(), g[f"b{bits}_scale_w"])
+            y = layer(x)
+            ref = g[f"b{bits}_s{s}p{p}_y"]
+            np.testing.assert_allclose(y.detach().cpu().numpy(), ref, rtol=1e-6, atol=1e-6 * np.abs(ref).max())
+            # integer accumulator: undo the dequantisation through the raw operator chain
+            xq = at.nn.quantization.static_quantize_int8(x, layer.scale_x, -127, 127)
+            qm = 2 ** (bits - 1) - 1
+            wq = at.nn.quantization.static_quantize_int8(layer.weight, layer.scale_w, -qm, qm, ch_axis=0)
+            yint = at.nn.bgemm_int8.conv2d_int8_ste(xq, wq.view(24, -1), lut, ((3, 3), (s, s), (p, p), (1, 1), 1))
+            np.testing.assert_array_equal(yint.detach().cpu().numpy().astype(np.int32), g[f"b{bits}_s{s}p{p}_yint"])
+
+
+def _fp64_layer_truth(x, w, bias, lut, scale_x, scale_w, qmax_w, geom, go, mode, dx=None, dw=None):
+    """float64 forward / backward of the whole signed layer from the oracle pieces."""
+    (kh, kw), (sh, sw), (ph, pw), (dh, dw_) = geom
+    B, C, H, W = x.shape
+    O = w.shape[0]
+    xq, xm = lo.fakequant_sym(x, scale_x, -127, 127)
+    wq, wm = lo.fakequant_sym(w, scale_w.reshape(-1, 1, 1, 1), -qmax_w, qmax_w)
+    cols = lo.im2col_index(lo.to_lut_index(xq, 128), kh, kw, sh, sw, ph, pw, dh, dw_, 128)
+    widx = lo.to_lut_index(wq.reshape(O, -1), 128)
+    yint = lo.bgemm_exact(cols, widx, lut).astype(np.float64)
+    s = (np.float32(scale_x) * scale_w).astype(np.float64)
+    y = yint * s[None, :, None] + (0 if bias is None else bias.astype(np.float64)[None, :, None])
+    g = go.reshape(B, O, -1).astype(np.float64) * s[None, :, None]
+    if mode == "ste":
+        gcols, gw = lo.ste_backward(g, cols, widx)
+    elif mode == "lre":
+        gcols, gw = lo.lre_backward(g, cols, widx, dx, dw)
+    else:
+        gcols, gw = lo.custom_backward(g, cols, widx, dx, dw)
+    gx = lo.fold(gcols, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw_)
+    sx = max(np.float64(np.float32(scale_x)), 1e-12)
+    gx = gx * xm / sx
+    gw = gw.reshape(w.shape) * wm / np.maximum(scale_w.astype(np.float64), 1e-12).reshape(-1, 1, 1, 1)
+    gb = go.astype(np.float64).sum(axis=(0, 2, 3))
+    return y, gx, gw, gb
+
+
+@pytest.mark.parametrize("mode", ["ste", "lre", "custom"])
+@pytest.mark.parametrize("geom", [(2, 6, 9, 9, 10, 3, 1, 1, 1), (2, 4, 10, 8, 7, 3, 2, 1, 1), (3, 8, 6, 6, 12, 1, 1, 0, 1),
+                                  (1, 3, 9, 11, 5, (3, 2), (2, 1), (1, 2), (1, 2))])
+def test_layer_forward_backward_against_fp64_truth(dev, mode, geom):
+    import approxtorch_b200 as at
+    B, C, H, W, O, k, s, p, d = geom
+    g4 = (_pair(k), _pair(s), _pair(p), _pair(d))
+    rng = np.random.default_rng(7)
+    torch.manual_seed(3)
+    lut = lo.lut_signed_noisy(128, seed=4)
+    if mode == "lre":
+        dx, dw = lo.lre_slopes(lut)
+        dw = dw.copy(); dw[128] = 3.25            # a non-zero slope at quantised zero exercises the padding rule
+    elif mode == "custom":
+        dx = (rng.standard_normal((256, 256)) * 10).astype(np.float32).reshape(-1)
+        dw = (rng.standard_normal((256, 256)) * 10).astype(np.float32).reshape(-1)
+    else:
+        dx = dw = None
+    for bits in (8, 4):
+        layer = at.nn.Conv2d_int8(C, O, _pair(k), _t(lut.reshape(-1), dev), grad=mode,
+                                  dx=None if dx is None else _t(dx, dev), dw=None if dw is None else _t(dw, dev),
+                                  bias=True, stride=_pair(s), padding=_pair(p), dilation=_pair(d),
+                                  weight_bits=bits, update_scale=False).to(dev)
+        x = (rng.standard_normal((B, C, H, W)) * 1.5).astype(np.float32)
+        with torch.no_grad():
+            layer.scale_x.fill_(0.02)              # clips part of the activations: masks matter
+        xt = _t(x, dev).requires_grad_(True)
+        y = layer(xt)
+        go = rng.standard_normal(tuple(y.shape)).astype(np.float32)
+        y.backward(_t(go, dev))
+        ry, rgx, rgw, rgb = _fp64_layer_truth(
+            x, layer.weight.detach().cpu().numpy(), layer.bias.detach().cpu().numpy(), lut,
+            np.float32(0.02), layer.scale_w.cpu().numpy(), 2 ** (bits - 1) - 1, g4, go, mode, dx, dw)
+        _close(y.flatten(2), ry)
+        _close(xt.grad, rgx)
+        _close(layer.weight.grad, rgw)
+        _close(layer.bias.grad, rgb)
+        # eval / no-grad forward is bit-identical
+        with torch.no_grad():
+            assert torch.equal(layer.eval()(_t(x, dev)), y.detach())
+
+
+def test_reference_signature_functions_agree_with_fused_layer(dev):
+    """conv2d_int8_{ste,lre} driven exactly as the reference layer drives them give the fused layer's numbers."""
+    import approxtorch_b200 as at
+    rng = np.random.default_rng(11)
+    lut = lo.lut_signed_truncated(4)
+    dx, dw = lo.lre_slopes(lut)
+    for mode in ("ste", "lre"):
+        layer = at.nn.Conv2d_int8(6, 8, 3, _t(lut.reshape(-1), dev), grad=mode, dx=_t(dx, dev), dw=_t(dw, dev),
+                                  bias=True, padding=1, update_scale=False).to(dev)
+        with torch.no_grad():
+            layer.scale_x.fill_(0.03)
+        x = _t(rng.standard_normal((2, 6, 7, 7)).astype(np.float32), dev)
+        xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+        ya = layer(xa)
+        q = at.nn.quantization
+        xq = q.static_quantize_int8(xb, layer.scale_x, -127, 127)
+        wq = q.static_quantize_int8(layer.weight, layer.scale_w, -127, 127, ch_axis=0)
+        geom = ((3, 3), (1, 1), (1, 1), (1, 1), 1)
+        if mode == "ste":
+            yb = at.nn.bgemm_int8.conv2d_int8_ste(xq, wq.view(8, -1), layer.lut, geom)
+        else:
+            yb = at.nn.bgemm_int8.conv2d_int8_lre(xq, wq.view(8, -1), layer.lut, layer.dx, layer.dw, geom)
+        yb = torch.addcmul(layer.bias.view(1, -1, 1, 1), yb.view(2, 8, 7, 7), (layer.scale_x * layer.scale_w).view(1, -1, 1, 1))
+        torch.testing.assert_close(ya, yb, rtol=1e-6, atol=1e-6)
+        go = torch.randn_like(ya)
+        ga = torch.autograd.grad(ya, [xa, layer.weight], go)
+        gb = torch.autograd.grad(yb, [xb, layer.weight], go)
+        for a, b in zip(ga, gb):
+            _close(a, b.cpu().numpy().astype(np.float64))
+
+
+def test_gemm_level_functions(dev):
+    import approxtorch_b200 as at
+    rng = np.random.default_rng(13)
+    N, K, L, O = 2, 19, 23, 7
+    x = rng.integers(-128, 128, (N, K, L)).astype(np.float32)
+    w = rng.integers(-128, 128, (O, K)).astype(np.float32)
+    go = rng.standard_normal((N, O, L)).astype(np.float32)
+    lut = lo.lut_signed_noisy(100, seed=9)
+    lt = _t(lut.reshape(-1), dev)
+    xi, wi = lo.to_lut_index(x, 128), lo.to_lut_index(w, 128)
+    dx, dw = lo.lre_slopes(lut)
+    DX = (rng.standard_normal(65536) * 5).astype(np.float32)
+    DW = (rng.standard_normal(65536) * 5).astype(np.float32)
+    cases = {
+        "ste": (lambda a, b: at.nn.bgemm_int8.bgemm_int8_ste(a, b, lt), lo.ste_backward(go, xi, wi)),
+        "lre": (lambda a, b: at.nn.bgemm_int8.bgemm_int8_lre(a, b, lt, _t(dx, dev), _t(dw, dev)),
+                lo.lre_backward(go, xi, wi, dx, dw)),
+        "custom": (lambda a, b: at.nn.bgemm_int8.bgemm_int8_custom(a, b, lt, _t(DX, dev), _t(DW, dev)),
+                   lo.custom_backward(go, xi, wi, DX, DW)),
+    }
+    for name, (fn, (rgx, rgw)) in cases.items():
+        xt, wt = _t(x, dev).requires_grad_(True), _t(w, dev).requires_grad_(True)
+        y = fn(xt, wt)
+        np.testing.assert_array_equal(y.detach().cpu().numpy().astype(np.int64), lo.bgemm_exact(xi, wi, lut))
+        y.backward(_t(go, dev))
+        _close(xt.grad, rgx)
+        _close(wt.grad, rgw)
+    # raw operators: [K,O] weight layout of the LRE op, every operand dtype, zero-size shapes, int8 custom twins
+    from approxtorch_b200.backend import ops
+    rgx, rgw = lo.lre_backward(go, xi, wi, dx, dw)
+    for xa, wa in ((x, w), (x.astype(np.int8), w.astype(np.int8)), (xi, wi)):
+        gx, gw = ops.bgemm_lre_backward_claude(_t(go, dev), _t(xa, dev), _t(np.ascontiguousarray(wa.T), dev),
+                                               _t(dx, dev), _t(dw, dev))
+        assert tuple(gw.shape) == (K, O)
+        _close(gx, rgx)
+        _close(gw, rgw.T)
+    gx, gw = ops.bgemm_lre_backward_claude(torch.zeros(0, O, L, device=dev), torch.zeros(0, K, L, device=dev),
+                                           _t(np.ascontiguousarray(w.T), dev), _t(dx, dev), _t(dw, dev))
+    assert gx.shape == (0, K, L) and not gw.any()
+    cgx, cgw = lo.custom_backward(go, xi, wi, DX, DW)
+    _close(ops.bgemm_custom_grad_int8_dx(_t(x.astype(np.int8), dev), _t(w.astype(np.int8), dev), _t(go, dev), _t(DX, dev)), cgx)
+    _close(ops.bgemm_custom_grad_int8_dw(_t(x.astype(np.int8), dev), _t(w.astype(np.int8), dev), _t(go, dev), _t(DW, dev)), cgw)
+    with pytest.raises(RuntimeError):
+        ops.bgemm_custom_grad_int8_dx(_t(xi, dev), _t(wi, dev), _t(go, dev), _t(DX, dev))     # wrong dtype
+
+
+def test_lre_backward_im2col_operator(dev):
+    from approxtorch_b200.backend import ops
+    rng = np.random.default_rng(17)
+    B, C, H, W, O = 2, 5, 8, 7, 6
+    x8 = rng.integers(-128, 128, (B, C, H, W)).astype(np.int8)
+    w = rng.integers(-128, 128, (O, C * 9)).astype(np.int8)
+    table_x = rng.standard_normal(256).astype(np.float32)
+    table_w = rng.standard_normal(256).astype(np.float32)
+    table_w[128] = 1e4                            # adversarial slope at the padding index
+    cols = lo.im2col_index(lo.index_of(x8, True), 3, 3, 2, 1, 1, 1)
+    go = rng.standard_normal((B, O, cols.shape[2])).astype(np.float32)
+    rgx, rgw = lo.lre_backward(go, cols, lo.index_of(w, True), table_x, table_w)
+    gx, gw = ops.bgemm_lre_backward_claude_im2col(_t(go, dev), _t(x8, dev), _t(np.ascontiguousarray(w.T), dev),
+                                                  _t(table_x, dev), _t(table_w, dev), 3, (2, 1), 1, 1)
+    _close(gx, rgx)
+    _close(gw, rgw.T)
+
+
+def _uint8_layer_truth(x, w, bias, lut, sx, zx, sw, zw, geom):
+    (kh, kw), (sh, sw_), (ph, pw), (dh, dw_) = geom
+    O = w.shape[0]
+    xq, _ = lo.fakequant_asym(x, sx, zx, 0, 255)
+    wq, _ = lo.fakequant_asym(w, sw.reshape(-1, 1, 1, 1), zw.reshape(-1, 1, 1, 1), 0, 255)
+    cols = lo.im2col_index(xq.astype(np.uint8), kh, kw, sh, sw_, ph, pw, dh, dw_, int(zx))
+    widx = wq.reshape(O, -1).astype(np.uint8)
+    t = lo.uint8_zero_point_correction(lo.bgemm_exact(cols, widx, lut), cols, widx, zx, zw)
+    s = (np.float32(sx) * sw).astype(np.float64)
+    return t * s[None, :, None] + (0 if bias is None else bias.astype(np.float64)[None, :, None])
+
+
+@pytest.mark.parametrize("geom", [(2, 6, 9, 9, 10, 3, 1, 1, 1), (2, 4, 10, 8, 7, 3, 2, 1, 1), (3, 8, 6, 6, 70, 1, 2, 0, 1)])
+def test_uint8_layer_inference_and_training_routes(dev, geom):
+    import approxtorch_b200 as at
+    B, C, H, W, O, k, s, p, d = geom
+    g4 = (_pair(k), _pair(s), _pair(p), _pair(d))
+    rng = np.random.default_rng(19)
+    torch.manual_seed(5)
+    lut = lo.lut_unsigned_truncated(6)
+    layer = at.nn.Conv2d_uint8(C, O, _pair(k), _t(lut.reshape(-1), dev), bias=True, stride=_pair(s),
+                               padding=_pair(p), update_scale=False).to(dev)
+    x = (rng.standard_normal((B, C, H, W)) * 1.2).astype(np.float32)
+    with torch.no_grad():
+        layer.x_min.fill_(-2.0)
+        layer.x_max.fill_(2.5)
+    layer._reset_qparams_from_stats()
+    assert torch.equal(layer.zero_x, torch.round(layer.zero_x)) and torch.equal(layer.zero_w, torch.round(layer.zero_w))
+    ref = _uint8_layer_truth(x, layer.weight.detach().cpu().numpy(), layer.bias.detach().cpu().numpy(), lut,
+                             layer.scale_x.item(), layer.zero_x.item(), layer.scale_w.cpu().numpy(),
+                             layer.zero_w.cpu().numpy(), g4)
+    with torch.no_grad():
+        y_inf = layer.eval()(_t(x, dev))
+    _close(y_inf.flatten(2), ref)
+    xt = _t(x, dev).requires_grad_(True)
+    y_tr = layer.train()(xt)                       # update_scale is off: statistics stay frozen
+    _close(y_tr.flatten(2), ref)
+    # STE gradient == autograd through the exact centred convolution surrogate
+    go = torch.randn_like(y_tr)
+    y_tr.backward(go)
+    q = at.nn.quantization
+    xs = _t(x, dev).requires_grad_(True)
+    ws = layer.weight.detach().clone().requires_grad_(True)
+    xq = q.static_quantize_uint8(xs, layer.scale_x, layer.zero_x, 0, 255) - layer.zero_x
+    wq = q.static_quantize_uint8(ws, layer.scale_w, layer.zero_w, 0, 255, ch_axis=0) - layer.zero_w.view(-1, 1, 1, 1)
+    prev = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        ysur = torch.nn.functional.conv2d(xq.double(), wq.double(), None, _pair(s), _pair(p)) \
+            * (layer.scale_x * layer.scale_w).double().view(1, -1, 1, 1)
+        gxs, gws = torch.autograd.grad(ysur, [xs, ws], go.double())
+    finally:
+        torch.backends.cudnn.allow_tf32 = prev
+    _close(xt.grad, gxs.cpu().numpy().astype(np.float64))
+    _close(layer.weight.grad, gws.cpu().numpy().astype(np.float64))
+
+
+def test_ema_statistics_on_device(dev):
+    import approxtorch_b200 as at
+    rng = np.random.default_rng(23)
+    lut = _t(lo.lut_exact_signed().reshape(-1), dev)
+    layer = at.nn.Conv2d_int8(3, 4, 3, lut, padding=1, scale_momentum=0.1).to(dev).train()
+    sx, sw = np.float32(1.0), layer.scale_w.cpu().numpy().copy()
+    for step in range(3):
+        x = (rng.standard_normal((2, 3, 6, 6)) * (step + 1)).astype(np.float32)
+        layer(_t(x, dev))
+        sx = lo.ema_scale_x(np.abs(x).max(), sx, 0.1)
+        sw = lo.ema(lo.weight_absmax_scale(layer.weight.detach().cpu().numpy(), 8, old=sw), sw, 0.1)
+        assert layer.scale_x.item() == sx
+        np.testing.assert_array_equal(layer.scale_w.cpu().numpy(), sw)
+    layer.freeze_scale()
+    before = layer.scale_x.clone()
+    layer(_t(x * 10, dev))
+    assert torch.equal(before, layer.scale_x)
+    layer.unfreeze_scale()
+    layer.eval()(_t(x * 10, dev))                  # eval never updates
+    assert torch.equal(before, layer.scale_x)
+
+
+def test_depthwise_layer(dev):
+    import approxtorch_b200 as at
+    from approxtorch_b200.backend import ops
+    rng = np.random.default_rng(29)
+    B, C, H, W = 2, 6, 9, 8
+    lut = lo.lut_signed_noisy(64, seed=6)
+    x8 = rng.integers(-127, 128, (B, C, H, W)).astype(np.int8)
+    w = rng.integers(-127, 128, (C, 9)).astype(np.float32)
+    y, wq = ops.dwconv_fake_int8_claude(_t(x8, dev), _t(w, dev), _t(lut.reshape(-1), dev), 3, 2, 1, 1)
+    cols = lo.im2col_index(lo.index_of(x8, True), 3, 3, 2, 2, 1, 1)            # [B, C*9, L]
+    L = cols.shape[2]
+    ref = np.stack([lo.bgemm_exact(cols[:, c * 9:(c + 1) * 9], lo.to_lut_index(w[c:c + 1], 128), lut)[:, 0]
+                    for c in range(C)], axis=1)
+    np.testing.assert_array_equal(y.flatten(2).cpu().numpy().astype(np.int64), ref)
+    for mode in ("ste", "lre"):
+        dx, dw = lo.lre_slopes(lut)
+        layer = at.nn.Conv2d_int8(C, C, 3, _t(lut.reshape(-1), dev), grad=mode, dx=_t(dx, dev), dw=_t(dw, dev),
+                                  padding=1, groups=C, update_scale=False).to(dev)
+        xt = torch.randn(B, C, H, W, device=dev, requires_grad=True)
+        out = layer(xt)
+        out.sum().backward()
+        assert out.shape == (B, C, H, W) and xt.grad is not None and layer.weight.grad.shape == layer.weight.shape
