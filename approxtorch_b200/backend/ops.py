@@ -69,7 +69,7 @@ class _Guard:
 
 # --------------------------------------------------------------------------- LUT images
 _IMAGE_BYTES = int(_lib.atb_lut_image_bytes())
-_images: "weakref.WeakKeyDictionary[Tensor, tuple[int, Tensor]]" = weakref.WeakKeyDictionary()
+_images: dict = {}      # id(lut) -> (weakref to lut, version, image); entries die with their tensor
 
 
 def lut_image(lut: Tensor) -> Tensor:
@@ -81,14 +81,15 @@ def lut_image(lut: Tensor) -> Tensor:
     _require(lut.is_cuda, "lut must be a CUDA tensor")
     _require(lut.dtype == torch.float32, "lut must be float32")
     _require(lut.numel() == 65536, "lut must have 65536 elements")
-    hit = _images.get(lut)
-    if hit is not None and hit[0] == lut._version and hit[1].device == lut.device:
-        return hit[1]
+    key = id(lut)
+    hit = _images.get(key)
+    if hit is not None and hit[0]() is lut and hit[1] == lut._version and hit[2].device == lut.device:
+        return hit[2]
     src = lut.detach().contiguous()
     img = torch.empty(_IMAGE_BYTES, dtype=torch.uint8, device=lut.device)
     with _Guard(lut):
         _check(_lib.atb_lut_prepare(_ptr(src), _ptr(img), _stream(lut)), "atb_lut_prepare")
-    _images[lut] = (lut._version, img)
+    _images[key] = (weakref.ref(lut, lambda _r, k=key: _images.pop(k, None)), lut._version, img)
     return img
 
 
@@ -102,13 +103,13 @@ def quantize_u8(x: Tensor, offset: int) -> Tensor:
 
 
 def _normalise_cfg(cfg: int) -> int:
-    """cfg < 0: automatic.  Otherwise bits 0-15 = pixel rows per block (multiple of 32, up to 512) and
+    """cfg < 0: automatic.  Otherwise bits 0-15 = pixel rows per block (multiple of 32 in [64, 512]) and
     bits 16-23 = split-K factor; the reference's tile ids (0..18, 100..118) do not name a tiling of
     this kernel and select the automatic plan."""
     if cfg < 0:
         return -1
     rows = cfg & 0xFFFF
-    if rows != 0 and (rows % 32 != 0 or rows > 512):
+    if rows != 0 and (rows % 32 != 0 or rows < 64 or rows > 512):
         return -1
     return cfg
 

@@ -102,25 +102,42 @@ __device__ __forceinline__ void stage_columns(uint8_t* stage, const uint8_t* s_t
     }
 }
 
-template <int CLS>
-__device__ __forceinline__ void lookup_step(const uint8_t* stage, const uint8_t* xrow, int lane,
-                                            int (&acc)[32][2])
+// Lookups of TWO k-steps for this thread's 32 pixel rows x 2 output channels.  Entries are unsigned
+// 16-bit (signed tables are stored with a +32768 bias that the epilogue removes), so the load needs no
+// sign extension, and the two steps' entries of one output are added with a single three-input add.
+__device__ __forceinline__ void lookup_pair(const uint8_t* stage_a, const uint8_t* stage_b,
+                                            const uint8_t* xrow_a, const uint8_t* xrow_b, int lane,
+                                            unsigned (&acc)[32][2])
 {
-    const uint4 xa = *reinterpret_cast<const uint4*>(xrow);
-    const uint4 xb = *reinterpret_cast<const uint4*>(xrow + 16);
-    const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-    const uint8_t* base = stage + lane * kRowPitch;
+    const uint4 a0 = *reinterpret_cast<const uint4*>(xrow_a);
+    const uint4 a1 = *reinterpret_cast<const uint4*>(xrow_a + 16);
+    const uint4 b0 = *reinterpret_cast<const uint4*>(xrow_b);
+    const uint4 b1 = *reinterpret_cast<const uint4*>(xrow_b + 16);
+    const uint32_t xa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const uint32_t xb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    const uint16_t* base_a = reinterpret_cast<const uint16_t*>(stage_a + lane * kRowPitch);
+    const uint16_t* base_b = reinterpret_cast<const uint16_t*>(stage_b + lane * kRowPitch);
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-        const uint32_t xv = (xw[j >> 2] >> (8 * (j & 3))) & 0xffu;
-        const uint8_t* p = base + 2u * xv;
-        if constexpr (CLS == LUT_I16) {
-            acc[j][0] += static_cast<int>(*reinterpret_cast<const int16_t*>(p));
-            acc[j][1] += static_cast<int>(*reinterpret_cast<const int16_t*>(p + 32 * kRowPitch));
-        } else {
-            acc[j][0] += static_cast<int>(*reinterpret_cast<const uint16_t*>(p));
-            acc[j][1] += static_cast<int>(*reinterpret_cast<const uint16_t*>(p + 32 * kRowPitch));
-        }
+        const uint16_t* pa = base_a + __byte_perm(xa[j >> 2], 0, 0x4440 | (j & 3));
+        const uint16_t* pb = base_b + __byte_perm(xb[j >> 2], 0, 0x4440 | (j & 3));
+        acc[j][0] += static_cast<unsigned>(pa[0]) + static_cast<unsigned>(pb[0]);
+        acc[j][1] += static_cast<unsigned>(pa[16 * kRowPitch]) + static_cast<unsigned>(pb[16 * kRowPitch]);
+    }
+}
+
+__device__ __forceinline__ void lookup_single(const uint8_t* stage_a, const uint8_t* xrow_a, int lane,
+                                              unsigned (&acc)[32][2])
+{
+    const uint4 a0 = *reinterpret_cast<const uint4*>(xrow_a);
+    const uint4 a1 = *reinterpret_cast<const uint4*>(xrow_a + 16);
+    const uint32_t xa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const uint16_t* base_a = reinterpret_cast<const uint16_t*>(stage_a + lane * kRowPitch);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const uint16_t* pa = base_a + __byte_perm(xa[j >> 2], 0, 0x4440 | (j & 3));
+        acc[j][0] += static_cast<unsigned>(pa[0]);
+        acc[j][1] += static_cast<unsigned>(pa[16 * kRowPitch]);
     }
 }
 
@@ -217,10 +234,35 @@ __device__ __forceinline__ void store_chunk(uint8_t* s_x, uint8_t* s_w, int buf,
     }
 }
 
-template <int CLS>
-__device__ __forceinline__ void gemm_body(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
-                                          const uint8_t* wcol, bool vec_x, bool vec_w, int pad,
-                                          long long r0, long long r_end, int c0, int kbeg, int kend)
+// Epilogue shared by both paths: `total(j, t)` yields the finished sum of row j, column slot t.
+template <class Total, class Bits>
+__device__ __forceinline__ void write_tile(const GemmArgs& a, long long r0, long long r_end, int c0, int warp, int lane,
+                                           int xsum, Total total, Bits bits)
+{
+    const int split = blockIdx.z;
+    const bool want_xsum = a.zero_x != nullptr;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const long long r = r0 + warp * 32 + j;
+        const int xs = __shfl_sync(0xffffffffu, xsum, j);
+        if (r >= r_end) continue;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const int o = c0 + lane + 32 * t;
+            if (o >= a.O) continue;
+            if (a.splits > 1) a.scratch[(static_cast<long long>(split) * a.R + r) * a.O + o] = bits(j, t);
+            else a.y[output_offset(r, o, a)] = finalize_output(total(j, t), xs, o, a);
+        }
+        if (a.splits > 1 && want_xsum && blockIdx.y == 0 && lane == 0)
+            a.scratch[static_cast<long long>(a.splits) * a.R * a.O + static_cast<long long>(split) * a.R + r] = xs;
+    }
+}
+
+// 16-bit table classes: staged conflict-free lookups, exact integer accumulation.
+// k-steps are processed in pairs: stage both steps' columns, barrier, look both up, barrier.
+__device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
+                                              const uint8_t* wcol, bool vec_x, bool vec_w, int pad, int bias,
+                                              long long r0, long long r_end, int c0, int kbeg, int kend)
 {
     uint8_t* s_tab = smem;
     uint8_t* s_stage = smem + kSmemStage;
@@ -232,10 +274,64 @@ __device__ __forceinline__ void gemm_body(const GemmArgs& a, uint8_t* smem, cons
     const int nwarps = blockDim.x >> 5;
     const int nch = (kend - kbeg + kChunk - 1) / kChunk;
 
-    using acc_t = typename std::conditional<CLS == LUT_F32, float, int>::type;
-    acc_t acc[32][2];
+    unsigned acc[32][2];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) { acc[j][0] = 0; acc[j][1] = 0; }
+    for (int j = 0; j < 32; ++j) { acc[j][0] = 0u; acc[j][1] = 0u; }
+    int xsum = 0;
+    const bool want_xsum = a.zero_x != nullptr;
+
+    uint32_t xr[4], wr[4];
+    if (nch > 0) {
+        load_chunk(a, rc, wcol, vec_x, vec_w, kbeg, kend, tid, pad, xr, wr);
+        store_chunk(s_x, s_w, 0, tid, xr, wr);
+    }
+    __syncthreads();          // table image and first operand tile are in shared memory
+
+    for (int ci = 0; ci < nch; ++ci) {
+        const int k0 = kbeg + ci * kChunk;
+        const int kc = min(kChunk, kend - k0);
+        const int cur = ci & 1;
+        const bool has_next = ci + 1 < nch;
+        if (has_next) load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr);
+        for (int kk = 0; kk < kc; kk += 2) {
+            const bool pair = kk + 1 < kc;
+            const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * 32;
+            const uint8_t* wstep = s_w + (cur * kChunk + kk) * kStagedCols;
+            stage_columns(s_stage, s_tab, wstep, warp, lane, nwarps);
+            if (pair) stage_columns(s_stage + kStageBytes, s_tab, wstep + kStagedCols, warp, lane, nwarps);
+            if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr);
+            __syncthreads();
+            if (want_xsum) {
+                xsum += static_cast<int>(xrow[lane]);
+                if (pair) xsum += static_cast<int>(xrow[kMaxBlockRows + lane]);
+            }
+            if (pair) lookup_pair(s_stage, s_stage + kStageBytes, xrow, xrow + kMaxBlockRows, lane, acc);
+            else lookup_single(s_stage, xrow, lane, acc);
+            __syncthreads();
+        }
+    }
+    const long long remove = static_cast<long long>(bias) * (kend - kbeg);     // +32768 per looked-up entry of a signed table
+    write_tile(a, r0, r_end, c0, warp, lane, xsum,
+               [&](int j, int t) { return static_cast<double>(static_cast<long long>(acc[j][t]) - remove); },
+               [&](int j, int t) { return static_cast<int>(static_cast<long long>(acc[j][t]) - remove); });
+}
+
+// Tables that are not 16-bit exact: lookups from the transposed fp32 table in global memory,
+// fp32 accumulation in ascending k.
+__device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
+                                              const uint8_t* wcol, bool vec_x, bool vec_w, int pad,
+                                              long long r0, long long r_end, int c0, int kbeg, int kend)
+{
+    uint8_t* s_x = smem + kSmemX;
+    uint8_t* s_w = smem + kSmemW;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int nch = (kend - kbeg + kChunk - 1) / kChunk;
+
+    float acc[32][2];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { acc[j][0] = 0.0f; acc[j][1] = 0.0f; }
     int xsum = 0;
     const bool want_xsum = a.zero_x != nullptr;
 
@@ -245,12 +341,6 @@ __device__ __forceinline__ void gemm_body(const GemmArgs& a, uint8_t* smem, cons
         store_chunk(s_x, s_w, 0, tid, xr, wr);
     }
     __syncthreads();
-    if (CLS != LUT_F32 && nch > 0) {
-        stage_columns(s_stage, s_tab, s_w, warp, lane, nwarps);
-        __syncthreads();
-    }
-
-    int step = 0;
     for (int ci = 0; ci < nch; ++ci) {
         const int k0 = kbeg + ci * kChunk;
         const int kc = min(kChunk, kend - k0);
@@ -262,45 +352,13 @@ __device__ __forceinline__ void gemm_body(const GemmArgs& a, uint8_t* smem, cons
             const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * 32;
             const uint8_t* wstep = s_w + (cur * kChunk + kk) * kStagedCols;
             if (want_xsum) xsum += static_cast<int>(xrow[lane]);
-            if constexpr (CLS == LUT_F32) {
-                lookup_step_f32(a.img->tabT32, wstep, xrow, lane, acc);
-                if (kk == kc - 1) __syncthreads();
-            } else {
-                const uint8_t* wnext = nullptr;
-                if (kk + 1 < kc) wnext = wstep + kStagedCols;
-                else if (has_next) wnext = s_w + ((cur ^ 1) * kChunk) * kStagedCols;
-                if (wnext != nullptr)
-                    stage_columns(s_stage + ((step + 1) & 1) * kStageBytes, s_tab, wnext, warp, lane, nwarps);
-                lookup_step<CLS>(s_stage + (step & 1) * kStageBytes, xrow, lane, acc);
-                __syncthreads();
-            }
-            ++step;
+            lookup_step_f32(a.img->tabT32, wstep, xrow, lane, acc);
         }
+        __syncthreads();
     }
-
-    // ---- epilogue ----
-    const int split = blockIdx.z;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        const long long r = r0 + warp * 32 + j;
-        const int xs = __shfl_sync(0xffffffffu, xsum, j);
-        if (r >= r_end) continue;
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            const int o = c0 + lane + 32 * t;
-            if (o >= a.O) continue;
-            if (a.splits > 1) {
-                int bits;
-                if constexpr (CLS == LUT_F32) bits = __float_as_int(acc[j][t]);
-                else bits = acc[j][t];
-                a.scratch[(static_cast<long long>(split) * a.R + r) * a.O + o] = bits;
-            } else {
-                a.y[output_offset(r, o, a)] = finalize_output(static_cast<double>(acc[j][t]), xs, o, a);
-            }
-        }
-        if (a.splits > 1 && want_xsum && blockIdx.y == 0 && lane == 0)
-            a.scratch[static_cast<long long>(a.splits) * a.R * a.O + static_cast<long long>(split) * a.R + r] = xs;
-    }
+    write_tile(a, r0, r_end, c0, warp, lane, xsum,
+               [&](int j, int t) { return static_cast<double>(acc[j][t]); },
+               [&](int j, int t) { return __float_as_int(acc[j][t]); });
 }
 
 __global__ void __launch_bounds__(kMaxBlockRows, 1) lut_gemm_kernel(const GemmArgs a)
@@ -353,16 +411,22 @@ __global__ void __launch_bounds__(kMaxBlockRows, 1) lut_gemm_kernel(const GemmAr
                        ((a.w_batch_stride & 15) == 0);
 
     const int cls = lut_class_of(a.img);
-    if (cls != LUT_F32) {
-        const uint4* src = reinterpret_cast<const uint4*>(a.img->tabT16);
-        uint4* dst = reinterpret_cast<uint4*>(smem);
-        for (int i = tid; i < kTableBytes / 16; i += bm) dst[i] = __ldg(src + i);
-    }
     // pad_index < 0: taps outside the image take the activation zero point (an integer-valued device scalar)
     const int pad = a.pad_index >= 0 ? a.pad_index : min(255, max(0, static_cast<int>(llrintf(__ldg(a.zero_x)))));
-    if (cls == LUT_I16) gemm_body<LUT_I16>(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend);
-    else if (cls == LUT_U16) gemm_body<LUT_U16>(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend);
-    else gemm_body<LUT_F32>(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend);
+    if (cls != LUT_F32) {
+        // signed entries are stored biased (+32768 == flipping bit 15), so every lookup is an unsigned 16-bit load
+        const uint32_t flip = (cls == LUT_I16) ? 0x80008000u : 0u;
+        const uint4* src = reinterpret_cast<const uint4*>(a.img->tabT16);
+        uint4* dst = reinterpret_cast<uint4*>(smem);
+        for (int i = tid; i < kTableBytes / 16; i += bm) {
+            uint4 v = __ldg(src + i);
+            v.x ^= flip; v.y ^= flip; v.z ^= flip; v.w ^= flip;
+            dst[i] = v;
+        }
+        gemm_body_int(a, smem, rc, wcol, vec_x, vec_w, pad, cls == LUT_I16 ? 32768 : 0, r0, r_end, c0, kbeg, kend);
+    } else {
+        gemm_body_f32(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend);
+    }
 }
 
 // Split-K: y = finalize(sum_s partial[s]) in ascending split order.
@@ -413,12 +477,24 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
     int bm = 0, splits = 0;
     if (cfg >= 0) { bm = cfg & 0xffff; splits = (cfg >> 16) & 0xff; }
     if (bm != 0) {
-        ATB_REQUIRE(bm % 32 == 0 && bm >= 32 && bm <= kMaxBlockRows, "cfg: block rows must be a multiple of 32 in [32, 512]");
+        ATB_REQUIRE(bm % 32 == 0 && bm >= kStagedCols && bm <= kMaxBlockRows, "cfg: block rows must be a multiple of 32 in [64, 512]");
     } else {
         long long want = ((span + 31) / 32) * 32;
-        if (want > kMaxBlockRows) want = kMaxBlockRows;
-        if (want < 32) want = 32;
-        bm = static_cast<int>(want);
+        if (want < kStagedCols) want = kStagedCols;     // one thread per staged column loads the weight tile
+        if (want <= kMaxBlockRows) {
+            bm = static_cast<int>(want);
+        } else {
+            // Whole waves of equal tiles: pick the block height whose (waves x per-tile cost) is lowest.
+            // Per-tile cost ~ rows + 256: 2 lookup wavefronts per row plus 512 staging wavefronts per k-step.
+            const long long col_tiles = ceil_div(O > 0 ? O : 1, kStagedCols);
+            long long best_cost = -1;
+            for (int cand = kMaxBlockRows; cand >= 384; cand -= 32) {
+                const long long rt_c = wb_rows > 0 ? (R / wb_rows) * ceil_div(wb_rows, cand) : (R + cand - 1) / cand;
+                const long long waves = (rt_c * col_tiles + sms - 1) / sms;
+                const long long cost = waves * (cand + 256);
+                if (best_cost < 0 || cost < best_cost) { best_cost = cost; bm = cand; }
+            }
+        }
     }
     const int tpb = wb_rows > 0 ? ceil_div(wb_rows, bm) : 0;
     const long long rt = wb_rows > 0 ? (R / (wb_rows > 0 ? wb_rows : 1)) * tpb : (R + bm - 1) / bm;

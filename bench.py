@@ -198,6 +198,19 @@ def run_gpu_arm(args):
     for _ in range(max(3, args.warmup)):
         step_resident()
     barrier()
+    if args.kernel_only:
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.steps):
+            step_resident()
+        t1.record()
+        barrier()
+        if rank == 0:
+            ms = t0.elapsed_time(t1) / args.steps
+            print(json.dumps({"kernel_only": True, "ms_per_step": ms, "value": MACS_PER_STEP / (ms * 1e-3), "unit": UNIT}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     sampler = ClockSampler(local)
     sampler.start()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
@@ -301,6 +314,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="run only warm-up + timed device-resident steps (no L2 flush, no end-to-end or CPU leg): "
+                         "the command profiled under ncu")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

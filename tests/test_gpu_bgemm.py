@@ -16,7 +16,8 @@ def _ops():
 
 
 def _t(a, dev):
-    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    a = np.asarray(a)
+    return torch.from_numpy(np.ascontiguousarray(a).reshape(a.shape)).to(dev)
 
 
 @pytest.mark.parametrize("name", ["affine", "noisy", "trunc4", "utrunc6"])

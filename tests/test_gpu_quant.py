@@ -11,7 +11,8 @@ pytestmark = pytest.mark.gpu
 
 
 def _t(a, dev):
-    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    a = np.asarray(a)
+    return torch.from_numpy(np.ascontiguousarray(a).reshape(a.shape)).to(dev)
 
 
 def test_per_tensor_fakequant_matches_reference_fixture(golden, dev):
