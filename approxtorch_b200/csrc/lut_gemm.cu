@@ -105,20 +105,28 @@ __device__ __forceinline__ void stage_columns(uint8_t* stage, const uint8_t* s_t
 // Lookups of TWO k-steps for this thread's 32 pixel rows x 2 output channels.  Entries are unsigned
 // 16-bit (signed tables are stored with a +32768 bias that the epilogue removes), so the load needs no
 // sign extension, and the two steps' entries of one output are added with a single three-input add.
+template <int TM>
+__device__ __forceinline__ void load_x_words(const uint8_t* xrow, uint32_t (&xw)[TM / 4])
+{
+#pragma unroll
+    for (int q = 0; q < TM / 16; ++q) {
+        const uint4 v = *reinterpret_cast<const uint4*>(xrow + 16 * q);
+        xw[4 * q] = v.x; xw[4 * q + 1] = v.y; xw[4 * q + 2] = v.z; xw[4 * q + 3] = v.w;
+    }
+}
+
+template <int TM>
 __device__ __forceinline__ void lookup_pair(const uint8_t* stage_a, const uint8_t* stage_b,
                                             const uint8_t* xrow_a, const uint8_t* xrow_b, int lane,
-                                            unsigned (&acc)[32][2])
+                                            unsigned (&acc)[TM][2])
 {
-    const uint4 a0 = *reinterpret_cast<const uint4*>(xrow_a);
-    const uint4 a1 = *reinterpret_cast<const uint4*>(xrow_a + 16);
-    const uint4 b0 = *reinterpret_cast<const uint4*>(xrow_b);
-    const uint4 b1 = *reinterpret_cast<const uint4*>(xrow_b + 16);
-    const uint32_t xa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-    const uint32_t xb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    uint32_t xa[TM / 4], xb[TM / 4];
+    load_x_words<TM>(xrow_a, xa);
+    load_x_words<TM>(xrow_b, xb);
     const uint16_t* base_a = reinterpret_cast<const uint16_t*>(stage_a + lane * kRowPitch);
     const uint16_t* base_b = reinterpret_cast<const uint16_t*>(stage_b + lane * kRowPitch);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < TM; ++j) {
         const uint16_t* pa = base_a + __byte_perm(xa[j >> 2], 0, 0x4440 | (j & 3));
         const uint16_t* pb = base_b + __byte_perm(xb[j >> 2], 0, 0x4440 | (j & 3));
         acc[j][0] += static_cast<unsigned>(pa[0]) + static_cast<unsigned>(pb[0]);
@@ -126,31 +134,31 @@ __device__ __forceinline__ void lookup_pair(const uint8_t* stage_a, const uint8_
     }
 }
 
+template <int TM>
 __device__ __forceinline__ void lookup_single(const uint8_t* stage_a, const uint8_t* xrow_a, int lane,
-                                              unsigned (&acc)[32][2])
+                                              unsigned (&acc)[TM][2])
 {
-    const uint4 a0 = *reinterpret_cast<const uint4*>(xrow_a);
-    const uint4 a1 = *reinterpret_cast<const uint4*>(xrow_a + 16);
-    const uint32_t xa[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    uint32_t xa[TM / 4];
+    load_x_words<TM>(xrow_a, xa);
     const uint16_t* base_a = reinterpret_cast<const uint16_t*>(stage_a + lane * kRowPitch);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < TM; ++j) {
         const uint16_t* pa = base_a + __byte_perm(xa[j >> 2], 0, 0x4440 | (j & 3));
         acc[j][0] += static_cast<unsigned>(pa[0]);
         acc[j][1] += static_cast<unsigned>(pa[16 * kRowPitch]);
     }
 }
 
+template <int TM>
 __device__ __forceinline__ void lookup_step_f32(const float* tabT, const uint8_t* wstep, const uint8_t* xrow,
-                                                int lane, float (&acc)[32][2])
+                                                int lane, float (&acc)[TM][2])
 {
-    const uint4 xa = *reinterpret_cast<const uint4*>(xrow);
-    const uint4 xb = *reinterpret_cast<const uint4*>(xrow + 16);
-    const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+    uint32_t xw[TM / 4];
+    load_x_words<TM>(xrow, xw);
     const float* c0 = tabT + (static_cast<uint32_t>(wstep[lane]) << 8);
     const float* c1 = tabT + (static_cast<uint32_t>(wstep[lane + 32]) << 8);
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
+    for (int j = 0; j < TM; ++j) {
         const uint32_t xv = (xw[j >> 2] >> (8 * (j & 3))) & 0xffu;
         acc[j][0] += __ldg(c0 + xv);
         acc[j][1] += __ldg(c1 + xv);
@@ -165,9 +173,11 @@ struct RowCursor {
 
 __device__ __forceinline__ void load_chunk(const GemmArgs& a, const RowCursor& rc, const uint8_t* wcol,
                                            bool vec_x, bool vec_w, int k0, int kend, int tid, int pad,
-                                           uint32_t (&xr)[4], uint32_t (&wr)[4])
+                                           uint32_t (&xr)[4], uint32_t (&wr)[4], int bm)
 {
-    if (a.image_mode) {
+    if (tid >= bm) {
+        // threads beyond the tile's rows (16-rows-per-warp layout) load no pixel operand
+    } else if (a.image_mode) {
         const int khw = a.g.KH * a.g.KW;
         int c = k0 / khw;
         int rem = k0 - c * khw;
@@ -220,12 +230,14 @@ __device__ __forceinline__ void load_chunk(const GemmArgs& a, const RowCursor& r
 }
 
 __device__ __forceinline__ void store_chunk(uint8_t* s_x, uint8_t* s_w, int buf, int tid,
-                                            const uint32_t (&xr)[4], const uint32_t (&wr)[4])
+                                            const uint32_t (&xr)[4], const uint32_t (&wr)[4], int bm)
 {
-    uint8_t* xd = s_x + buf * kChunk * kMaxBlockRows + tid;
+    if (tid < bm) {
+        uint8_t* xd = s_x + buf * kChunk * kMaxBlockRows + tid;
 #pragma unroll
-    for (int kk = 0; kk < kChunk; ++kk)
-        xd[kk * kMaxBlockRows] = static_cast<uint8_t>(xr[kk >> 2] >> (8 * (kk & 3)));
+        for (int kk = 0; kk < kChunk; ++kk)
+            xd[kk * kMaxBlockRows] = static_cast<uint8_t>(xr[kk >> 2] >> (8 * (kk & 3)));
+    }
     if (tid < kStagedCols) {
         uint8_t* wd = s_w + buf * kChunk * kStagedCols + tid;
 #pragma unroll
@@ -235,15 +247,15 @@ __device__ __forceinline__ void store_chunk(uint8_t* s_x, uint8_t* s_w, int buf,
 }
 
 // Epilogue shared by both paths: `total(j, t)` yields the finished sum of row j, column slot t.
-template <class Total, class Bits>
+template <int TM, class Total, class Bits>
 __device__ __forceinline__ void write_tile(const GemmArgs& a, long long r0, long long r_end, int c0, int warp, int lane,
                                            int xsum, Total total, Bits bits)
 {
     const int split = blockIdx.z;
     const bool want_xsum = a.zero_x != nullptr;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        const long long r = r0 + warp * 32 + j;
+    for (int j = 0; j < TM; ++j) {
+        const long long r = r0 + warp * TM + j;
         const int xs = __shfl_sync(0xffffffffu, xsum, j);
         if (r >= r_end) continue;
 #pragma unroll
@@ -260,6 +272,7 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, long long r0, long
 
 // 16-bit table classes: staged conflict-free lookups, exact integer accumulation.
 // k-steps are processed in pairs: stage both steps' columns, barrier, look both up, barrier.
+template <int TM>
 __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
                                               const uint8_t* wcol, bool vec_x, bool vec_w, int pad, int bias,
                                               long long r0, long long r_end, int c0, int kbeg, int kend)
@@ -274,16 +287,17 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
     const int nwarps = blockDim.x >> 5;
     const int nch = (kend - kbeg + kChunk - 1) / kChunk;
 
-    unsigned acc[32][2];
+    const int bm = nwarps * TM;
+    unsigned acc[TM][2];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) { acc[j][0] = 0u; acc[j][1] = 0u; }
+    for (int j = 0; j < TM; ++j) { acc[j][0] = 0u; acc[j][1] = 0u; }
     int xsum = 0;
     const bool want_xsum = a.zero_x != nullptr;
 
     uint32_t xr[4], wr[4];
     if (nch > 0) {
-        load_chunk(a, rc, wcol, vec_x, vec_w, kbeg, kend, tid, pad, xr, wr);
-        store_chunk(s_x, s_w, 0, tid, xr, wr);
+        load_chunk(a, rc, wcol, vec_x, vec_w, kbeg, kend, tid, pad, xr, wr, bm);
+        store_chunk(s_x, s_w, 0, tid, xr, wr, bm);
     }
     __syncthreads();          // table image and first operand tile are in shared memory
 
@@ -292,32 +306,33 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
         const int kc = min(kChunk, kend - k0);
         const int cur = ci & 1;
         const bool has_next = ci + 1 < nch;
-        if (has_next) load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr);
+        if (has_next) load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr, bm);
         for (int kk = 0; kk < kc; kk += 2) {
             const bool pair = kk + 1 < kc;
-            const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * 32;
+            const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * TM;
             const uint8_t* wstep = s_w + (cur * kChunk + kk) * kStagedCols;
             stage_columns(s_stage, s_tab, wstep, warp, lane, nwarps);
             if (pair) stage_columns(s_stage + kStageBytes, s_tab, wstep + kStagedCols, warp, lane, nwarps);
-            if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr);
+            if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr, bm);
             __syncthreads();
-            if (want_xsum) {
+            if (want_xsum && lane < TM) {
                 xsum += static_cast<int>(xrow[lane]);
                 if (pair) xsum += static_cast<int>(xrow[kMaxBlockRows + lane]);
             }
-            if (pair) lookup_pair(s_stage, s_stage + kStageBytes, xrow, xrow + kMaxBlockRows, lane, acc);
-            else lookup_single(s_stage, xrow, lane, acc);
+            if (pair) lookup_pair<TM>(s_stage, s_stage + kStageBytes, xrow, xrow + kMaxBlockRows, lane, acc);
+            else lookup_single<TM>(s_stage, xrow, lane, acc);
             __syncthreads();
         }
     }
     const long long remove = static_cast<long long>(bias) * (kend - kbeg);     // +32768 per looked-up entry of a signed table
-    write_tile(a, r0, r_end, c0, warp, lane, xsum,
+    write_tile<TM>(a, r0, r_end, c0, warp, lane, xsum,
                [&](int j, int t) { return static_cast<double>(static_cast<long long>(acc[j][t]) - remove); },
                [&](int j, int t) { return static_cast<int>(static_cast<long long>(acc[j][t]) - remove); });
 }
 
 // Tables that are not 16-bit exact: lookups from the transposed fp32 table in global memory,
 // fp32 accumulation in ascending k.
+template <int TM>
 __device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
                                               const uint8_t* wcol, bool vec_x, bool vec_w, int pad,
                                               long long r0, long long r_end, int c0, int kbeg, int kend)
@@ -329,16 +344,17 @@ __device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, 
     const int warp = tid >> 5;
     const int nch = (kend - kbeg + kChunk - 1) / kChunk;
 
-    float acc[32][2];
+    const int bm = (blockDim.x >> 5) * TM;
+    float acc[TM][2];
 #pragma unroll
-    for (int j = 0; j < 32; ++j) { acc[j][0] = 0.0f; acc[j][1] = 0.0f; }
+    for (int j = 0; j < TM; ++j) { acc[j][0] = 0.0f; acc[j][1] = 0.0f; }
     int xsum = 0;
     const bool want_xsum = a.zero_x != nullptr;
 
     uint32_t xr[4], wr[4];
     if (nch > 0) {
-        load_chunk(a, rc, wcol, vec_x, vec_w, kbeg, kend, tid, pad, xr, wr);
-        store_chunk(s_x, s_w, 0, tid, xr, wr);
+        load_chunk(a, rc, wcol, vec_x, vec_w, kbeg, kend, tid, pad, xr, wr, bm);
+        store_chunk(s_x, s_w, 0, tid, xr, wr, bm);
     }
     __syncthreads();
     for (int ci = 0; ci < nch; ++ci) {
@@ -346,26 +362,29 @@ __device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, 
         const int kc = min(kChunk, kend - k0);
         const int cur = ci & 1;
         const bool has_next = ci + 1 < nch;
-        if (has_next) load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr);
+        if (has_next) load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr, bm);
         for (int kk = 0; kk < kc; ++kk) {
-            if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr);
-            const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * 32;
+            if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr, bm);
+            const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * TM;
             const uint8_t* wstep = s_w + (cur * kChunk + kk) * kStagedCols;
-            if (want_xsum) xsum += static_cast<int>(xrow[lane]);
-            lookup_step_f32(a.img->tabT32, wstep, xrow, lane, acc);
+            if (want_xsum && lane < TM) xsum += static_cast<int>(xrow[lane]);
+            lookup_step_f32<TM>(a.img->tabT32, wstep, xrow, lane, acc);
         }
         __syncthreads();
     }
-    write_tile(a, r0, r_end, c0, warp, lane, xsum,
+    write_tile<TM>(a, r0, r_end, c0, warp, lane, xsum,
                [&](int j, int t) { return static_cast<double>(acc[j][t]); },
                [&](int j, int t) { return __float_as_int(acc[j][t]); });
 }
 
-__global__ void __launch_bounds__(kMaxBlockRows, 1) lut_gemm_kernel(const GemmArgs a)
+// TM = pixel rows per warp: 32 (one thread per row loads tiles, 64 accumulators per thread) or 16
+// (twice the warps for the same tile, 32 accumulators per thread).
+template <int TM>
+__global__ void __launch_bounds__(kMaxBlockRows * 32 / TM, 1) lut_gemm_kernel(const GemmArgs a)
 {
     extern __shared__ __align__(16) uint8_t smem[];
     const int tid = threadIdx.x;
-    const int bm = blockDim.x;
+    const int bm = (blockDim.x >> 5) * TM;
 
     long long r0, r_end;
     long long wbatch = 0;
@@ -386,7 +405,7 @@ __global__ void __launch_bounds__(kMaxBlockRows, 1) lut_gemm_kernel(const GemmAr
     const int kend = min(a.K, ch_end * kChunk);
 
     // this thread's pixel row for the tile loads (clamped: rows past the end are never stored)
-    const long long r = min(r0 + tid, r_end - 1);
+    const long long r = min(r0 + min(tid, bm - 1), r_end - 1);
     RowCursor rc;
     bool vec_x = false;
     if (a.image_mode) {
@@ -418,14 +437,14 @@ __global__ void __launch_bounds__(kMaxBlockRows, 1) lut_gemm_kernel(const GemmAr
         const uint32_t flip = (cls == LUT_I16) ? 0x80008000u : 0u;
         const uint4* src = reinterpret_cast<const uint4*>(a.img->tabT16);
         uint4* dst = reinterpret_cast<uint4*>(smem);
-        for (int i = tid; i < kTableBytes / 16; i += bm) {
+        for (int i = tid; i < kTableBytes / 16; i += blockDim.x) {
             uint4 v = __ldg(src + i);
             v.x ^= flip; v.y ^= flip; v.z ^= flip; v.w ^= flip;
             dst[i] = v;
         }
-        gemm_body_int(a, smem, rc, wcol, vec_x, vec_w, pad, cls == LUT_I16 ? 32768 : 0, r0, r_end, c0, kbeg, kend);
+        gemm_body_int<TM>(a, smem, rc, wcol, vec_x, vec_w, pad, cls == LUT_I16 ? 32768 : 0, r0, r_end, c0, kbeg, kend);
     } else {
-        gemm_body_f32(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend);
+        gemm_body_f32<TM>(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend);
     }
 }
 
@@ -524,7 +543,9 @@ static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes,
 {
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(lut_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+        cudaError_t e = cudaFuncSetAttribute(lut_gemm_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(lut_gemm_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
         attr_set = true;
     }
@@ -554,7 +575,9 @@ static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes,
     a.splits = plan.splits;
     a.chunks_per_split = ceil_div(ceil_div(a.K, kChunk), plan.splits);
     dim3 grid(static_cast<unsigned>(row_tiles), static_cast<unsigned>(col_tiles), static_cast<unsigned>(plan.splits));
-    lut_gemm_kernel<<<grid, plan.block_rows, kSmemTotal, stream>>>(a);
+    const bool wide = cfg >= 0 && ((cfg >> 24) & 1);        // cfg bit 24: 16 rows per warp, twice the warps
+    if (wide) lut_gemm_kernel<16><<<grid, plan.block_rows * 2, kSmemTotal, stream>>>(a);
+    else lut_gemm_kernel<32><<<grid, plan.block_rows, kSmemTotal, stream>>>(a);
     rc = check_launch("lut_gemm_kernel");
     if (rc != ATB_OK) return rc;
     if (plan.splits > 1) {

@@ -186,7 +186,7 @@ def run_gpu_arm(args):
         for i in range(BATCH):
             _C.check(_C.lib.atb_quantize_transpose_u8(ops._ptr(b_dev[i]), ops.U8, K, NCOL, NCOL, 1, 0,
                                                       ops._ptr(bq[i]), stream), "transpose")
-        ops.lut_gemm_launch(a_dev, bq, image, y, BATCH * M, K, 1, NCOL, wb_rows=M, w_batch_stride=NCOL * K)
+        ops.lut_gemm_launch(a_dev, bq, image, y, BATCH * M, K, 1, NCOL, wb_rows=M, w_batch_stride=NCOL * K, cfg=args.cfg)
     launches_per_step = BATCH + 1
 
     def barrier():
@@ -222,7 +222,7 @@ def run_gpu_arm(args):
             _C.check(_C.lib.atb_quantize_transpose_u8(ops._ptr(b_dev[j]), ops.U8, K, NCOL, NCOL, 1, 0,
                                                       ops._ptr(bq[j]), stream), "transpose")
         gemm_ev[i][0].record()
-        ops.lut_gemm_launch(a_dev, bq, image, y, BATCH * M, K, 1, NCOL, wb_rows=M, w_batch_stride=NCOL * K)
+        ops.lut_gemm_launch(a_dev, bq, image, y, BATCH * M, K, 1, NCOL, wb_rows=M, w_batch_stride=NCOL * K, cfg=args.cfg)
         gemm_ev[i][1].record()
         ev[i][1].record()
     barrier()
@@ -314,6 +314,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cfg", type=int, default=-1, help="tiling override passed to the LUT-GEMM launch (-1: automatic)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="run only warm-up + timed device-resident steps (no L2 flush, no end-to-end or CPU leg): "
                          "the command profiled under ncu")
