@@ -2,7 +2,8 @@
 approxtorch/backend/csrc/dummy_module.cpp:6-22, whose only job is to load the operator library).
 
 The library is ``approxtorch_b200/lib/libapproxtorch_b200.so``, built in-tree by
-``python -m approxtorch_b200.build``.  There is no fallback: if it is missing the import fails.
+``python -m approxtorch_b200.build`` (and refreshed here when a source file is newer and nvcc is present).
+There is no fallback: if it is missing the import fails.
 """
 
 from __future__ import annotations
@@ -13,6 +14,17 @@ import os
 _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB_PATH = os.path.join(_PKG, "lib", "libapproxtorch_b200.so")
 
+
+def _refresh_if_stale() -> None:
+    """Rebuild the library when a source is newer than it and a compiler is at hand (a no-op otherwise)."""
+    from ..build import build_library, sources
+    import shutil
+    have_nvcc = os.path.exists("/usr/local/cuda/bin/nvcc") or shutil.which("nvcc") is not None
+    if have_nvcc and sources():
+        build_library()
+
+
+_refresh_if_stale()
 if not os.path.exists(LIB_PATH):
     raise ImportError(
         f"{LIB_PATH} is missing: build the CUDA library first with "
