@@ -50,6 +50,9 @@ _SIGNATURES = {
     "atb_lut_gemm_plan": (_i, [_ll, _i, _i, _i, _i, ctypes.POINTER(GemmPlan)]),
     "atb_lut_bgemm_fwd": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll,
                                _vp, _vp, _vp, _vp, _vp, _i, _vp, _sz, _vp]),
+    "atb_static_scratch_bytes": (_sz, []),
+    "atb_lut_bgemm_fwd_noalloc": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll,
+                                       _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "atb_lut_conv2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp] + [_i] * 13 + [_i]
                            + [_vp] * 5 + [_i, _vp, _sz, _vp]),
     "atb_absmax": (_i, [_vp, _ll, _i, _vp, _vp]),

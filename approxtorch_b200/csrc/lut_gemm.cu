@@ -623,6 +623,62 @@ extern "C" int atb_lut_bgemm_fwd(const uint8_t* x, const uint8_t* w, const void*
     return launch_gemm(a, cfg, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
 }
 
+// ---- entry point for callers that cannot allocate device memory ------------------------------------
+// Split-K partial sums normally go to a caller-supplied scratch buffer.  Some hosts of this library
+// cannot provide one: code running inside a CUDA-graph capture or under a memory pool that forbids new
+// allocations, and bindings from runtimes whose tensors cannot be created from inside an operator call.
+// For them the library carries its own fixed scratch area in device global memory.  It exists once per
+// GPU that loads the library and is held until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[ATB_STATIC_SCRATCH_BYTES];
+
+static int static_scratch_address(void** out)
+{
+    // The symbol name is only a host-side handle: the device address has to be asked for, once per
+    // device, while that device is current.
+    static void* cached[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        set_error("cudaGetDevice: %s", e != cudaSuccess ? cudaGetErrorString(e) : "device index out of range");
+        return ATB_ERR_CUDA;
+    }
+    if (cached[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            set_error("cudaGetSymbolAddress(static scratch): %s", cudaGetErrorString(e));
+            return ATB_ERR_CUDA;
+        }
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return ATB_OK;
+}
+
+extern "C" size_t atb_static_scratch_bytes(void) { return ATB_STATIC_SCRATCH_BYTES; }
+
+extern "C" int atb_lut_bgemm_fwd_noalloc(const uint8_t* x, const uint8_t* w, const void* lut_image, float* y,
+                                         int N, int K, int L, int O, int wb_rows, long long w_batch_stride,
+                                         const float* alpha, const float* beta, const float* zero_x,
+                                         const float* zero_w, const int* wsum, int cfg, void* stream)
+{
+    ATB_REQUIRE(N >= 0 && K >= 0 && L >= 0 && O >= 0, "negative dimension");
+    atb_gemm_plan plan;
+    int rc = make_plan(static_cast<long long>(N) * L, K, O, wb_rows, cfg, &plan, nullptr, nullptr);
+    if (rc != ATB_OK) return rc;
+    if (plan.scratch_bytes > ATB_STATIC_SCRATCH_BYTES) {
+        set_error("this shape needs %zu bytes of split-K scratch but the built-in area holds %zu; "
+                  "use atb_lut_bgemm_fwd with a caller buffer, or force fewer splits through cfg",
+                  plan.scratch_bytes, static_cast<size_t>(ATB_STATIC_SCRATCH_BYTES));
+        return ATB_ERR_SCRATCH;
+    }
+    void* scratch = nullptr;
+    rc = static_scratch_address(&scratch);
+    if (rc != ATB_OK) return rc;
+    return atb_lut_bgemm_fwd(x, w, lut_image, y, N, K, L, O, wb_rows, w_batch_stride, alpha, beta, zero_x, zero_w,
+                             wsum, cfg, scratch, ATB_STATIC_SCRATCH_BYTES, stream);
+}
+
 extern "C" int atb_lut_conv2d_fwd(const void* x, int dtype, const uint8_t* w, const void* lut_image, float* y,
                                   int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw,
                                   int ph, int pw, int dh, int dw, int pad_index,

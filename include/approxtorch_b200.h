@@ -89,6 +89,25 @@ int atb_lut_bgemm_fwd(const uint8_t* x, const uint8_t* w, const void* lut_image,
                       const float* alpha, const float* beta, const float* zero_x, const float* zero_w, const int* wsum,
                       int cfg, void* scratch, size_t scratch_bytes, void* stream);
 
+/* The same batched LUT GEMM for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: its operators allocate their split-K workspace from torch's allocator on every call.)
+ * A host that is capturing a CUDA graph, runs under a closed memory pool, or binds this library from a
+ * runtime that cannot create device buffers inside an operator call has no scratch buffer to hand in, so
+ * this variant keeps the split-K partial sums in a fixed area of ATB_STATIC_SCRATCH_BYTES bytes of device
+ * global memory that is part of the library image: every GPU that loads the library holds it until the
+ * process exits.  Arguments and results are those of atb_lut_bgemm_fwd; shapes whose plan needs more
+ * scratch than the area holds are refused with ATB_ERR_SCRATCH (atb_lut_gemm_plan reports the need, and
+ * cfg can force fewer splits).  The first call on a device looks the area's address up, so make that
+ * call before starting any stream capture.  All calls on a device share the area and it keeps what the
+ * last call left; the kernels overwrite every element they later read, so nothing has to be cleared,
+ * but two such calls that overlap in time on one GPU (different streams) race on it. */
+#define ATB_STATIC_SCRATCH_BYTES (32u << 20)
+size_t atb_static_scratch_bytes(void);
+int atb_lut_bgemm_fwd_noalloc(const uint8_t* x, const uint8_t* w, const void* lut_image, float* y,
+                              int N, int K, int L, int O, int wb_rows, long long w_batch_stride,
+                              const float* alpha, const float* beta, const float* zero_x, const float* zero_w, const int* wsum,
+                              int cfg, void* stream);
+
 /* im2col-free approximate Conv2d forward on the quantised image (int8 values or uint8 indices):
  * the column matrix is never materialised; taps outside the image look up `pad_index`
  * (pad_index == -1: the rounded value of *zero_x, read on the device, so no host copy is needed).

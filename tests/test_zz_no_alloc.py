@@ -1,0 +1,65 @@
+"""The allocation-free LUT-GEMM entry point (split-K partial sums in the library's built-in scratch area)
+must give exactly what the ordinary entry point gives with a caller-supplied scratch buffer.
+
+It serves hosts that cannot allocate device memory at call time (graph capture, closed memory pools,
+foreign-runtime bindings).  Checked through the C ABI on two calls in a row with different data, so that
+whatever the first call left in the shared area cannot leak into the second.  This file sorts last so a
+run that stops at the first failure has already exercised everything else."""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import lut_oracle as lo
+
+pytestmark = pytest.mark.gpu
+
+
+def _call_both(ops, _C, x, w, image, N, K, L, O, cfg):
+    lib = _C.lib
+    plan = _C.GemmPlan()
+    assert lib.atb_lut_gemm_plan(N * L, K, O, 0, cfg, ctypes.byref(plan)) == 0
+    assert plan.splits > 1 and 0 < plan.scratch_bytes <= lib.atb_static_scratch_bytes()
+    stream = ops._stream(x)
+    y_ref = torch.empty((N, O, L), dtype=torch.float32, device=x.device)
+    scratch = torch.empty(plan.scratch_bytes, dtype=torch.uint8, device=x.device)
+    _C.check(lib.atb_lut_bgemm_fwd(ops._ptr(x), ops._ptr(w), ops._ptr(image), ops._ptr(y_ref), N, K, L, O, 0, 0,
+                                   None, None, None, None, None, cfg, ops._ptr(scratch), plan.scratch_bytes, stream),
+             "atb_lut_bgemm_fwd")
+    y_new = torch.full((N, O, L), float("nan"), dtype=torch.float32, device=x.device)
+    _C.check(lib.atb_lut_bgemm_fwd_noalloc(ops._ptr(x), ops._ptr(w), ops._ptr(image), ops._ptr(y_new), N, K, L, O,
+                                           0, 0, None, None, None, None, None, cfg, stream),
+             "atb_lut_bgemm_fwd_noalloc")
+    return y_ref, y_new
+
+
+def test_noalloc_entry_matches_caller_scratch_entry(dev):
+    from approxtorch_b200.backend import ops, _C
+    rng = np.random.default_rng(77)
+    lut = lo.lut_signed_noisy(64, seed=8)
+    image = ops.lut_image(torch.from_numpy(lut.reshape(-1)).to(dev))
+    cfg = (4 << 16) | 128                           # 128-row blocks, 4-way split-K: needs scratch
+    for call, (N, K, L, O) in enumerate([(2, 200, 300, 70), (3, 160, 129, 33)]):
+        x = torch.from_numpy(rng.integers(0, 256, (N, K, L), dtype=np.uint8)).to(dev)
+        w = torch.from_numpy(rng.integers(0, 256, (O, K), dtype=np.uint8)).to(dev)
+        y_ref, y_new = _call_both(ops, _C, x, w, image, N, K, L, O, cfg)
+        torch.cuda.synchronize()
+        assert torch.equal(y_ref, y_new), f"call {call}: outputs differ"
+        oracle = lo.bgemm_exact(x.cpu().numpy(), w.cpu().numpy(), lut)
+        np.testing.assert_array_equal(y_new.cpu().numpy().astype(np.int64), oracle)
+
+
+def test_noalloc_entry_refuses_oversized_shapes(dev):
+    from approxtorch_b200.backend import ops, _C
+    lib = _C.lib
+    limit = lib.atb_static_scratch_bytes()
+    N, K, L, O = 1, 64, 1 << 20, 64                 # 4 splits x 1 Mi rows x 65 x 4 B  >> the built-in area
+    plan = _C.GemmPlan()
+    cfg = (4 << 16) | 512
+    assert lib.atb_lut_gemm_plan(N * L, K, O, 0, cfg, ctypes.byref(plan)) == 0 and plan.scratch_bytes > limit
+    dummy = torch.zeros(16, dtype=torch.uint8, device=dev)
+    rc = lib.atb_lut_bgemm_fwd_noalloc(ops._ptr(dummy), ops._ptr(dummy), ops._ptr(dummy), ops._ptr(dummy), N, K, L, O,
+                                       0, 0, None, None, None, None, None, cfg, ops._stream(dummy))
+    assert rc == 3 and "built-in area" in _C.last_error()
