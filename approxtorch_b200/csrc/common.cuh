@@ -49,6 +49,9 @@ int sm_count();
 // ---------------------------------------------------------------------------------------------
 struct LutImage {
     int flags[4];
+    // tabTP16: transposed and x-permuted, entry (w, x) at w*256 + 2*(x & 127) + (x >> 7), so that the 32-bit
+    // word i of row w holds the pair {x = i (low half), x = i + 128 (high half)}
+    int16_t tabTP16[65536];
     int16_t tabT16[65536];
     int16_t tab16[65536];
     float tabT32[65536];

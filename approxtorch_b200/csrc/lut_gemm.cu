@@ -6,17 +6,23 @@
 // roofline is the shared-memory load pipe (32 four-byte bank reads per clock per SM).  A plain
 // gather from a 128 KB table in shared memory would spend ~3.4 bank wavefronts per 32 lookups on
 // uniformly distributed operands, because 32 data-dependent addresses collide in the 32 banks.
-// The kernel removes those collisions by construction:
+// The kernel removes those collisions by construction and fetches two lookups per load:
 //
-//  * The whole transposed 16-bit table (tabT[w][x], 128 KB) is resident in shared memory.
-//  * For every k-step the block STAGES the 64 table columns its 64 output channels need:
-//    staged row c = tabT[w_idx(c, k)][0..255], copied (conflict-free, 512 contiguous bytes) to a
-//    row pitch of 516 bytes.  516/4 = 129 is odd, so for one activation value x the 32 lanes of a
-//    warp, each owning one staged row, hit 32 different banks: bank = (lane + x/2) mod 32.
-//  * The lookups of the step then read stage[lane][x] with a warp-uniform x (the activation of the
-//    pixel row a warp works on) and lane-dependent rows: one wavefront per 32 lookups.
-//  * Each thread keeps 32 pixel rows x 2 output channels of int32 accumulators in registers, so
+//  * The whole transposed 16-bit table (128 KB) is resident in shared memory, stored so that the 32-bit
+//    word i of row w holds the entries {x = i, x = i + 128}.
+//  * For every k-step the block STAGES the 64 table columns its 64 output channels need as 32 PAIR rows:
+//    pair row p interleaves the columns of output channels p and p + 32, word x = {T[w_p][x], T[w_p+32][x]}.
+//    Building a pair row is two conflict-free word reads, two byte-permutes and two conflict-free word
+//    writes per lane and per 2 x 2 entries (the x-permuted table layout makes both halves land in lanes'
+//    consecutive words).  The pair-row pitch is 257 words (odd), so for one activation value x the 32 lanes
+//    of a warp - one pair row each - hit 32 different banks: bank = (lane + x) mod 32.
+//  * A lookup instruction reads stage[lane][x] with a warp-uniform x (the activation of the pixel row the
+//    warp works on): one wavefront and one instruction per 64 lookups.
+//  * Each thread keeps 32 pixel rows x 2 output channels of exact integer accumulators in registers, so
 //    staging one column (8 wavefronts) is amortised over `block_rows` (up to 512) lookups.
+//  * Entries are unsigned 16-bit (signed tables carry a +32768 bias removed in the epilogue).  A fetched
+//    word v = lo + 65536*hi is accumulated as S0 += v and S1 += hi; the low channel's sum is
+//    S0 - 65536*S1 (exact modulo 2^32, and all sums are below 2^31 for K <= 32768).
 //
 // Integer-valued tables (the int16 / uint16 images) accumulate exactly in int32.  Tables that are
 // not 16-bit exact take the fp32 path: lookups go to the transposed fp32 table in global memory
@@ -33,8 +39,9 @@ namespace atb {
 
 constexpr int kStagedCols = 64;                          // output channels per thread block
 constexpr int kChunk = 16;                               // k-steps per operand tile
-constexpr int kRowPitch = 516;                           // bytes per staged row (256 x int16 + 4 B skew)
-constexpr int kStageBytes = kStagedCols * kRowPitch;     // 33024
+constexpr int kPairRows = kStagedCols / 2;               // staged pair rows per k-step
+constexpr int kPairPitch = 1028;                         // bytes per pair row (256 x 2 x uint16 + 4 B skew)
+constexpr int kStageBytes = kPairRows * kPairPitch;      // 32896
 constexpr int kMaxBlockRows = 512;
 constexpr int kTableBytes = 65536 * 2;
 constexpr int kSmemStage = kTableBytes;
@@ -86,25 +93,25 @@ __device__ __forceinline__ long long output_offset(long long r, int o, const Gem
     return (n * a.O + o) * a.L + l;
 }
 
-// One k-step of staging: every warp copies its share of the 64 table columns into `stage`.
-__device__ __forceinline__ void stage_columns(uint8_t* stage, const uint8_t* s_tab, const uint8_t* wstep,
-                                              int warp, int lane, int nwarps)
+// One k-step of staging: every warp builds its share of the 32 pair rows.
+__device__ __forceinline__ void stage_pairs(uint8_t* stage, const uint8_t* s_tab, const uint8_t* wstep,
+                                            int warp, int lane, int nwarps)
 {
     const uint32_t* tab = reinterpret_cast<const uint32_t*>(s_tab);
-    for (int c = warp; c < kStagedCols; c += nwarps) {
-        const uint32_t* src = tab + static_cast<uint32_t>(wstep[c]) * 128u;
-        uint32_t* dst = reinterpret_cast<uint32_t*>(stage + c * kRowPitch);
-        const uint32_t v0 = src[lane], v1 = src[lane + 32], v2 = src[lane + 64], v3 = src[lane + 96];
-        dst[lane] = v0;
-        dst[lane + 32] = v1;
-        dst[lane + 64] = v2;
-        dst[lane + 96] = v3;
+    for (int p = warp; p < kPairRows; p += nwarps) {
+        const uint32_t* src_a = tab + static_cast<uint32_t>(wstep[p]) * 128u;
+        const uint32_t* src_b = tab + static_cast<uint32_t>(wstep[p + kPairRows]) * 128u;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(stage + p * kPairPitch);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = lane + 32 * j;
+            const uint32_t va = src_a[i], vb = src_b[i];          // {x = i, x = i + 128} of either column
+            dst[i] = __byte_perm(va, vb, 0x5410);                 // x = i:       {A[i], B[i]}
+            dst[i + 128] = __byte_perm(va, vb, 0x7632);           // x = i + 128: {A[i+128], B[i+128]}
+        }
     }
 }
 
-// Lookups of TWO k-steps for this thread's 32 pixel rows x 2 output channels.  Entries are unsigned
-// 16-bit (signed tables are stored with a +32768 bias that the epilogue removes), so the load needs no
-// sign extension, and the two steps' entries of one output are added with a single three-input add.
 template <int TM>
 __device__ __forceinline__ void load_x_words(const uint8_t* xrow, uint32_t (&xw)[TM / 4])
 {
@@ -115,6 +122,8 @@ __device__ __forceinline__ void load_x_words(const uint8_t* xrow, uint32_t (&xw)
     }
 }
 
+// Lookups of TWO k-steps for this thread's TM pixel rows x 2 output channels: per row two word loads
+// (each {low channel, high channel}), one three-input add into S0 and one into S1.
 template <int TM>
 __device__ __forceinline__ void lookup_pair(const uint8_t* stage_a, const uint8_t* stage_b,
                                             const uint8_t* xrow_a, const uint8_t* xrow_b, int lane,
@@ -123,14 +132,14 @@ __device__ __forceinline__ void lookup_pair(const uint8_t* stage_a, const uint8_
     uint32_t xa[TM / 4], xb[TM / 4];
     load_x_words<TM>(xrow_a, xa);
     load_x_words<TM>(xrow_b, xb);
-    const uint16_t* base_a = reinterpret_cast<const uint16_t*>(stage_a + lane * kRowPitch);
-    const uint16_t* base_b = reinterpret_cast<const uint16_t*>(stage_b + lane * kRowPitch);
+    const uint32_t* base_a = reinterpret_cast<const uint32_t*>(stage_a + lane * kPairPitch);
+    const uint32_t* base_b = reinterpret_cast<const uint32_t*>(stage_b + lane * kPairPitch);
 #pragma unroll
     for (int j = 0; j < TM; ++j) {
-        const uint16_t* pa = base_a + __byte_perm(xa[j >> 2], 0, 0x4440 | (j & 3));
-        const uint16_t* pb = base_b + __byte_perm(xb[j >> 2], 0, 0x4440 | (j & 3));
-        acc[j][0] += static_cast<unsigned>(pa[0]) + static_cast<unsigned>(pb[0]);
-        acc[j][1] += static_cast<unsigned>(pa[16 * kRowPitch]) + static_cast<unsigned>(pb[16 * kRowPitch]);
+        const uint32_t va = base_a[__byte_perm(xa[j >> 2], 0, 0x4440 | (j & 3))];
+        const uint32_t vb = base_b[__byte_perm(xb[j >> 2], 0, 0x4440 | (j & 3))];
+        acc[j][0] += va + vb;
+        acc[j][1] += (va >> 16) + (vb >> 16);
     }
 }
 
@@ -140,12 +149,12 @@ __device__ __forceinline__ void lookup_single(const uint8_t* stage_a, const uint
 {
     uint32_t xa[TM / 4];
     load_x_words<TM>(xrow_a, xa);
-    const uint16_t* base_a = reinterpret_cast<const uint16_t*>(stage_a + lane * kRowPitch);
+    const uint32_t* base_a = reinterpret_cast<const uint32_t*>(stage_a + lane * kPairPitch);
 #pragma unroll
     for (int j = 0; j < TM; ++j) {
-        const uint16_t* pa = base_a + __byte_perm(xa[j >> 2], 0, 0x4440 | (j & 3));
-        acc[j][0] += static_cast<unsigned>(pa[0]);
-        acc[j][1] += static_cast<unsigned>(pa[16 * kRowPitch]);
+        const uint32_t va = base_a[__byte_perm(xa[j >> 2], 0, 0x4440 | (j & 3))];
+        acc[j][0] += va;
+        acc[j][1] += va >> 16;
     }
 }
 
@@ -311,8 +320,8 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
             const bool pair = kk + 1 < kc;
             const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * TM;
             const uint8_t* wstep = s_w + (cur * kChunk + kk) * kStagedCols;
-            stage_columns(s_stage, s_tab, wstep, warp, lane, nwarps);
-            if (pair) stage_columns(s_stage + kStageBytes, s_tab, wstep + kStagedCols, warp, lane, nwarps);
+            stage_pairs(s_stage, s_tab, wstep, warp, lane, nwarps);
+            if (pair) stage_pairs(s_stage + kStageBytes, s_tab, wstep + kStagedCols, warp, lane, nwarps);
             if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr, bm);
             __syncthreads();
             if (want_xsum && lane < TM) {
@@ -325,9 +334,14 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
         }
     }
     const long long remove = static_cast<long long>(bias) * (kend - kbeg);     // +32768 per looked-up entry of a signed table
+    // acc[j][0] holds sum(lo) + 65536 * sum(hi) modulo 2^32, acc[j][1] holds sum(hi)
+    auto total = [&](int j, int t) -> long long {
+        const unsigned v = t == 0 ? acc[j][0] - (acc[j][1] << 16) : acc[j][1];
+        return static_cast<long long>(v) - remove;
+    };
     write_tile<TM>(a, r0, r_end, c0, warp, lane, xsum,
-               [&](int j, int t) { return static_cast<double>(static_cast<long long>(acc[j][t]) - remove); },
-               [&](int j, int t) { return static_cast<int>(static_cast<long long>(acc[j][t]) - remove); });
+                   [&](int j, int t) { return static_cast<double>(total(j, t)); },
+                   [&](int j, int t) { return static_cast<int>(total(j, t)); });
 }
 
 // Tables that are not 16-bit exact: lookups from the transposed fp32 table in global memory,
@@ -435,7 +449,7 @@ __global__ void __launch_bounds__(kMaxBlockRows * 32 / TM, 1) lut_gemm_kernel(co
     if (cls != LUT_F32) {
         // signed entries are stored biased (+32768 == flipping bit 15), so every lookup is an unsigned 16-bit load
         const uint32_t flip = (cls == LUT_I16) ? 0x80008000u : 0u;
-        const uint4* src = reinterpret_cast<const uint4*>(a.img->tabT16);
+        const uint4* src = reinterpret_cast<const uint4*>(a.img->tabTP16);
         uint4* dst = reinterpret_cast<uint4*>(smem);
         for (int i = tid; i < kTableBytes / 16; i += blockDim.x) {
             uint4 v = __ldg(src + i);

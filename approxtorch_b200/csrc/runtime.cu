@@ -48,6 +48,8 @@ __global__ void lut_prepare_kernel(const float* __restrict__ lut, LutImage* __re
     img->tab32[i] = v;
     img->tabT16[t] = v16;
     img->tabT32[t] = v;
+    const int xi = i >> 8, wi = i & 255;
+    img->tabTP16[(wi << 8) + ((xi & 127) << 1) + (xi >> 7)] = v16;
 }
 
 }  // namespace atb
