@@ -103,13 +103,13 @@ def quantize_u8(x: Tensor, offset: int) -> Tensor:
 
 
 def _normalise_cfg(cfg: int) -> int:
-    """cfg < 0: automatic.  Otherwise bits 0-15 = pixel rows per block (multiple of 32 in [64, 512]) and
+    """cfg < 0: automatic.  Otherwise bits 0-15 = pixel rows per block (64, 128, 256 or 512; 0 = automatic) and
     bits 16-23 = split-K factor; the reference's tile ids (0..18, 100..118) do not name a tiling of
     this kernel and select the automatic plan."""
     if cfg < 0:
         return -1
     rows = cfg & 0xFFFF
-    if rows != 0 and (rows % 32 != 0 or rows < 64 or rows > 512):
+    if rows not in (0, 64, 128, 256, 512):
         return -1
     return cfg
 

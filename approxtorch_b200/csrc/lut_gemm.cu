@@ -122,39 +122,22 @@ __device__ __forceinline__ void load_x_words(const uint8_t* xrow, uint32_t (&xw)
     }
 }
 
-// Lookups of TWO k-steps for this thread's TM pixel rows x 2 output channels: per row two word loads
-// (each {low channel, high channel}), one three-input add into S0 and one into S1.
-template <int TM>
-__device__ __forceinline__ void lookup_pair(const uint8_t* stage_a, const uint8_t* stage_b,
-                                            const uint8_t* xrow_a, const uint8_t* xrow_b, int lane,
+// Lookups of one k-step for this thread's TM pixel rows x 2 output channels: per row one word load
+// ({low channel, high channel}), S0 += word, S1 += high half (one dot-product-accumulate instruction
+// that multiplies the halves by {0, 1}, or a shift and an add).
+template <int TM, bool DP2A>
+__device__ __forceinline__ void lookup_step(const uint8_t* stage, const uint8_t* xrow, int lane,
                                             unsigned (&acc)[TM][2])
 {
-    uint32_t xa[TM / 4], xb[TM / 4];
-    load_x_words<TM>(xrow_a, xa);
-    load_x_words<TM>(xrow_b, xb);
-    const uint32_t* base_a = reinterpret_cast<const uint32_t*>(stage_a + lane * kPairPitch);
-    const uint32_t* base_b = reinterpret_cast<const uint32_t*>(stage_b + lane * kPairPitch);
+    uint32_t xw[TM / 4];
+    load_x_words<TM>(xrow, xw);
+    const uint32_t* base = reinterpret_cast<const uint32_t*>(stage + lane * kPairPitch);
 #pragma unroll
     for (int j = 0; j < TM; ++j) {
-        const uint32_t va = base_a[__byte_perm(xa[j >> 2], 0, 0x4440 | (j & 3))];
-        const uint32_t vb = base_b[__byte_perm(xb[j >> 2], 0, 0x4440 | (j & 3))];
-        acc[j][0] += va + vb;
-        acc[j][1] += (va >> 16) + (vb >> 16);
-    }
-}
-
-template <int TM>
-__device__ __forceinline__ void lookup_single(const uint8_t* stage_a, const uint8_t* xrow_a, int lane,
-                                              unsigned (&acc)[TM][2])
-{
-    uint32_t xa[TM / 4];
-    load_x_words<TM>(xrow_a, xa);
-    const uint32_t* base_a = reinterpret_cast<const uint32_t*>(stage_a + lane * kPairPitch);
-#pragma unroll
-    for (int j = 0; j < TM; ++j) {
-        const uint32_t va = base_a[__byte_perm(xa[j >> 2], 0, 0x4440 | (j & 3))];
-        acc[j][0] += va;
-        acc[j][1] += va >> 16;
+        const uint32_t v = base[__byte_perm(xw[j >> 2], 0, 0x4440 | (j & 3))];
+        acc[j][0] += v;
+        if constexpr (DP2A) acc[j][1] = __dp2a_lo(v, 0x00000100u, acc[j][1]);
+        else acc[j][1] += v >> 16;
     }
 }
 
@@ -280,23 +263,28 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, long long r0, long
 }
 
 // 16-bit table classes: staged conflict-free lookups, exact integer accumulation.
-// k-steps are processed in pairs: stage both steps' columns, barrier, look both up, barrier.
-template <int TM>
+// Software pipeline per k-step: issue the table reads for the NEXT step's pair rows, do this step's
+// lookups (which hides the latency of those reads), permute and store the next step's pair rows into the
+// other stage buffer, one barrier.
+template <int NW, bool DP2A>
 __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
                                               const uint8_t* wcol, bool vec_x, bool vec_w, int pad, int bias,
                                               long long r0, long long r_end, int c0, int kbeg, int kend)
 {
+    constexpr int TM = 32;
+    constexpr int RPW = kPairRows / NW;          // pair rows each warp stages per k-step
+    constexpr bool kPipelined = RPW <= 2;        // keep the next step's table words in registers across the lookups
     uint8_t* s_tab = smem;
     uint8_t* s_stage = smem + kSmemStage;
     uint8_t* s_x = smem + kSmemX;
     uint8_t* s_w = smem + kSmemW;
+    const uint32_t* tab = reinterpret_cast<const uint32_t*>(s_tab);
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
-    const int nwarps = blockDim.x >> 5;
     const int nch = (kend - kbeg + kChunk - 1) / kChunk;
+    constexpr int bm = NW * TM;
 
-    const int bm = nwarps * TM;
     unsigned acc[TM][2];
 #pragma unroll
     for (int j = 0; j < TM; ++j) { acc[j][0] = 0u; acc[j][1] = 0u; }
@@ -309,27 +297,57 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
         store_chunk(s_x, s_w, 0, tid, xr, wr, bm);
     }
     __syncthreads();          // table image and first operand tile are in shared memory
+    if (nch > 0) {
+        stage_pairs(s_stage, s_tab, s_w, warp, lane, NW);
+        __syncthreads();
+    }
 
+    int step = 0;
     for (int ci = 0; ci < nch; ++ci) {
         const int k0 = kbeg + ci * kChunk;
         const int kc = min(kChunk, kend - k0);
         const int cur = ci & 1;
         const bool has_next = ci + 1 < nch;
         if (has_next) load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr, bm);
-        for (int kk = 0; kk < kc; kk += 2) {
-            const bool pair = kk + 1 < kc;
+        for (int kk = 0; kk < kc; ++kk, ++step) {
+            if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr, bm);
             const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * TM;
             const uint8_t* wstep = s_w + (cur * kChunk + kk) * kStagedCols;
-            stage_pairs(s_stage, s_tab, wstep, warp, lane, nwarps);
-            if (pair) stage_pairs(s_stage + kStageBytes, s_tab, wstep + kStagedCols, warp, lane, nwarps);
-            if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr, bm);
-            __syncthreads();
-            if (want_xsum && lane < TM) {
-                xsum += static_cast<int>(xrow[lane]);
-                if (pair) xsum += static_cast<int>(xrow[kMaxBlockRows + lane]);
+            const uint8_t* wnext = nullptr;
+            if (kk + 1 < kc) wnext = wstep + kStagedCols;
+            else if (has_next) wnext = s_w + ((cur ^ 1) * kChunk) * kStagedCols;
+            uint8_t* stage_next = s_stage + ((step + 1) & 1) * kStageBytes;
+            const uint8_t* stage_cur = s_stage + (step & 1) * kStageBytes;
+            if (want_xsum) xsum += static_cast<int>(xrow[lane]);
+
+            if constexpr (kPipelined) {
+                uint32_t va[RPW][4], vb[RPW][4];
+                if (wnext != nullptr) {
+#pragma unroll
+                    for (int q = 0; q < RPW; ++q) {
+                        const int p = warp + q * NW;
+                        const uint32_t* src_a = tab + static_cast<uint32_t>(wnext[p]) * 128u;
+                        const uint32_t* src_b = tab + static_cast<uint32_t>(wnext[p + kPairRows]) * 128u;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) { va[q][j] = src_a[lane + 32 * j]; vb[q][j] = src_b[lane + 32 * j]; }
+                    }
+                }
+                lookup_step<TM, DP2A>(stage_cur, xrow, lane, acc);
+                if (wnext != nullptr) {
+#pragma unroll
+                    for (int q = 0; q < RPW; ++q) {
+                        uint32_t* dst = reinterpret_cast<uint32_t*>(stage_next + (warp + q * NW) * kPairPitch);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            dst[lane + 32 * j] = __byte_perm(va[q][j], vb[q][j], 0x5410);
+                            dst[lane + 32 * j + 128] = __byte_perm(va[q][j], vb[q][j], 0x7632);
+                        }
+                    }
+                }
+            } else {
+                if (wnext != nullptr) stage_pairs(stage_next, s_tab, wnext, warp, lane, NW);
+                lookup_step<TM, DP2A>(stage_cur, xrow, lane, acc);
             }
-            if (pair) lookup_pair<TM>(s_stage, s_stage + kStageBytes, xrow, xrow + kMaxBlockRows, lane, acc);
-            else lookup_single<TM>(s_stage, xrow, lane, acc);
             __syncthreads();
         }
     }
@@ -391,14 +409,15 @@ __device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, 
                [&](int j, int t) { return __float_as_int(acc[j][t]); });
 }
 
-// TM = pixel rows per warp: 32 (one thread per row loads tiles, 64 accumulators per thread) or 16
-// (twice the warps for the same tile, 32 accumulators per thread).
-template <int TM>
-__global__ void __launch_bounds__(kMaxBlockRows * 32 / TM, 1) lut_gemm_kernel(const GemmArgs a)
+// NW warps per block, 32 pixel rows per warp (one thread per row loads the operand tiles, 64 accumulators
+// per thread).  DP2A selects how the high half of a fetched word is accumulated.
+template <int NW, bool DP2A>
+__global__ void __launch_bounds__(NW * 32, 1) lut_gemm_kernel(const GemmArgs a)
 {
+    constexpr int TM = 32;
     extern __shared__ __align__(16) uint8_t smem[];
     const int tid = threadIdx.x;
-    const int bm = (blockDim.x >> 5) * TM;
+    constexpr int bm = NW * TM;
 
     long long r0, r_end;
     long long wbatch = 0;
@@ -456,7 +475,7 @@ __global__ void __launch_bounds__(kMaxBlockRows * 32 / TM, 1) lut_gemm_kernel(co
             v.x ^= flip; v.y ^= flip; v.z ^= flip; v.w ^= flip;
             dst[i] = v;
         }
-        gemm_body_int<TM>(a, smem, rc, wcol, vec_x, vec_w, pad, cls == LUT_I16 ? 32768 : 0, r0, r_end, c0, kbeg, kend);
+        gemm_body_int<NW, DP2A>(a, smem, rc, wcol, vec_x, vec_w, pad, cls == LUT_I16 ? 32768 : 0, r0, r_end, c0, kbeg, kend);
     } else {
         gemm_body_f32<TM>(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend);
     }
@@ -510,24 +529,11 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
     int bm = 0, splits = 0;
     if (cfg >= 0) { bm = cfg & 0xffff; splits = (cfg >> 16) & 0xff; }
     if (bm != 0) {
-        ATB_REQUIRE(bm % 32 == 0 && bm >= kStagedCols && bm <= kMaxBlockRows, "cfg: block rows must be a multiple of 32 in [64, 512]");
+        ATB_REQUIRE(bm == 64 || bm == 128 || bm == 256 || bm == 512, "cfg: block rows must be 64, 128, 256 or 512");
     } else {
-        long long want = ((span + 31) / 32) * 32;
-        if (want < kStagedCols) want = kStagedCols;     // one thread per staged column loads the weight tile
-        if (want <= kMaxBlockRows) {
-            bm = static_cast<int>(want);
-        } else {
-            // Whole waves of equal tiles: pick the block height whose (waves x per-tile cost) is lowest.
-            // Per-tile cost ~ rows + 256: 2 lookup wavefronts per row plus 512 staging wavefronts per k-step.
-            const long long col_tiles = ceil_div(O > 0 ? O : 1, kStagedCols);
-            long long best_cost = -1;
-            for (int cand = kMaxBlockRows; cand >= 384; cand -= 32) {
-                const long long rt_c = wb_rows > 0 ? (R / wb_rows) * ceil_div(wb_rows, cand) : (R + cand - 1) / cand;
-                const long long waves = (rt_c * col_tiles + sms - 1) / sms;
-                const long long cost = waves * (cand + 256);
-                if (best_cost < 0 || cost < best_cost) { best_cost = cost; bm = cand; }
-            }
-        }
+        // 32 staged pair rows divide evenly over 2, 4, 8 or 16 warps; a warp covers 32 pixel rows
+        bm = 64;
+        while (bm < kMaxBlockRows && bm < span) bm *= 2;
     }
     const int tpb = wb_rows > 0 ? ceil_div(wb_rows, bm) : 0;
     const long long rt = wb_rows > 0 ? (R / (wb_rows > 0 ? wb_rows : 1)) * tpb : (R + bm - 1) / bm;
@@ -553,16 +559,32 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
     return ATB_OK;
 }
 
-static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes, cudaStream_t stream)
+template <int NW, bool DP2A>
+static int launch_one(dim3 grid, const GemmArgs& a, cudaStream_t stream)
 {
-    static bool attr_set = false;
+    static bool attr_set = false;      // the opt-in shared-memory size is a per-function attribute
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(lut_gemm_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(lut_gemm_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+        cudaError_t e = cudaFuncSetAttribute(lut_gemm_kernel<NW, DP2A>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
         attr_set = true;
     }
+    lut_gemm_kernel<NW, DP2A><<<grid, NW * 32, kSmemTotal, stream>>>(a);
+    return ATB_OK;
+}
+
+static int launch_variant(int nwarps, bool dp2a, dim3 grid, const GemmArgs& a, cudaStream_t stream)
+{
+    switch (nwarps) {
+        case 16: return dp2a ? launch_one<16, true>(grid, a, stream) : launch_one<16, false>(grid, a, stream);
+        case 8: return dp2a ? launch_one<8, true>(grid, a, stream) : launch_one<8, false>(grid, a, stream);
+        case 4: return dp2a ? launch_one<4, true>(grid, a, stream) : launch_one<4, false>(grid, a, stream);
+        case 2: return dp2a ? launch_one<2, true>(grid, a, stream) : launch_one<2, false>(grid, a, stream);
+        default: set_error("block rows must be 64, 128, 256 or 512"); return ATB_ERR_INVALID;
+    }
+}
+
+static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes, cudaStream_t stream)
+{
     if (a.R == 0 || a.O == 0) return ATB_OK;
     ATB_REQUIRE(a.K <= 32768, "K above 32768 is not supported (int32 accumulators)");
     ATB_REQUIRE(a.wb_rows == 0 || a.R % a.wb_rows == 0, "rows must be a multiple of wb_rows");
@@ -589,9 +611,9 @@ static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes,
     a.splits = plan.splits;
     a.chunks_per_split = ceil_div(ceil_div(a.K, kChunk), plan.splits);
     dim3 grid(static_cast<unsigned>(row_tiles), static_cast<unsigned>(col_tiles), static_cast<unsigned>(plan.splits));
-    const bool wide = cfg >= 0 && ((cfg >> 24) & 1);        // cfg bit 24: 16 rows per warp, twice the warps
-    if (wide) lut_gemm_kernel<16><<<grid, plan.block_rows * 2, kSmemTotal, stream>>>(a);
-    else lut_gemm_kernel<32><<<grid, plan.block_rows, kSmemTotal, stream>>>(a);
+    const bool shift_add = cfg >= 0 && ((cfg >> 24) & 1);      // cfg bit 24: accumulate high halves with shift + add
+    rc = launch_variant(plan.block_rows / 32, !shift_add, grid, a, stream);
+    if (rc != ATB_OK) return rc;
     rc = check_launch("lut_gemm_kernel");
     if (rc != ATB_OK) return rc;
     if (plan.splits > 1) {

@@ -71,7 +71,7 @@ int atb_im2col_u8(const void* x, int dtype, int N, int C, int H, int W, int kh, 
  *
  * The plan says how the launch will be tiled and how much scratch (bytes) a split-K launch needs. */
 typedef struct {
-    int block_rows;      /* pixel rows per thread block (a multiple of 32 in [64, 512]) */
+    int block_rows;      /* pixel rows per thread block: 64, 128, 256 or 512 */
     int splits;          /* split-K factor; > 1 needs scratch */
     size_t scratch_bytes;
 } atb_gemm_plan;

@@ -58,8 +58,8 @@ def test_shape_sweep_against_oracle(dev, shape):
     np.testing.assert_array_equal(wq.cpu().numpy(), lo.to_lut_index(w, 128))
 
 
-@pytest.mark.parametrize("cfg", [-1, 0, 7, 100, 32, 64, 128, 256, 480, 512, (3 << 16) | 128, (2 << 16) | 512,
-                                 (5 << 16)])
+@pytest.mark.parametrize("cfg", [-1, 0, 7, 100, 64, 128, 256, 512, (3 << 16) | 128, (2 << 16) | 512, (5 << 16),
+                                 (1 << 24) | 256, (1 << 24) | (2 << 16) | 64])
 def test_forced_tilings_and_split_k_are_bit_identical(dev, cfg):
     ops = _ops()
     rng = np.random.default_rng(5)
