@@ -239,26 +239,56 @@ __device__ __forceinline__ void store_chunk(uint8_t* s_x, uint8_t* s_w, int buf,
 }
 
 // Epilogue shared by both paths: `total(j, t)` yields the finished sum of row j, column slot t.
+// Thread (warp, lane) holds pixel rows warp*32 + j (j = 0..31) of output channels lane and lane + 32.
+// Split-K partials and the L == 1 layout are written directly (lanes span consecutive channels, which is
+// the fast axis there).  For L > 1 the fast axis of y[n, o, l] is the pixel, so each warp first turns its
+// 32 x 64 tile around in shared memory (the table / stage area is free by now) and then stores 128
+// contiguous bytes per channel.
 template <int TM, class Total, class Bits>
-__device__ __forceinline__ void write_tile(const GemmArgs& a, long long r0, long long r_end, int c0, int warp, int lane,
-                                           int xsum, Total total, Bits bits)
+__device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, long long r0, long long r_end, int c0,
+                                           int warp, int lane, int xsum, Total total, Bits bits)
 {
+    static_assert(TM == 32, "the transposed epilogue maps lanes to the warp's 32 pixel rows");
     const int split = blockIdx.z;
     const bool want_xsum = a.zero_x != nullptr;
+    if (a.splits > 1 || a.L == 1) {
+#pragma unroll
+        for (int j = 0; j < TM; ++j) {
+            const long long r = r0 + warp * TM + j;
+            const int xs = __shfl_sync(0xffffffffu, xsum, j);
+            if (r >= r_end) continue;
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+                const int o = c0 + lane + 32 * t;
+                if (o >= a.O) continue;
+                if (a.splits > 1) a.scratch[(static_cast<long long>(split) * a.R + r) * a.O + o] = bits(j, t);
+                else a.y[output_offset(r, o, a)] = finalize_output(total(j, t), xs, o, a);
+            }
+            if (a.splits > 1 && want_xsum && blockIdx.y == 0 && lane == 0)
+                a.scratch[static_cast<long long>(a.splits) * a.R * a.O + static_cast<long long>(split) * a.R + r] = xs;
+        }
+        return;
+    }
+    __syncthreads();                                   // every warp has left the main loop
+    constexpr int kPitch = 33;                         // words per channel row of the turned tile
+    float* tile = reinterpret_cast<float*>(smem) + warp * (kStagedCols * kPitch);
 #pragma unroll
     for (int j = 0; j < TM; ++j) {
-        const long long r = r0 + warp * TM + j;
         const int xs = __shfl_sync(0xffffffffu, xsum, j);
-        if (r >= r_end) continue;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
             const int o = c0 + lane + 32 * t;
-            if (o >= a.O) continue;
-            if (a.splits > 1) a.scratch[(static_cast<long long>(split) * a.R + r) * a.O + o] = bits(j, t);
-            else a.y[output_offset(r, o, a)] = finalize_output(total(j, t), xs, o, a);
+            tile[(lane + 32 * t) * kPitch + j] = (o < a.O) ? finalize_output(total(j, t), xs, o, a) : 0.0f;
         }
-        if (a.splits > 1 && want_xsum && blockIdx.y == 0 && lane == 0)
-            a.scratch[static_cast<long long>(a.splits) * a.R * a.O + static_cast<long long>(split) * a.R + r] = xs;
+    }
+    __syncwarp();
+    const long long r = r0 + warp * TM + lane;         // this lane's pixel row
+    if (r < r_end) {
+        const long long n = r / a.L;
+        const long long l = r - n * a.L;
+        float* dst = a.y + (n * a.O + c0) * a.L + l;
+        const int ncols = min(kStagedCols, a.O - c0);
+        for (int c = 0; c < ncols; ++c) dst[static_cast<long long>(c) * a.L] = tile[c * kPitch + lane];
     }
 }
 
@@ -357,7 +387,7 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
         const unsigned v = t == 0 ? acc[j][0] - (acc[j][1] << 16) : acc[j][1];
         return static_cast<long long>(v) - remove;
     };
-    write_tile<TM>(a, r0, r_end, c0, warp, lane, xsum,
+    write_tile<TM>(a, smem, r0, r_end, c0, warp, lane, xsum,
                    [&](int j, int t) { return static_cast<double>(total(j, t)); },
                    [&](int j, int t) { return static_cast<int>(total(j, t)); });
 }
@@ -404,7 +434,7 @@ __device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, 
         }
         __syncthreads();
     }
-    write_tile<TM>(a, r0, r_end, c0, warp, lane, xsum,
+    write_tile<TM>(a, smem, r0, r_end, c0, warp, lane, xsum,
                [&](int j, int t) { return static_cast<double>(acc[j][t]); },
                [&](int j, int t) { return __float_as_int(acc[j][t]); });
 }
@@ -540,12 +570,21 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
     const long long tiles = rt * ceil_div(O > 0 ? O : 1, kStagedCols);
     const int nchunks = K > 0 ? ceil_div(K, kChunk) : 1;
     if (splits == 0) {
+        // Split-K is chosen from whole waves of `sms` equal blocks: time ~ ceil(tiles * S / sms) / S tile
+        // times, with a few percent per extra split for the reduction pass and the repeated prologues.
+        // Grids that already fill the GPU only split for a modelled gain of 10 % or more (the partial sums
+        // need S times the output in scratch).
         splits = 1;
-        if (tiles > 0 && tiles < sms && nchunks > 1) {
-            long long s = (sms + tiles - 1) / tiles;
-            if (s > 32) s = 32;
-            if (s > nchunks) s = nchunks;
-            splits = static_cast<int>(s);
+        if (tiles > 0 && tiles < 4LL * sms && nchunks > 1) {
+            const double base = static_cast<double>((tiles + sms - 1) / sms);
+            double best = base;
+            int best_s = 1;
+            for (int s = 2; s <= 16 && s <= nchunks; ++s) {
+                const double waves = static_cast<double>((tiles * s + sms - 1) / sms) / s;
+                const double cost = waves * (1.0 + 0.03 * (s - 1));
+                if (cost < best - 1e-9) { best = cost; best_s = s; }
+            }
+            if (tiles < sms || best <= 0.9 * base) splits = best_s;
         }
     }
     if (splits > nchunks) splits = nchunks;

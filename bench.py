@@ -156,6 +156,70 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# ----------------------------------------------------------------------------------------------- ResNet legs
+def build_resnet50_uint8(dev, calib_images=8):
+    """torchvision ResNet-50, random init, every conv but the first swapped for the unsigned approximate layer
+    (table = exact unsigned product with the low 6 bits cleared), scales frozen after one calibration pass."""
+    import torch
+    import torchvision
+    import approxtorch_b200 as at
+    from oracle import lut_oracle as lo
+    torch.manual_seed(0)
+    model = torchvision.models.resnet50()
+    lut = torch.from_numpy(lo.lut_unsigned_truncated(6).reshape(-1)).to(dev)
+    at.convert_model(model, lut, qtype="uint8", update_scale=True, scale_momentum=1.0)
+    model = model.to(dev).train()
+    with torch.no_grad():
+        model(torch.randn(calib_images, 3, 224, 224, device=dev))        # momentum 1: ranges := this batch's min/max
+    model.eval()
+    for m in model.modules():
+        if isinstance(m, at.nn.Conv2d_uint8):
+            m.freeze_scale()
+    return model
+
+
+def resnet50_inference_leg(dev, world, rank, steps, total_batch=128):
+    """img/s of ResNet-50 approximate-conv inference, the batch of 128 split evenly over the ranks;
+    device-resident and end-to-end (pinned host images in, logits out)."""
+    import torch
+    import torch.distributed as dist
+    per_rank = max(1, total_batch // world)
+    model = build_resnet50_uint8(dev)
+    g = torch.Generator().manual_seed(1 + rank)
+    x_host = torch.randn(per_rank, 3, 224, 224, generator=g).pin_memory()
+    x_dev = x_host.to(dev)
+    out_host = torch.empty(per_rank, 1000).pin_memory()
+    res = {}
+    with torch.no_grad():
+        for name in ("resident", "e2e"):
+            def once():
+                if name == "resident":
+                    return model(x_dev)
+                y = model(x_host.to(dev, non_blocking=True))
+                out_host.copy_(y, non_blocking=True)
+                return y
+            for _ in range(2):
+                once()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(steps):
+                once()
+            t1.record()
+            torch.cuda.synchronize()
+            ms = torch.tensor([t0.elapsed_time(t1) / steps], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            res[name] = per_rank * world / (ms.item() * 1e-3)
+    del model
+    torch.cuda.empty_cache()
+    return {"resnet50_uint8_infer_img_s": res["resident"], "resnet50_uint8_infer_img_s_e2e": res["e2e"],
+            "resnet50_batch_per_gpu": per_rank, "resnet50_lut_macs_per_img": 3.969e9,
+            "resnet50_lut_mac_s_per_gpu": res["resident"] * 3.969e9 / world}
+
+
 # ----------------------------------------------------------------------------------------------- GPU arm
 def run_gpu_arm(args):
     import torch
@@ -241,12 +305,32 @@ def run_gpu_arm(args):
     a_in = torch.empty_like(a_dev)
     b_in = torch.empty_like(b_dev)
 
+    copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
     def step_e2e():
-        a_in.copy_(a_host, non_blocking=True)
-        b_in.copy_(b_host, non_blocking=True)
+        """All 16 items through the public operator; H2D of item i+1 and D2H of item i-1 overlap the compute of
+        item i (three streams, events between them).  Everything is joined back into the current stream."""
+        main = torch.cuda.current_stream(dev)
+        copy_in.wait_stream(main)
+        copy_out.wait_stream(main)
+        ready = []
+        with torch.cuda.stream(copy_in):
+            for i in range(BATCH):
+                a_in[i].copy_(a_host[i], non_blocking=True)
+                b_in[i].copy_(b_host[i], non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(copy_in)
+                ready.append(ev_in)
         for i in range(BATCH):
+            main.wait_event(ready[i])
             yi = ops.gemm_fake_int8_claude(a_in[i], b_in[i], lut)        # the reference's public operator
-            y_host[i].copy_(yi, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(main)
+            copy_out.wait_event(done)
+            with torch.cuda.stream(copy_out):
+                y_host[i].copy_(yi, non_blocking=True)
+            yi.record_stream(copy_out)
+        main.wait_stream(copy_out)
     for _ in range(2):
         step_e2e()
     barrier()
@@ -265,6 +349,13 @@ def run_gpu_arm(args):
     if world > 1:
         dist.all_reduce(e2e_total, op=dist.ReduceOp.MAX)
     e2e_value = world * MACS_PER_STEP / (e2e_total.item() / args.steps * 1e-3)
+
+    extra = {}
+    if not args.no_models:
+        try:
+            extra = resnet50_inference_leg(dev, world, rank, steps=3)
+        except Exception as exc:                 # the model leg must never hide the headline number
+            extra = {"resnet50_error": f"{type(exc).__name__}: {exc}"[:200]}
 
     if rank == 0:
         peaks = {}
@@ -302,6 +393,7 @@ def run_gpu_arm(args):
                                  "peak_gbs": hbm_peak, "frac": alg_bytes / gemm_s / 1e9 / hbm_peak,
                                  "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"}},
             "cpu_baseline": cpu,
+            "extra": extra,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -314,6 +406,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-models", action="store_true", help="skip the ResNet-50 inference leg reported under extra")
     ap.add_argument("--cfg", type=int, default=-1, help="tiling override passed to the LUT-GEMM launch (-1: automatic)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="run only warm-up + timed device-resident steps (no L2 flush, no end-to-end or CPU leg): "
