@@ -371,7 +371,7 @@ def run_gpu_arm(args):
         run_mhz = clocks.get("sm_mhz")
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
         alg_bytes = a_np.nbytes + BATCH * NCOL * K + y.numel() * 4
-        cpu, _ = cpu_baseline(a_np, b_np, lut_np)
+        cpu = cpu_baseline(a_np, b_np, lut_np)[0] if world == 1 else None     # the CPU leg is a single-GPU-run item
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
