@@ -106,6 +106,29 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def gpu_reference_leg(a, b, lut):
+    """Throughput of the reference's own CUDA operators (rebuilt for sm_100a into oracle/_ref/gpu) on the same
+    workload and box, timed by the reference's protocol in a process of its own; None when they were not built."""
+    import tempfile
+    from oracle import build_ref_gpu
+    if build_ref_gpu.built_library() is None:
+        return None
+    with tempfile.TemporaryDirectory() as d:
+        req, rep = os.path.join(d, "req.npz"), os.path.join(d, "rep.npz")
+        np.savez(req, op=np.array("bench_bgemm16"), arg0=a, arg1=b, arg2=lut)
+        proc = subprocess.run([sys.executable, os.path.join(REPO, "oracle", "ref_gpu_worker.py"), req, rep],
+                              capture_output=True, text=True, timeout=900)
+        if proc.returncode != 0 or not os.path.exists(rep):
+            return {"error": proc.stderr[-300:]}
+        out = np.load(rep, allow_pickle=False)
+        if "error" in out:
+            return {"error": str(out["error"])}
+        ms = float(out["ms_per_step"])
+    return {"value": MACS_PER_STEP / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms,
+            "kind": "reference CUDA operators (gemm_fake_int8_forward_cuda_claude x16) rebuilt for sm_100a, same box",
+            "protocol": "5 warm-up + 30 timed iterations between CUDA events, device-resident operands"}
+
+
 # ----------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -388,11 +411,15 @@ def run_gpu_arm(args):
                          "peak_note": f"{sms} SMs x 32 shared-memory bank reads/clk x {max_mhz:.0f} MHz (max SM clock); "
                                       "1 lookup per LUT-MAC",
                          "frac_at_sampled_clock": (achieved / (sms * 32 * run_mhz * 1e6)) if run_mhz else None,
-                         "kernel_ms": gemm_s * 1e3, "traffic": None,
+                         "kernel_ms": gemm_s * 1e3,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
+                         # workload, from the ncu capture summarised under profiles/ (bytes per launch)
+                         "traffic": 70.6e6,
                          "hbm": {"algorithmic_bytes": int(alg_bytes), "achieved_gbs": alg_bytes / gemm_s / 1e9,
                                  "peak_gbs": hbm_peak, "frac": alg_bytes / gemm_s / 1e9 / hbm_peak,
                                  "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"}},
             "cpu_baseline": cpu,
+            "gpu_reference": gpu_reference_leg(a_np, b_np, lut_np) if world == 1 and not args.no_models else None,
             "extra": extra,
         }
         print(json.dumps(line), flush=True)
