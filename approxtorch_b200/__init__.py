@@ -2,7 +2,7 @@
 
 Public surface (same names as the reference package, approxtorch/__init__.py:11-21):
 ``convert_model``, ``nn`` (Conv2d_int8, Conv2d_uint8, the autograd Functions, quantization),
-``backend.ops`` (``torch.ops.approxtorch.*``), ``load_lut``, ``grad_lut``.
+``backend.ops`` (``torch.ops.approxtorch.*``), ``load_lut``, ``grad_lut``, ``calib``.
 ``install_as_approxtorch()`` makes ``import approxtorch`` resolve to this package.
 """
 
@@ -11,6 +11,7 @@ from . import nn
 from .convert_model import convert_model
 from . import load_lut
 from . import grad_lut
+from . import calib
 
 __version__ = "0.1.0"
 
@@ -24,6 +25,6 @@ def install_as_approxtorch() -> None:
     if other is not None and other is not me:
         raise RuntimeError("a different 'approxtorch' package is already imported")
     sys.modules["approxtorch"] = me
-    for sub in ("backend", "nn", "convert_model", "load_lut", "grad_lut"):
+    for sub in ("backend", "nn", "convert_model", "load_lut", "grad_lut", "calib"):
         sys.modules["approxtorch." + sub] = sys.modules[__name__ + "." + sub]
     sys.modules["approxtorch.backend.ops"] = sys.modules[__name__ + ".backend.ops"]

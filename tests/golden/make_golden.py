@@ -243,7 +243,38 @@ def golden_setup():
     save("setup", **out)
 
 
+# ---------------------------------------------------------------- calibration tool
+def calib_model():
+    torch.manual_seed(0)
+    return torch.nn.Sequential(torch.nn.Conv2d(3, 4, 3, padding=1), torch.nn.ReLU(), torch.nn.Conv2d(4, 6, 3, padding=1),
+                               torch.nn.BatchNorm2d(6), torch.nn.Conv2d(6, 5, 1, bias=False))
+
+
+def golden_calib():
+    import contextlib
+    import io
+    g = torch.Generator().manual_seed(1)
+    data = [torch.randn(4, 3, 8, 8, generator=g) for _ in range(3)]
+    out = {"data": np.stack([t2n(d) for d in data])}
+    with tempfile.TemporaryDirectory() as d, contextlib.redirect_stdout(io.StringIO()):
+        for bits in (8, 4):
+            sd = ref_at.calib.calibrate_int8(calib_model(), [(x, 0) for x in data], 10, os.path.join(d, "c.pt"), weight_bits=bits)
+            out[f"i8_{bits}_keys"] = np.array(list(sd.keys()))
+            for k, v in sd.items():
+                if k.endswith(("scale_x", "scale_w")):
+                    out[f"i8_{bits}_{k}"] = t2n(v)
+        for n in (None, 7):
+            sd = ref_at.calib.calibrate_uint8(calib_model(), data, n)
+            tag = "all" if n is None else str(n)
+            out[f"u8_{tag}_keys"] = np.array(list(sd.keys()))
+            for k, v in sd.items():
+                if k.rsplit(".", 1)[-1] in ("x_min", "x_max", "w_min", "w_max", "scale_x", "zero_x", "scale_w", "zero_w"):
+                    out[f"u8_{tag}_{k}"] = t2n(v)
+    save("calib", **out)
+
+
 if __name__ == "__main__":
+    golden_calib()
     golden_fakequant()
     golden_stats()
     golden_bgemm()

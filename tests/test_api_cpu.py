@@ -228,3 +228,39 @@ def test_install_as_approxtorch_alias():
         for k in [k for k in sys.modules if k == "approxtorch" or k.startswith("approxtorch.")]:
             del sys.modules[k]
         sys.modules.update(saved)
+
+
+def test_calibration_matches_reference_fixture(golden, tmp_path):
+    """calibrate_int8 / calibrate_uint8 on a small float model against the checkpoints the reference's own
+    calibration tool produced for the same model and batches (key order included)."""
+    g = golden("calib")
+
+    def model():
+        torch.manual_seed(0)
+        return nn.Sequential(nn.Conv2d(3, 4, 3, padding=1), nn.ReLU(), nn.Conv2d(4, 6, 3, padding=1),
+                             nn.BatchNorm2d(6), nn.Conv2d(6, 5, 1, bias=False))
+    data = [torch.from_numpy(d) for d in g["data"]]
+    for bits in (8, 4):
+        sd = at.calib.calibrate_int8(model(), [(x, 0) for x in data], 10, str(tmp_path / "c.pt"), weight_bits=bits)
+        assert list(sd.keys()) == list(g[f"i8_{bits}_keys"])
+        for k, v in sd.items():
+            if k.endswith(("scale_x", "scale_w")):
+                np.testing.assert_array_equal(v.numpy(), g[f"i8_{bits}_{k}"])
+        assert torch.load(tmp_path / "c.pt").keys() == sd.keys()
+    for n, tag in ((None, "all"), (7, "7")):
+        m = model().train()
+        sd = at.calib.calibrate_uint8(m, data, n)
+        assert m.training                                    # train / eval flags are restored
+        assert list(sd.keys()) == list(g[f"u8_{tag}_keys"])
+        for k, v in sd.items():
+            if k.rsplit(".", 1)[-1] in ("x_min", "x_max", "w_min", "w_max", "scale_x", "zero_x", "scale_w", "zero_w"):
+                np.testing.assert_array_equal(v.numpy(), g[f"u8_{tag}_{k}"])
+    # the uint8 checkpoint loads straight into a converted model
+    lut = torch.zeros(65536)
+    conv = convert_model(model(), lut, qtype="uint8")
+    res = conv.load_state_dict(at.calib.calibrate_uint8(model(), data, None), strict=False)
+    assert not res.unexpected_keys and all(k.endswith("lut") for k in res.missing_keys)
+    with pytest.raises(ValueError):
+        at.calib.calibrate_uint8(nn.Sequential(nn.Conv2d(1, 1, 1)), data, None)
+    with pytest.raises(TypeError):
+        at.calib.calibrate_uint8(model(), data, True)
