@@ -54,7 +54,9 @@ struct GemmArgs {
     const uint8_t* w;
     const LutImage* img;
     float* y;
-    int* scratch;          // split-K partials [S][R][O] followed by row sums [S][R]
+    int* scratch;          // split-K partials [S][srows][O] followed by row sums [S][srows]
+    long long srow0, srows;   // pixel rows the split-K scratch covers: [srow0, srow0 + srows)
+    int tile0;             // first row tile of this launch (added to blockIdx.x)
     long long R;           // pixel rows
     int K, L, O;
     int wb_rows;           // pixel rows per weight matrix (0: one matrix for all rows)
@@ -261,11 +263,11 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
             for (int t = 0; t < 2; ++t) {
                 const int o = c0 + lane + 32 * t;
                 if (o >= a.O) continue;
-                if (a.splits > 1) a.scratch[(static_cast<long long>(split) * a.R + r) * a.O + o] = bits(j, t);
+                if (a.splits > 1) a.scratch[(static_cast<long long>(split) * a.srows + (r - a.srow0)) * a.O + o] = bits(j, t);
                 else a.y[output_offset(r, o, a)] = finalize_output(total(j, t), xs, o, a);
             }
             if (a.splits > 1 && want_xsum && blockIdx.y == 0 && lane == 0)
-                a.scratch[static_cast<long long>(a.splits) * a.R * a.O + static_cast<long long>(split) * a.R + r] = xs;
+                a.scratch[static_cast<long long>(a.splits) * a.srows * a.O + static_cast<long long>(split) * a.srows + (r - a.srow0)] = xs;
         }
         return;
     }
@@ -451,13 +453,14 @@ __global__ void __launch_bounds__(NW * 32, 1) lut_gemm_kernel(const GemmArgs a)
 
     long long r0, r_end;
     long long wbatch = 0;
+    const int row_tile = a.tile0 + static_cast<int>(blockIdx.x);
     if (a.wb_rows > 0) {
-        wbatch = blockIdx.x / a.tiles_per_batch;
-        const int t = blockIdx.x - static_cast<int>(wbatch) * a.tiles_per_batch;
+        wbatch = row_tile / a.tiles_per_batch;
+        const int t = row_tile - static_cast<int>(wbatch) * a.tiles_per_batch;
         r0 = wbatch * a.wb_rows + static_cast<long long>(t) * bm;
         r_end = min(a.R, (wbatch + 1) * a.wb_rows);
     } else {
-        r0 = static_cast<long long>(blockIdx.x) * bm;
+        r0 = static_cast<long long>(row_tile) * bm;
         r_end = a.R;
     }
     const int c0 = blockIdx.y * kStagedCols;
@@ -511,15 +514,15 @@ __global__ void __launch_bounds__(NW * 32, 1) lut_gemm_kernel(const GemmArgs a)
     }
 }
 
-// Split-K: y = finalize(sum_s partial[s]) in ascending split order.
+// Split-K: y = finalize(sum_s partial[s]) in ascending split order, over the rows the scratch covers.
 __global__ void lut_gemm_reduce_kernel(const GemmArgs a)
 {
-    const long long total = a.R * a.O;
+    const long long total = a.srows * a.O;
     const int cls = lut_class_of(a.img);
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const long long r = i / a.O;
-        const int o = static_cast<int>(i - r * a.O);
+        const long long rs = i / a.O;
+        const int o = static_cast<int>(i - rs * a.O);
         double sum = 0.0;
         if (cls == LUT_F32) {
             float f = 0.0f;
@@ -532,8 +535,8 @@ __global__ void lut_gemm_reduce_kernel(const GemmArgs a)
         }
         long long xs = 0;
         if (a.zero_x != nullptr)
-            for (int s = 0; s < a.splits; ++s) xs += a.scratch[a.splits * total + static_cast<long long>(s) * a.R + r];
-        a.y[output_offset(r, o, a)] = finalize_output(sum, xs, o, a);
+            for (int s = 0; s < a.splits; ++s) xs += a.scratch[a.splits * total + static_cast<long long>(s) * a.srows + rs];
+        a.y[output_offset(a.srow0 + rs, o, a)] = finalize_output(sum, xs, o, a);
     }
 }
 
@@ -549,6 +552,22 @@ __global__ void lut_gemm_empty_k_kernel(const GemmArgs a)
     }
 }
 
+// First pixel row of row tile t.
+static long long tile_first_row(long long t, int bm, int wb_rows, int tiles_per_batch)
+{
+    if (wb_rows > 0) return (t / tiles_per_batch) * wb_rows + (t % tiles_per_batch) * static_cast<long long>(bm);
+    return t * bm;
+}
+
+// Modelled duration of `blocks` equal thread blocks of `ksteps` k-steps each, in k-step units: whole waves
+// of `sms` blocks, each paying a fixed prologue (table image into shared memory, first operand tile) and
+// epilogue worth about a dozen k-steps.
+static double wave_cost(long long blocks, int ksteps, int sms)
+{
+    constexpr double kFixed = 12.0;
+    return static_cast<double>((blocks + sms - 1) / sms) * (ksteps + kFixed);
+}
+
 static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_plan* p,
                      int* tiles_per_batch, long long* row_tiles)
 {
@@ -557,7 +576,8 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
     const int sms = sm_count();
     const long long span = wb_rows > 0 ? wb_rows : R;
     int bm = 0, splits = 0;
-    if (cfg >= 0) { bm = cfg & 0xffff; splits = (cfg >> 16) & 0xff; }
+    bool allow_tail = true;
+    if (cfg >= 0) { bm = cfg & 0xffff; splits = (cfg >> 16) & 0xff; allow_tail = ((cfg >> 25) & 1) == 0; }
     if (bm != 0) {
         ATB_REQUIRE(bm == 64 || bm == 128 || bm == 256 || bm == 512, "cfg: block rows must be 64, 128, 256 or 512");
     } else {
@@ -567,15 +587,37 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
     }
     const int tpb = wb_rows > 0 ? ceil_div(wb_rows, bm) : 0;
     const long long rt = wb_rows > 0 ? (R / (wb_rows > 0 ? wb_rows : 1)) * tpb : (R + bm - 1) / bm;
-    const long long tiles = rt * ceil_div(O > 0 ? O : 1, kStagedCols);
+    const int ct = ceil_div(O > 0 ? O : 1, kStagedCols);
+    const long long tiles = rt * ct;
     const int nchunks = K > 0 ? ceil_div(K, kChunk) : 1;
+    long long tail_rt = 0;
     if (splits == 0) {
-        // Split-K is chosen from whole waves of `sms` equal blocks: time ~ ceil(tiles * S / sms) / S tile
-        // times, with a few percent per extra split for the reduction pass and the repeated prologues.
-        // Grids that already fill the GPU only split for a modelled gain of 10 % or more (the partial sums
-        // need S times the output in scratch).
         splits = 1;
-        if (tiles > 0 && tiles < 4LL * sms && nchunks > 1) {
+        // (1) Grids of more than one wave whose last wave is ragged: the whole waves run unsplit, and only
+        // the trailing row tiles are split along K so that they fill one more (shorter) wave.  Their partial
+        // sums are the only ones that go through scratch.
+        if (allow_tail && tiles > sms && tiles % sms != 0 && nchunks > 1) {
+            const long long full = tiles / sms;
+            const long long main_rt = (full * sms) / ct;
+            const long long t_rt = rt - main_rt;
+            if (main_rt > 0 && t_rt > 0) {
+                const double base = wave_cost(tiles, K, sms);
+                double best = base;
+                int best_s = 1;
+                for (int s = 2; s <= 16 && s <= nchunks; ++s) {
+                    const int cps = ceil_div(nchunks, s);
+                    const int s_eff = ceil_div(nchunks, cps);
+                    const double cost = wave_cost(main_rt * ct, K, sms) + wave_cost(t_rt * ct * s_eff, cps * kChunk, sms) + 6.0;
+                    if (cost < best - 1e-9) { best = cost; best_s = s; }
+                }
+                if (best_s > 1 && best <= 0.95 * base) { splits = best_s; tail_rt = t_rt; }
+            }
+        }
+        // (2) Otherwise split-K over all tiles, chosen from whole waves of `sms` equal blocks: time ~
+        // ceil(tiles * S / sms) / S tile times, with a few percent per extra split for the reduction pass and
+        // the repeated prologues.  Grids that already fill the GPU only split for a modelled gain of 10 % or
+        // more (the partial sums need S times the output in scratch).
+        if (tail_rt == 0 && tiles > 0 && tiles < 4LL * sms && nchunks > 1) {
             const double base = static_cast<double>((tiles + sms - 1) / sms);
             double best = base;
             int best_s = 1;
@@ -590,9 +632,12 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
     if (splits > nchunks) splits = nchunks;
     const int cps = ceil_div(nchunks, splits);
     splits = ceil_div(nchunks, cps);
+    if (splits == 1) tail_rt = 0;
+    const long long srow0 = tail_rt > 0 ? tile_first_row(rt - tail_rt, bm, wb_rows, tpb) : 0;
     p->block_rows = bm;
     p->splits = splits;
-    p->scratch_bytes = splits > 1 ? static_cast<size_t>(splits) * static_cast<size_t>(R) * (static_cast<size_t>(O) + 1) * 4u : 0u;
+    p->scratch_bytes = splits > 1 ? static_cast<size_t>(splits) * static_cast<size_t>(R - srow0) * (static_cast<size_t>(O) + 1) * 4u : 0u;
+    p->tail_row_tiles = static_cast<int>(tail_rt);
     if (tiles_per_batch) *tiles_per_batch = tpb;
     if (row_tiles) *row_tiles = rt;
     return ATB_OK;
@@ -647,16 +692,33 @@ static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes,
     }
     a.scratch = static_cast<int*>(scratch);
     a.tiles_per_batch = tpb;
-    a.splits = plan.splits;
-    a.chunks_per_split = ceil_div(ceil_div(a.K, kChunk), plan.splits);
-    dim3 grid(static_cast<unsigned>(row_tiles), static_cast<unsigned>(col_tiles), static_cast<unsigned>(plan.splits));
     const bool shift_add = cfg >= 0 && ((cfg >> 24) & 1);      // cfg bit 24: accumulate high halves with shift + add
+    const int nchunks = ceil_div(a.K, kChunk);
+    const long long tail_rt = plan.tail_row_tiles;
+    const long long main_rt = row_tiles - tail_rt;
+    if (tail_rt > 0) {
+        // whole waves, unsplit
+        a.tile0 = 0; a.splits = 1; a.chunks_per_split = nchunks; a.srow0 = 0; a.srows = a.R;
+        dim3 grid(static_cast<unsigned>(main_rt), static_cast<unsigned>(col_tiles), 1u);
+        rc = launch_variant(plan.block_rows / 32, !shift_add, grid, a, stream);
+        if (rc != ATB_OK) return rc;
+        rc = check_launch("lut_gemm_kernel");
+        if (rc != ATB_OK) return rc;
+    }
+    // the split-K part: every tile, or only the trailing row tiles
+    a.tile0 = static_cast<int>(main_rt) * (tail_rt > 0 ? 1 : 0);
+    a.splits = plan.splits;
+    a.chunks_per_split = ceil_div(nchunks, plan.splits);
+    a.srow0 = tail_rt > 0 ? tile_first_row(main_rt, plan.block_rows, a.wb_rows, tpb) : 0;
+    a.srows = a.R - a.srow0;
+    dim3 grid(static_cast<unsigned>(tail_rt > 0 ? tail_rt : row_tiles), static_cast<unsigned>(col_tiles),
+              static_cast<unsigned>(plan.splits));
     rc = launch_variant(plan.block_rows / 32, !shift_add, grid, a, stream);
     if (rc != ATB_OK) return rc;
     rc = check_launch("lut_gemm_kernel");
     if (rc != ATB_OK) return rc;
     if (plan.splits > 1) {
-        lut_gemm_reduce_kernel<<<grid_for(a.R * a.O, 256, 8 * sm_count()), 256, 0, stream>>>(a);
+        lut_gemm_reduce_kernel<<<grid_for(a.srows * a.O, 256, 8 * sm_count()), 256, 0, stream>>>(a);
         rc = check_launch("lut_gemm_reduce_kernel");
     }
     return rc;

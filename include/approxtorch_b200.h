@@ -69,11 +69,17 @@ int atb_im2col_u8(const void* x, int dtype, int N, int C, int H, int W, int kh, 
  * xsum = sum_k x_idx of the row; they are combined in integer arithmetic before the single
  * conversion to fp32.  Integer tables accumulate in int32 (exact), other tables in fp32 in ascending k.
  *
+ * cfg: -1 automatic.  Otherwise bits 0-15 pixel rows per block (64, 128, 256 or 512; 0 = automatic),
+ * bits 16-23 split-K factor for every tile (0 = automatic), bit 24 accumulate with shift + add instead of the
+ * dot-product instruction, bit 25 never split only the trailing row tiles.
+ *
  * The plan says how the launch will be tiled and how much scratch (bytes) a split-K launch needs. */
 typedef struct {
     int block_rows;      /* pixel rows per thread block: 64, 128, 256 or 512 */
     int splits;          /* split-K factor; > 1 needs scratch */
     size_t scratch_bytes;
+    int tail_row_tiles;  /* 0: `splits` applies to every tile; n > 0: only the last n row tiles are split (they
+                            complete a ragged last wave), the rest run unsplit in a launch of their own */
 } atb_gemm_plan;
 
 int atb_lut_gemm_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_plan* plan /*host*/);

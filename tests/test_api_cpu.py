@@ -197,6 +197,11 @@ def test_library_exports_every_declared_symbol():
     plan = _C.GemmPlan()
     assert _C.lib.atb_lut_gemm_plan(65536, 576, 256, 4096, -1, plan) == 0
     assert plan.block_rows % 32 == 0 and plan.splits >= 1
+    # 128 row tiles x 4 column tiles on 148 SMs: three whole waves unsplit, the last 17 row tiles split in two
+    assert (plan.block_rows, plan.splits, plan.tail_row_tiles) == (512, 2, 17)
+    assert plan.scratch_bytes == 2 * 17 * 512 * 257 * 4
+    assert _C.lib.atb_lut_gemm_plan(65536, 576, 256, 4096, 1 << 25, plan) == 0
+    assert (plan.splits, plan.tail_row_tiles, plan.scratch_bytes) == (1, 0, 0)
     assert _C.lib.atb_lut_gemm_plan(-1, 1, 1, 0, -1, plan) != 0 and "negative" in _C.last_error()
 
 

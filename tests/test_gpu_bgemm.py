@@ -198,11 +198,84 @@ def test_benchmark_size_rows_against_oracle(dev):
                         Bt * M, K, 1, Nc, wb_rows=M, w_batch_stride=Nc * K)
     yh = y.cpu().numpy().astype(np.int64)
     rows = rng.integers(0, M, 24)
-    for b in (0, 7, 15):
+    for b in (0, 7, 13, 15):
         ref = lo.gemm_exact(A[b][rows], Bm[b].T, lut)
         np.testing.assert_array_equal(yh[b][rows], ref)
     tab = lut.reshape(256, 256).astype(np.int64)
-    for b in (3, 12):
+    for b in (3, 12, 13, 15):
         counts = np.stack([np.bincount(A[b][:, k], minlength=256) for k in range(K)])      # [K, 256]
         expect = np.array([(counts * tab[:, Bm[b][o]].T).sum() for o in range(Nc)])
         np.testing.assert_array_equal(yh[b].sum(axis=0), expect)
+
+
+def _plan(ops, R, K, O, wb_rows=0, cfg=-1):
+    import ctypes
+    from approxtorch_b200.backend import _C
+    plan = _C.GemmPlan()
+    assert _C.lib.atb_lut_gemm_plan(R, K, O, wb_rows, cfg, ctypes.byref(plan)) == 0
+    return plan
+
+
+NO_TAIL = 1 << 25            # cfg bit 25: never split only the trailing row tiles
+
+
+def test_ragged_last_wave_is_split_along_k_column_operand(dev):
+    """More than one wave of tiles with a ragged last wave: the trailing row tiles run split-K in a launch of
+    their own.  Same integers as the oracle and as the unsplit plan, with and without the zero-point terms."""
+    ops = _ops()
+    rng = np.random.default_rng(77)
+    N, K, L, O = 1, 80, 20000, 256
+    plan = _plan(ops, N * L, K, O)
+    assert plan.tail_row_tiles > 0 and plan.splits > 1
+    assert plan.scratch_bytes < plan.splits * N * L * (O + 1) * 4         # scratch covers the tail rows only
+    assert _plan(ops, N * L, K, O, cfg=NO_TAIL).tail_row_tiles == 0
+    x = rng.integers(0, 256, (N, K, L), dtype=np.uint8)
+    w = rng.integers(0, 256, (O, K), dtype=np.uint8)
+    lut = lo.lut_signed_noisy(64, seed=4)
+    ref = c_oracle.bgemm_u8(x, w, lut)
+    img = ops.lut_image(_t(lut.reshape(-1), dev))
+    y = torch.empty((N, O, L), dtype=torch.float32, device=dev)
+    ops.lut_gemm_launch(_t(x, dev), _t(w, dev), img, y, N, K, L, O)
+    np.testing.assert_array_equal(y.cpu().numpy().astype(np.float64), ref)
+    # asymmetric epilogue: row sums of the tail rows travel through scratch too
+    alpha = _t(rng.uniform(0.5, 2.0, O).astype(np.float32), dev)
+    beta = _t(rng.uniform(-1, 1, O).astype(np.float32), dev)
+    zx = _t(np.array([37.0], dtype=np.float32), dev)
+    zw = _t(rng.integers(0, 256, O).astype(np.float32), dev)
+    wsum = _t(w.astype(np.int64).sum(axis=1).astype(np.int32), dev)
+    ya, yb = torch.empty_like(y), torch.empty_like(y)
+    ops.lut_gemm_launch(_t(x, dev), _t(w, dev), img, ya, N, K, L, O, alpha=alpha, beta=beta, zero_x=zx, zero_w=zw, wsum=wsum)
+    ops.lut_gemm_launch(_t(x, dev), _t(w, dev), img, yb, N, K, L, O, alpha=alpha, beta=beta, zero_x=zx, zero_w=zw, wsum=wsum,
+                        cfg=NO_TAIL)
+    assert torch.equal(ya, yb)
+    t = (ref - zw.cpu().numpy().astype(np.float64)[None, :, None] * x.astype(np.int64).sum(axis=1)[:, None, :]
+         - 37.0 * wsum.cpu().numpy().astype(np.float64)[None, :, None] + K * 37.0 * zw.cpu().numpy().astype(np.float64)[None, :, None])
+    expect = (t.astype(np.float32) * alpha.cpu().numpy()[None, :, None]) + beta.cpu().numpy()[None, :, None]
+    np.testing.assert_array_equal(ya.cpu().numpy(), expect.astype(np.float32))
+
+
+def test_ragged_last_wave_per_batch_weights_and_image_operand(dev):
+    ops = _ops()
+    rng = np.random.default_rng(78)
+    lut = lo.lut_affine_asymmetric()
+    img = ops.lut_image(_t(lut.reshape(-1), dev))
+    # one weight matrix per batch item, batch rows not a multiple of the block rows
+    Bt, M, K, Nc = 5, 4600, 96, 256
+    assert _plan(ops, Bt * M, K, Nc, wb_rows=M).tail_row_tiles > 0
+    A = rng.integers(0, 256, (Bt, M, K), dtype=np.uint8)
+    Bm = rng.integers(0, 256, (Bt, Nc, K), dtype=np.uint8)
+    y = torch.empty((Bt, M, Nc), dtype=torch.float32, device=dev)
+    ops.lut_gemm_launch(_t(A, dev), _t(Bm, dev), img, y, Bt * M, K, 1, Nc, wb_rows=M, w_batch_stride=Nc * K)
+    for b in range(Bt):
+        np.testing.assert_array_equal(y[b].cpu().numpy().astype(np.int64), lo.gemm_exact(A[b], Bm[b].T, lut))
+    # image operand (im2col in the tile loader)
+    B, C, H, W, O = 8, 8, 80, 80, 128
+    assert _plan(ops, B * H * W, C * 9, O).tail_row_tiles > 0
+    x8 = rng.integers(-127, 128, (B, C, H, W)).astype(np.int8)
+    widx = rng.integers(0, 256, (O, C * 9), dtype=np.uint8)
+    cols = lo.im2col_index(lo.index_of(x8, True), 3, 3, 1, 1, 1, 1, 1, 1, 128)
+    ref = c_oracle.bgemm_u8(cols, widx, lut)
+    g4 = ((3, 3), (1, 1), (1, 1), (1, 1))
+    yc = ops.lut_conv2d_launch(_t(x8, dev), _t(widx, dev), img, g4, 128)
+    np.testing.assert_array_equal(yc.flatten(2).cpu().numpy().astype(np.float64), ref)
+    assert torch.equal(yc, ops.lut_conv2d_launch(_t(x8, dev), _t(widx, dev), img, g4, 128, cfg=NO_TAIL))
