@@ -49,8 +49,9 @@ int sm_count();
 // ---------------------------------------------------------------------------------------------
 struct LutImage {
     int flags[4];
-    // tabTP16: transposed and x-permuted, entry (w, x) at w*256 + 2*(x & 127) + (x >> 7), so that the 32-bit
-    // word i of row w holds the pair {x = i (low half), x = i + 128 (high half)}
+    // tabTP16: transposed and x-permuted.  A 32-bit word of row w holds the pair i = {x = i (low half),
+    // x = i + 128 (high half)}, i = 0..127, and pair i is word 4 * (i & 31) + (i >> 5) of the row, so that lane l
+    // of a warp reads the pairs l, l + 32, l + 64, l + 96 with one 16-byte load
     int16_t tabTP16[65536];
     int16_t tabT16[65536];
     int16_t tab16[65536];

@@ -8,13 +8,13 @@
 // uniformly distributed operands, because 32 data-dependent addresses collide in the 32 banks.
 // The kernel removes those collisions by construction and fetches two lookups per load:
 //
-//  * The whole transposed 16-bit table (128 KB) is resident in shared memory, stored so that the 32-bit
-//    word i of row w holds the entries {x = i, x = i + 128}.
+//  * The whole transposed 16-bit table (128 KB) is resident in shared memory, stored so that a 32-bit word
+//    of row w holds the entries {x = i, x = i + 128} and a lane's 16-byte load yields the four such pairs
+//    (i = lane + 32 j) that the lane will write out.
 //  * For every k-step the block STAGES the 64 table columns its 64 output channels need as 32 PAIR rows:
 //    pair row p interleaves the columns of output channels p and p + 32, word x = {T[w_p][x], T[w_p+32][x]}.
-//    Building a pair row is two conflict-free word reads, two byte-permutes and two conflict-free word
-//    writes per lane and per 2 x 2 entries (the x-permuted table layout makes both halves land in lanes'
-//    consecutive words).  The pair-row pitch is 257 words (odd), so for one activation value x the 32 lanes
+//    Building a pair row is two 16-byte reads, eight byte-permutes and eight conflict-free word writes per
+//    lane (the x-permuted table layout makes both halves land in lanes' consecutive words).  The pair-row pitch is 257 words (odd), so for one activation value x the 32 lanes
 //    of a warp - one pair row each - hit 32 different banks: bank = (lane + x) mod 32.
 //  * A lookup instruction reads stage[lane][x] with a warp-uniform x (the activation of the pixel row the
 //    warp works on): one wavefront and one instruction per 64 lookups.
@@ -99,17 +99,18 @@ __device__ __forceinline__ long long output_offset(long long r, int o, const Gem
 __device__ __forceinline__ void stage_pairs(uint8_t* stage, const uint8_t* s_tab, const uint8_t* wstep,
                                             int warp, int lane, int nwarps)
 {
-    const uint32_t* tab = reinterpret_cast<const uint32_t*>(s_tab);
+    const uint4* tab = reinterpret_cast<const uint4*>(s_tab);
     for (int p = warp; p < kPairRows; p += nwarps) {
-        const uint32_t* src_a = tab + static_cast<uint32_t>(wstep[p]) * 128u;
-        const uint32_t* src_b = tab + static_cast<uint32_t>(wstep[p + kPairRows]) * 128u;
+        // one 16-byte load per column: the pairs {x = i, x = i + 128} for i = lane, lane + 32, lane + 64, lane + 96
+        const uint4 a4 = tab[static_cast<uint32_t>(wstep[p]) * 32u + lane];
+        const uint4 b4 = tab[static_cast<uint32_t>(wstep[p + kPairRows]) * 32u + lane];
+        const uint32_t va[4] = {a4.x, a4.y, a4.z, a4.w}, vb[4] = {b4.x, b4.y, b4.z, b4.w};
         uint32_t* dst = reinterpret_cast<uint32_t*>(stage + p * kPairPitch);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int i = lane + 32 * j;
-            const uint32_t va = src_a[i], vb = src_b[i];          // {x = i, x = i + 128} of either column
-            dst[i] = __byte_perm(va, vb, 0x5410);                 // x = i:       {A[i], B[i]}
-            dst[i + 128] = __byte_perm(va, vb, 0x7632);           // x = i + 128: {A[i+128], B[i+128]}
+            dst[i] = __byte_perm(va[j], vb[j], 0x5410);           // x = i:       {A[i], B[i]}
+            dst[i + 128] = __byte_perm(va[j], vb[j], 0x7632);     // x = i + 128: {A[i+128], B[i+128]}
         }
     }
 }
@@ -310,7 +311,7 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
     uint8_t* s_stage = smem + kSmemStage;
     uint8_t* s_x = smem + kSmemX;
     uint8_t* s_w = smem + kSmemW;
-    const uint32_t* tab = reinterpret_cast<const uint32_t*>(s_tab);
+    const uint4* tab4 = reinterpret_cast<const uint4*>(s_tab);
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
@@ -358,10 +359,10 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
 #pragma unroll
                     for (int q = 0; q < RPW; ++q) {
                         const int p = warp + q * NW;
-                        const uint32_t* src_a = tab + static_cast<uint32_t>(wnext[p]) * 128u;
-                        const uint32_t* src_b = tab + static_cast<uint32_t>(wnext[p + kPairRows]) * 128u;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) { va[q][j] = src_a[lane + 32 * j]; vb[q][j] = src_b[lane + 32 * j]; }
+                        const uint4 a4 = tab4[static_cast<uint32_t>(wnext[p]) * 32u + lane];
+                        const uint4 b4 = tab4[static_cast<uint32_t>(wnext[p + kPairRows]) * 32u + lane];
+                        va[q][0] = a4.x; va[q][1] = a4.y; va[q][2] = a4.z; va[q][3] = a4.w;
+                        vb[q][0] = b4.x; vb[q][1] = b4.y; vb[q][2] = b4.z; vb[q][3] = b4.w;
                     }
                 }
                 lookup_step<TM, DP2A>(stage_cur, xrow, lane, acc);

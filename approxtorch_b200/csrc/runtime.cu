@@ -49,7 +49,10 @@ __global__ void lut_prepare_kernel(const float* __restrict__ lut, LutImage* __re
     img->tabT16[t] = v16;
     img->tabT32[t] = v;
     const int xi = i >> 8, wi = i & 255;
-    img->tabTP16[(wi << 8) + ((xi & 127) << 1) + (xi >> 7)] = v16;
+    // pair i = xi & 127 = {x = i, x = i + 128} sits at word 4 * (i & 31) + (i >> 5) of row wi: a 16-byte load by
+    // lane l then yields the pairs l, l + 32, l + 64, l + 96
+    const int pair = xi & 127;
+    img->tabTP16[(wi << 8) + (((pair & 31) << 2) + (pair >> 5)) * 2 + (xi >> 7)] = v16;
 }
 
 }  // namespace atb
