@@ -39,9 +39,9 @@ namespace atb {
 
 constexpr int kStagedCols = 64;                          // output channels per thread block
 constexpr int kChunk = 16;                               // k-steps per operand tile
-constexpr int kPairRows = kStagedCols / 2;               // staged pair rows per k-step
-constexpr int kPairPitch = 1028;                         // bytes per pair row (256 x 2 x uint16 + 4 B skew)
-constexpr int kStageBytes = kPairRows * kPairPitch;      // 32896
+constexpr int kQuadRows = kStagedCols / 4;               // staged quad rows per k-step
+constexpr int kQuadPitch = 2056;                         // bytes per quad row (256 x 4 x uint16 + 8 B skew)
+constexpr int kStageBytes = kQuadRows * kQuadPitch;      // 32896
 constexpr int kMaxBlockRows = 512;
 constexpr int kTableBytes = 65536 * 2;
 constexpr int kSmemStage = kTableBytes;
@@ -95,23 +95,44 @@ __device__ __forceinline__ long long output_offset(long long r, int o, const Gem
     return (n * a.O + o) * a.L + l;
 }
 
-// One k-step of staging: every warp builds its share of the 32 pair rows.
-__device__ __forceinline__ void stage_pairs(uint8_t* stage, const uint8_t* s_tab, const uint8_t* wstep,
-                                            int warp, int lane, int nwarps)
+// Quad row p interleaves the table columns of output channels p, p + 16, p + 32 and p + 48: its 8-byte entry x
+// is {T[w_p][x], T[w_p+16][x]} (first word) and {T[w_p+32][x], T[w_p+48][x]} (second word).
+struct QuadWords {
+    uint32_t a[4], b[4], c[4], d[4];        // pairs {x = i, x = i + 128}, i = lane + 32 j, of the four columns
+};
+
+__device__ __forceinline__ void fetch_quad(const uint8_t* s_tab, const uint8_t* wstep, int p, int lane, QuadWords& v)
 {
     const uint4* tab = reinterpret_cast<const uint4*>(s_tab);
-    for (int p = warp; p < kPairRows; p += nwarps) {
-        // one 16-byte load per column: the pairs {x = i, x = i + 128} for i = lane, lane + 32, lane + 64, lane + 96
-        const uint4 a4 = tab[static_cast<uint32_t>(wstep[p]) * 32u + lane];
-        const uint4 b4 = tab[static_cast<uint32_t>(wstep[p + kPairRows]) * 32u + lane];
-        const uint32_t va[4] = {a4.x, a4.y, a4.z, a4.w}, vb[4] = {b4.x, b4.y, b4.z, b4.w};
-        uint32_t* dst = reinterpret_cast<uint32_t*>(stage + p * kPairPitch);
+    const uint4 a4 = tab[static_cast<uint32_t>(wstep[p]) * 32u + lane];
+    const uint4 b4 = tab[static_cast<uint32_t>(wstep[p + kQuadRows]) * 32u + lane];
+    const uint4 c4 = tab[static_cast<uint32_t>(wstep[p + 2 * kQuadRows]) * 32u + lane];
+    const uint4 d4 = tab[static_cast<uint32_t>(wstep[p + 3 * kQuadRows]) * 32u + lane];
+    v.a[0] = a4.x; v.a[1] = a4.y; v.a[2] = a4.z; v.a[3] = a4.w;
+    v.b[0] = b4.x; v.b[1] = b4.y; v.b[2] = b4.z; v.b[3] = b4.w;
+    v.c[0] = c4.x; v.c[1] = c4.y; v.c[2] = c4.z; v.c[3] = c4.w;
+    v.d[0] = d4.x; v.d[1] = d4.y; v.d[2] = d4.z; v.d[3] = d4.w;
+}
+
+__device__ __forceinline__ void store_quad(uint8_t* stage, int p, int lane, const QuadWords& v)
+{
+    uint2* dst = reinterpret_cast<uint2*>(stage + p * kQuadPitch);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int i = lane + 32 * j;
-            dst[i] = __byte_perm(va[j], vb[j], 0x5410);           // x = i:       {A[i], B[i]}
-            dst[i + 128] = __byte_perm(va[j], vb[j], 0x7632);     // x = i + 128: {A[i+128], B[i+128]}
-        }
+    for (int j = 0; j < 4; ++j) {
+        const int i = lane + 32 * j;
+        dst[i] = make_uint2(__byte_perm(v.a[j], v.b[j], 0x5410), __byte_perm(v.c[j], v.d[j], 0x5410));        // x = i
+        dst[i + 128] = make_uint2(__byte_perm(v.a[j], v.b[j], 0x7632), __byte_perm(v.c[j], v.d[j], 0x7632));  // x = i + 128
+    }
+}
+
+// One k-step of staging: every warp builds its share of the 16 quad rows.
+__device__ __forceinline__ void stage_quads(uint8_t* stage, const uint8_t* s_tab, const uint8_t* wstep,
+                                            int warp, int lane, int nwarps)
+{
+    for (int p = warp; p < kQuadRows; p += nwarps) {
+        QuadWords v;
+        fetch_quad(s_tab, wstep, p, lane, v);
+        store_quad(stage, p, lane, v);
     }
 }
 
@@ -125,22 +146,29 @@ __device__ __forceinline__ void load_x_words(const uint8_t* xrow, uint32_t (&xw)
     }
 }
 
-// Lookups of one k-step for this thread's TM pixel rows x 2 output channels: per row one word load
-// ({low channel, high channel}), S0 += word, S1 += high half (one dot-product-accumulate instruction
-// that multiplies the halves by {0, 1}, or a shift and an add).
-template <int TM, bool DP2A>
-__device__ __forceinline__ void lookup_step(const uint8_t* stage, const uint8_t* xrow, int lane,
-                                            unsigned (&acc)[TM][2])
+// Lookups of one k-step.  Lane (h, q) = (lane / 16, lane % 16) works on 16 pixel rows (h * 16 + j of the
+// warp's 32) and the four output channels of quad row q: per row ONE 8-byte load, then per word S0 += word
+// and S1 += high half (a dot-product-accumulate that multiplies the halves by {0, 1}, or shift + add).
+// An 8-byte shared load is served half a warp at a time, and the 16 lanes of a half (one quad row each, the
+// same activation value x) hit all 32 banks once: bank = (2 q + 2 x + {0, 1}) mod 32.
+template <bool DP2A>
+__device__ __forceinline__ void lookup_step(const uint8_t* stage, const uint8_t* xrow16, int q, unsigned (&acc)[16][4])
 {
-    uint32_t xw[TM / 4];
-    load_x_words<TM>(xrow, xw);
-    const uint32_t* base = reinterpret_cast<const uint32_t*>(stage + lane * kPairPitch);
+    uint32_t xw[4];
+    load_x_words<16>(xrow16, xw);
+    const uint2* base = reinterpret_cast<const uint2*>(stage + q * kQuadPitch);
 #pragma unroll
-    for (int j = 0; j < TM; ++j) {
-        const uint32_t v = base[__byte_perm(xw[j >> 2], 0, 0x4440 | (j & 3))];
-        acc[j][0] += v;
-        if constexpr (DP2A) acc[j][1] = __dp2a_lo(v, 0x00000100u, acc[j][1]);
-        else acc[j][1] += v >> 16;
+    for (int j = 0; j < 16; ++j) {
+        const uint2 v = base[__byte_perm(xw[j >> 2], 0, 0x4440 | (j & 3))];
+        acc[j][0] += v.x;
+        acc[j][2] += v.y;
+        if constexpr (DP2A) {
+            acc[j][1] = __dp2a_lo(v.x, 0x00000100u, acc[j][1]);
+            acc[j][3] = __dp2a_lo(v.y, 0x00000100u, acc[j][3]);
+        } else {
+            acc[j][1] += v.x >> 16;
+            acc[j][3] += v.y >> 16;
+        }
     }
 }
 
@@ -241,33 +269,39 @@ __device__ __forceinline__ void store_chunk(uint8_t* s_x, uint8_t* s_w, int buf,
     }
 }
 
-// Epilogue shared by both paths: `total(j, t)` yields the finished sum of row j, column slot t.
-// Thread (warp, lane) holds pixel rows warp*32 + j (j = 0..31) of output channels lane and lane + 32.
+// Epilogue shared by both paths: `total(j, t)` yields the finished sum of this thread's row slot j, column slot t.
+// QUAD = false (fp32 path): thread (warp, lane) holds pixel rows warp*32 + j (j = 0..31) of output channels
+// lane and lane + 32.  QUAD = true (integer path): thread (warp, h, q) holds pixel rows warp*32 + h*16 + j
+// (j = 0..15) of output channels q + 16 t (t = 0..3).  `xsum` is the operand sum of pixel row warp*32 + lane.
 // Split-K partials and the L == 1 layout are written directly (lanes span consecutive channels, which is
 // the fast axis there).  For L > 1 the fast axis of y[n, o, l] is the pixel, so each warp first turns its
 // 32 x 64 tile around in shared memory (the table / stage area is free by now) and then stores 128
 // contiguous bytes per channel.
-template <int TM, class Total, class Bits>
+template <bool QUAD, class Total, class Bits>
 __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, long long r0, long long r_end, int c0,
                                            int warp, int lane, int xsum, Total total, Bits bits)
 {
-    static_assert(TM == 32, "the transposed epilogue maps lanes to the warp's 32 pixel rows");
+    constexpr int NJ = QUAD ? 16 : 32;               // row slots per thread
+    constexpr int NT = QUAD ? 4 : 2;                 // column slots per thread
+    const int row_base = QUAD ? (lane >> 4) * 16 : 0;        // first of this thread's rows within the warp's 32
+    const int col_base = QUAD ? (lane & 15) : lane;          // first of this thread's columns within the 64
+    constexpr int col_step = QUAD ? 16 : 32;
     const int split = blockIdx.z;
     const bool want_xsum = a.zero_x != nullptr;
     if (a.splits > 1 || a.L == 1) {
 #pragma unroll
-        for (int j = 0; j < TM; ++j) {
-            const long long r = r0 + warp * TM + j;
-            const int xs = __shfl_sync(0xffffffffu, xsum, j);
+        for (int j = 0; j < NJ; ++j) {
+            const long long r = r0 + warp * 32 + row_base + j;
+            const int xs = __shfl_sync(0xffffffffu, xsum, row_base + j);
             if (r >= r_end) continue;
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {
-                const int o = c0 + lane + 32 * t;
+            for (int t = 0; t < NT; ++t) {
+                const int o = c0 + col_base + col_step * t;
                 if (o >= a.O) continue;
                 if (a.splits > 1) a.scratch[(static_cast<long long>(split) * a.srows + (r - a.srow0)) * a.O + o] = bits(j, t);
                 else a.y[output_offset(r, o, a)] = finalize_output(total(j, t), xs, o, a);
             }
-            if (a.splits > 1 && want_xsum && blockIdx.y == 0 && lane == 0)
+            if (a.splits > 1 && want_xsum && blockIdx.y == 0 && col_base == 0)
                 a.scratch[static_cast<long long>(a.splits) * a.srows * a.O + static_cast<long long>(split) * a.srows + (r - a.srow0)] = xs;
         }
         return;
@@ -276,16 +310,16 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
     constexpr int kPitch = 33;                         // words per channel row of the turned tile
     float* tile = reinterpret_cast<float*>(smem) + warp * (kStagedCols * kPitch);
 #pragma unroll
-    for (int j = 0; j < TM; ++j) {
-        const int xs = __shfl_sync(0xffffffffu, xsum, j);
+    for (int j = 0; j < NJ; ++j) {
+        const int xs = __shfl_sync(0xffffffffu, xsum, row_base + j);
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            const int o = c0 + lane + 32 * t;
-            tile[(lane + 32 * t) * kPitch + j] = (o < a.O) ? finalize_output(total(j, t), xs, o, a) : 0.0f;
+        for (int t = 0; t < NT; ++t) {
+            const int oc = col_base + col_step * t;
+            tile[oc * kPitch + row_base + j] = (c0 + oc < a.O) ? finalize_output(total(j, t), xs, c0 + oc, a) : 0.0f;
         }
     }
     __syncwarp();
-    const long long r = r0 + warp * TM + lane;         // this lane's pixel row
+    const long long r = r0 + warp * 32 + lane;         // this lane's pixel row
     if (r < r_end) {
         const long long n = r / a.L;
         const long long l = r - n * a.L;
@@ -296,31 +330,31 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
 }
 
 // 16-bit table classes: staged conflict-free lookups, exact integer accumulation.
-// Software pipeline per k-step: issue the table reads for the NEXT step's pair rows, do this step's
-// lookups (which hides the latency of those reads), permute and store the next step's pair rows into the
+// Software pipeline per k-step: issue the table reads for the NEXT step's quad rows, do this step's
+// lookups (which hides the latency of those reads), permute and store the next step's quad rows into the
 // other stage buffer, one barrier.
 template <int NW, bool DP2A>
 __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
                                               const uint8_t* wcol, bool vec_x, bool vec_w, int pad, int bias,
                                               long long r0, long long r_end, int c0, int kbeg, int kend)
 {
-    constexpr int TM = 32;
-    constexpr int RPW = kPairRows / NW;          // pair rows each warp stages per k-step
-    constexpr bool kPipelined = RPW <= 2;        // keep the next step's table words in registers across the lookups
+    constexpr int TM = 32;                       // pixel rows per warp
+    constexpr bool kPipelined = NW >= kQuadRows; // one quad row per warp: keep the next step's table words in registers
     uint8_t* s_tab = smem;
     uint8_t* s_stage = smem + kSmemStage;
     uint8_t* s_x = smem + kSmemX;
     uint8_t* s_w = smem + kSmemW;
-    const uint4* tab4 = reinterpret_cast<const uint4*>(s_tab);
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
+    const int q = lane & 15;                     // this lane's quad row
+    const int h = lane >> 4;                     // which 16 of the warp's 32 pixel rows
     const int nch = (kend - kbeg + kChunk - 1) / kChunk;
     constexpr int bm = NW * TM;
 
-    unsigned acc[TM][2];
+    unsigned acc[16][4];
 #pragma unroll
-    for (int j = 0; j < TM; ++j) { acc[j][0] = 0u; acc[j][1] = 0u; }
+    for (int j = 0; j < 16; ++j) { acc[j][0] = 0u; acc[j][1] = 0u; acc[j][2] = 0u; acc[j][3] = 0u; }
     int xsum = 0;
     const bool want_xsum = a.zero_x != nullptr;
 
@@ -331,7 +365,7 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
     }
     __syncthreads();          // table image and first operand tile are in shared memory
     if (nch > 0) {
-        stage_pairs(s_stage, s_tab, s_w, warp, lane, NW);
+        stage_quads(s_stage, s_tab, s_w, warp, lane, NW);
         __syncthreads();
     }
 
@@ -354,45 +388,27 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
             if (want_xsum) xsum += static_cast<int>(xrow[lane]);
 
             if constexpr (kPipelined) {
-                uint32_t va[RPW][4], vb[RPW][4];
-                if (wnext != nullptr) {
-#pragma unroll
-                    for (int q = 0; q < RPW; ++q) {
-                        const int p = warp + q * NW;
-                        const uint4 a4 = tab4[static_cast<uint32_t>(wnext[p]) * 32u + lane];
-                        const uint4 b4 = tab4[static_cast<uint32_t>(wnext[p + kPairRows]) * 32u + lane];
-                        va[q][0] = a4.x; va[q][1] = a4.y; va[q][2] = a4.z; va[q][3] = a4.w;
-                        vb[q][0] = b4.x; vb[q][1] = b4.y; vb[q][2] = b4.z; vb[q][3] = b4.w;
-                    }
-                }
-                lookup_step<TM, DP2A>(stage_cur, xrow, lane, acc);
-                if (wnext != nullptr) {
-#pragma unroll
-                    for (int q = 0; q < RPW; ++q) {
-                        uint32_t* dst = reinterpret_cast<uint32_t*>(stage_next + (warp + q * NW) * kPairPitch);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            dst[lane + 32 * j] = __byte_perm(va[q][j], vb[q][j], 0x5410);
-                            dst[lane + 32 * j + 128] = __byte_perm(va[q][j], vb[q][j], 0x7632);
-                        }
-                    }
-                }
+                QuadWords v;
+                if (wnext != nullptr && warp < kQuadRows) fetch_quad(s_tab, wnext, warp, lane, v);
+                lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
+                if (wnext != nullptr && warp < kQuadRows) store_quad(stage_next, warp, lane, v);
             } else {
-                if (wnext != nullptr) stage_pairs(stage_next, s_tab, wnext, warp, lane, NW);
-                lookup_step<TM, DP2A>(stage_cur, xrow, lane, acc);
+                if (wnext != nullptr) stage_quads(stage_next, s_tab, wnext, warp, lane, NW);
+                lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
             }
             __syncthreads();
         }
     }
     const long long remove = static_cast<long long>(bias) * (kend - kbeg);     // +32768 per looked-up entry of a signed table
-    // acc[j][0] holds sum(lo) + 65536 * sum(hi) modulo 2^32, acc[j][1] holds sum(hi)
+    // per word: acc[j][2u] holds sum(lo) + 65536 * sum(hi) modulo 2^32, acc[j][2u + 1] holds sum(hi)
     auto total = [&](int j, int t) -> long long {
-        const unsigned v = t == 0 ? acc[j][0] - (acc[j][1] << 16) : acc[j][1];
+        const int u = (t >> 1) * 2;
+        const unsigned v = (t & 1) == 0 ? acc[j][u] - (acc[j][u + 1] << 16) : acc[j][u + 1];
         return static_cast<long long>(v) - remove;
     };
-    write_tile<TM>(a, smem, r0, r_end, c0, warp, lane, xsum,
-                   [&](int j, int t) { return static_cast<double>(total(j, t)); },
-                   [&](int j, int t) { return static_cast<int>(total(j, t)); });
+    write_tile<true>(a, smem, r0, r_end, c0, warp, lane, xsum,
+                     [&](int j, int t) { return static_cast<double>(total(j, t)); },
+                     [&](int j, int t) { return static_cast<int>(total(j, t)); });
 }
 
 // Tables that are not 16-bit exact: lookups from the transposed fp32 table in global memory,
@@ -437,7 +453,7 @@ __device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, 
         }
         __syncthreads();
     }
-    write_tile<TM>(a, smem, r0, r_end, c0, warp, lane, xsum,
+    write_tile<false>(a, smem, r0, r_end, c0, warp, lane, xsum,
                [&](int j, int t) { return static_cast<double>(acc[j][t]); },
                [&](int j, int t) { return __float_as_int(acc[j][t]); });
 }
