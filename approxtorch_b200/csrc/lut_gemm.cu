@@ -95,6 +95,10 @@ __device__ __forceinline__ long long output_offset(long long r, int o, const Gem
     return (n * a.O + o) * a.L + l;
 }
 
+// Position of output channel c (0..63 within the block) in a k-step's row of staged weight indices: the four
+// channels of quad row p = c % 16 are adjacent.
+__device__ __forceinline__ int w_slot(int c) { return ((c & (kQuadRows - 1)) << 2) + (c >> 4); }
+
 // Quad row p interleaves the table columns of output channels p, p + 16, p + 32 and p + 48: its 8-byte entry x
 // is {T[w_p][x], T[w_p+16][x]} (first word) and {T[w_p+32][x], T[w_p+48][x]} (second word).
 struct QuadWords {
@@ -104,10 +108,13 @@ struct QuadWords {
 __device__ __forceinline__ void fetch_quad(const uint8_t* s_tab, const uint8_t* wstep, int p, int lane, QuadWords& v)
 {
     const uint4* tab = reinterpret_cast<const uint4*>(s_tab);
-    const uint4 a4 = tab[static_cast<uint32_t>(wstep[p]) * 32u + lane];
-    const uint4 b4 = tab[static_cast<uint32_t>(wstep[p + kQuadRows]) * 32u + lane];
-    const uint4 c4 = tab[static_cast<uint32_t>(wstep[p + 2 * kQuadRows]) * 32u + lane];
-    const uint4 d4 = tab[static_cast<uint32_t>(wstep[p + 3 * kQuadRows]) * 32u + lane];
+    // the weight indices of a k-step are stored quad row by quad row (w_slot), so the four this quad row needs
+    // arrive with one word load
+    const uint32_t w4 = reinterpret_cast<const uint32_t*>(wstep)[p];
+    const uint4 a4 = tab[(w4 & 0xffu) * 32u + lane];
+    const uint4 b4 = tab[((w4 >> 8) & 0xffu) * 32u + lane];
+    const uint4 c4 = tab[((w4 >> 16) & 0xffu) * 32u + lane];
+    const uint4 d4 = tab[(w4 >> 24) * 32u + lane];
     v.a[0] = a4.x; v.a[1] = a4.y; v.a[2] = a4.z; v.a[3] = a4.w;
     v.b[0] = b4.x; v.b[1] = b4.y; v.b[2] = b4.z; v.b[3] = b4.w;
     v.c[0] = c4.x; v.c[1] = c4.y; v.c[2] = c4.z; v.c[3] = c4.w;
@@ -178,8 +185,8 @@ __device__ __forceinline__ void lookup_step_f32(const float* tabT, const uint8_t
 {
     uint32_t xw[TM / 4];
     load_x_words<TM>(xrow, xw);
-    const float* c0 = tabT + (static_cast<uint32_t>(wstep[lane]) << 8);
-    const float* c1 = tabT + (static_cast<uint32_t>(wstep[lane + 32]) << 8);
+    const float* c0 = tabT + (static_cast<uint32_t>(wstep[w_slot(lane)]) << 8);
+    const float* c1 = tabT + (static_cast<uint32_t>(wstep[w_slot(lane + 32)]) << 8);
 #pragma unroll
     for (int j = 0; j < TM; ++j) {
         const uint32_t xv = (xw[j >> 2] >> (8 * (j & 3))) & 0xffu;
@@ -262,7 +269,7 @@ __device__ __forceinline__ void store_chunk(uint8_t* s_x, uint8_t* s_w, int buf,
             xd[kk * kMaxBlockRows] = static_cast<uint8_t>(xr[kk >> 2] >> (8 * (kk & 3)));
     }
     if (tid < kStagedCols) {
-        uint8_t* wd = s_w + buf * kChunk * kStagedCols + tid;
+        uint8_t* wd = s_w + buf * kChunk * kStagedCols + w_slot(tid);
 #pragma unroll
         for (int kk = 0; kk < kChunk; ++kk)
             wd[kk * kStagedCols] = static_cast<uint8_t>(wr[kk >> 2] >> (8 * (kk & 3)));
