@@ -6,20 +6,22 @@
 // roofline is the shared-memory load pipe (32 four-byte bank reads per clock per SM).  A plain
 // gather from a 128 KB table in shared memory would spend ~3.4 bank wavefronts per 32 lookups on
 // uniformly distributed operands, because 32 data-dependent addresses collide in the 32 banks.
-// The kernel removes those collisions by construction and fetches two lookups per load:
+// The kernel removes those collisions by construction and fetches four lookups per load:
 //
 //  * The whole transposed 16-bit table (128 KB) is resident in shared memory, stored so that a 32-bit word
 //    of row w holds the entries {x = i, x = i + 128} and a lane's 16-byte load yields the four such pairs
 //    (i = lane + 32 j) that the lane will write out.
-//  * For every k-step the block STAGES the 64 table columns its 64 output channels need as 32 PAIR rows:
-//    pair row p interleaves the columns of output channels p and p + 32, word x = {T[w_p][x], T[w_p+32][x]}.
-//    Building a pair row is two 16-byte reads, eight byte-permutes and eight conflict-free word writes per
-//    lane (the x-permuted table layout makes both halves land in lanes' consecutive words).  The pair-row pitch is 257 words (odd), so for one activation value x the 32 lanes
-//    of a warp - one pair row each - hit 32 different banks: bank = (lane + x) mod 32.
-//  * A lookup instruction reads stage[lane][x] with a warp-uniform x (the activation of the pixel row the
-//    warp works on): one wavefront and one instruction per 64 lookups.
-//  * Each thread keeps 32 pixel rows x 2 output channels of exact integer accumulators in registers, so
-//    staging one column (8 wavefronts) is amortised over `block_rows` (up to 512) lookups.
+//  * For every k-step the block STAGES the 64 table columns its 64 output channels need as 16 QUAD rows:
+//    quad row p interleaves the columns of output channels p, p + 16, p + 32 and p + 48, its 8-byte entry x
+//    being {T[w_p][x], T[w_p+16][x]} {T[w_p+32][x], T[w_p+48][x]}.  Building a quad row is four 16-byte
+//    reads, 16 byte-permutes and eight conflict-free 8-byte writes per lane.
+//  * The quad-row pitch is 2056 bytes (514 words, 2 mod 32).  An 8-byte shared load is served half a warp
+//    at a time, and the 16 lanes of a half - one quad row each, the same activation value x (that of the
+//    pixel row the half works on) - hit all 32 banks once: bank = (2 q + 2 x + {0, 1}) mod 32.  So a lookup
+//    instruction costs one wavefront per 64 lookups and one instruction per 128.
+//  * Each thread keeps 16 pixel rows x 4 output channels of exact integer accumulators in registers (a warp
+//    32 rows x 64 channels), so staging one column (8 wavefronts) is amortised over `block_rows` (up to 512)
+//    lookups.
 //  * Entries are unsigned 16-bit (signed tables carry a +32768 bias removed in the epilogue).  A fetched
 //    word v = lo + 65536*hi is accumulated as S0 += v and S1 += hi; the low channel's sum is
 //    S0 - 65536*S1 (exact modulo 2^32, and all sums are below 2^31 for K <= 32768).
