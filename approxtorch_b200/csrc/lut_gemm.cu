@@ -210,27 +210,34 @@ __device__ __forceinline__ void load_chunk(const GemmArgs& a, const RowCursor& r
     if (tid >= bm) {
         // threads beyond the tile's rows (16-rows-per-warp layout) load no pixel operand
     } else if (a.image_mode) {
+        // Branch-free gather: every tap is loaded unconditionally (from the tap, or from the start of the sample
+        // when the tap lies outside the image or past the last k) and the pad value is selected afterwards, so
+        // that the 16 loads are independent and their latencies overlap.
         const int khw = a.g.KH * a.g.KW;
         int c = k0 / khw;
-        int rem = k0 - c * khw;
+        const int rem = k0 - c * khw;
         int i = rem / a.g.KW;
         int j = rem - i * a.g.KW;
-        xr[0] = xr[1] = xr[2] = xr[3] = 0u;
+        uint32_t v[kChunk];
 #pragma unroll
         for (int kk = 0; kk < kChunk; ++kk) {
-            if (k0 + kk < kend) {
-                const int ih = rc.ih0 + i * a.g.DH;
-                const int iw = rc.iw0 + j * a.g.DW;
-                uint32_t v = static_cast<uint32_t>(pad);
-                if (static_cast<unsigned>(ih) < static_cast<unsigned>(a.g.H) &&
-                    static_cast<unsigned>(iw) < static_cast<unsigned>(a.g.W)) {
-                    v = static_cast<uint32_t>(__ldg(rc.base + (static_cast<long long>(c) * a.g.H + ih) * a.g.W + iw))
-                        ^ static_cast<uint32_t>(a.x_xor);
-                }
-                xr[kk >> 2] |= v << (8 * (kk & 3));
-            }
-            if (++j == a.g.KW) { j = 0; if (++i == a.g.KH) { i = 0; ++c; } }
+            const int ih = rc.ih0 + i * a.g.DH;
+            const int iw = rc.iw0 + j * a.g.DW;
+            const bool inside = static_cast<unsigned>(ih) < static_cast<unsigned>(a.g.H) &&
+                                static_cast<unsigned>(iw) < static_cast<unsigned>(a.g.W) && (k0 + kk < kend);
+            const long long off = inside ? (static_cast<long long>(c) * a.g.H + ih) * a.g.W + iw : 0LL;
+            const uint32_t b = static_cast<uint32_t>(__ldg(rc.base + off)) ^ static_cast<uint32_t>(a.x_xor);
+            v[kk] = inside ? b : static_cast<uint32_t>(pad);
+            const bool wrap_j = ++j == a.g.KW;
+            j = wrap_j ? 0 : j;
+            i += wrap_j ? 1 : 0;
+            const bool wrap_i = i == a.g.KH;
+            i = wrap_i ? 0 : i;
+            c += wrap_i ? 1 : 0;
         }
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+            xr[q] = v[4 * q] | (v[4 * q + 1] << 8) | (v[4 * q + 2] << 16) | (v[4 * q + 3] << 24);
     } else if (vec_x) {
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(rc.base + k0));
         xr[0] = v.x; xr[1] = v.y; xr[2] = v.z; xr[3] = v.w;
