@@ -48,6 +48,29 @@ constexpr int TM = 128, TN = 128, TK = 8, PITCH = 132;
 // problem descriptions: a(m, r), b(r, n), store(m, n, v)
 // ------------------------------------------------------------------------------------------------
 
+// Operand fetch of one thread for one 128 x 8 slice of A and of B: slot q covers element e = tid + 256 q.
+// kARFast / kBRFast say which index runs fastest over the threads (the one that is contiguous in memory).
+// Problems whose index arithmetic is cheap use this generic form; the conv problems bring their own, which
+// hoists everything that does not change from slice to slice.
+template <class Prob>
+__device__ __forceinline__ void generic_fetch(const Prob& p, int tid, int m0, int n0, int r0, int rend,
+                                              float (&ra)[4], float (&rb)[4])
+{
+    const int M = p.M(), N = p.N();
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int e = tid + 256 * q;
+        const int ml = Prob::kARFast ? (e >> 3) : (e & 127);
+        const int rl = Prob::kARFast ? (e & 7) : (e >> 7);
+        const int m = m0 + ml, r = r0 + rl;
+        ra[q] = (m < M && r < rend) ? p.a(m, r) : 0.0f;
+        const int nl = Prob::kBRFast ? (e >> 3) : (e & 127);
+        const int sl = Prob::kBRFast ? (e & 7) : (e >> 7);
+        const int n = n0 + nl, sr = r0 + sl;
+        rb[q] = (n < N && sr < rend) ? p.b(sr, n) : 0.0f;
+    }
+}
+
 // column space, grad_x of batch item z:  C[k, l] = sum_o dx[idx(w[o,k])] * go[z, o, l]
 struct ColGradX {
     const float* go; const void* w; int w_dtype; int w_ok; const float* dx; float* gx;
@@ -64,6 +87,11 @@ struct ColGradX {
     }
     __device__ float b(int o, int l) const { return __ldg(go + (z * O + o) * L + l); }
     __device__ void store(int k, int l, float v) const { gx[(z * K + k) * L + l] = v; }
+    __device__ void prep(int, int, int) {}
+    __device__ void fetch(int tid, int m0, int n0, int r0, int rend, float (&ra)[4], float (&rb)[4]) const
+    {
+        generic_fetch(*this, tid, m0, n0, r0, rend, ra, rb);
+    }
 };
 
 // column space, grad_w:  C[o, k] = sum_{p=(n,l)} go[n,o,l] * dw[idx(x[n,k,l])]
@@ -96,6 +124,11 @@ struct ColGradW {
     __device__ void store(int o, int k, float v) const
     {
         atomicAdd(gw + (w_ok ? static_cast<long long>(o) * K + k : static_cast<long long>(k) * O + o), v);
+    }
+    __device__ void prep(int, int, int) {}
+    __device__ void fetch(int tid, int m0, int n0, int r0, int rend, float (&ra)[4], float (&rb)[4]) const
+    {
+        generic_fetch(*this, tid, m0, n0, r0, rend, ra, rb);
     }
 };
 
@@ -139,6 +172,60 @@ struct ConvGradX {
         const unsigned n = fdiv(m, divHW);
         const unsigned hw = m - n * (g.H * g.W);
         gx[(static_cast<long long>(n) * g.C + c) * (g.H * g.W) + hw] = v;
+    }
+    // Every thread fetches for ONE image pixel m and ONE input channel c (element e = tid + 256 q has
+    // m = m0 + (tid & 127), r = r0 + (tid >> 7) + 2 q), so the pixel's decomposition is done once per block tile
+    // and the (o, i, j) decomposition of r once per slot, shared by the A and the B element.
+    const float* go_n;        // &go[n, 0, 0, 0] of this thread's pixel
+    int hp, wp;               // h + PH, w + PW (or a large negative value when m is past the end)
+    int ckk;                  // c * KH * KW, or -1 when c is past the end
+    __device__ void prep(int tid, int m0, int n0)
+    {
+        const int m = m0 + (tid & 127);
+        hp = wp = -(1 << 28);
+        go_n = go;
+        if (m < M()) {
+            const unsigned n = fdiv(m, divHW);
+            const unsigned hw = m - n * (g.H * g.W);
+            const unsigned h = fdiv(hw, divW);
+            hp = static_cast<int>(h) + g.PH;
+            wp = static_cast<int>(hw - h * g.W) + g.PW;
+            go_n = go + static_cast<long long>(n) * O * g.OH * g.OW;
+        }
+        const int c = n0 + (tid & 127);
+        ckk = c < g.C ? c * (g.KH * g.KW) : -1;
+    }
+    __device__ void fetch(int tid, int, int, int r0, int rend, float (&ra)[4], float (&rb)[4]) const
+    {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int r = r0 + (tid >> 7) + 2 * q;
+            float av = 0.0f, bv = 0.0f;
+            if (r < rend) {
+                const unsigned o = fdiv(r, divKK);
+                const unsigned ij = r - o * (g.KH * g.KW);
+                const unsigned i = fdiv(ij, divKW);
+                const unsigned j = ij - i * g.KW;
+                const int th = hp - static_cast<int>(i) * g.DH;
+                const int tw = wp - static_cast<int>(j) * g.DW;
+                if (th >= 0 && tw >= 0) {
+                    unsigned oh = th, ow = tw;
+                    bool hit = true;
+                    if (g.SH != 1 || g.SW != 1) {
+                        oh = fdiv(th, divSH); ow = fdiv(tw, divSW);
+                        hit = oh * g.SH == static_cast<unsigned>(th) && ow * g.SW == static_cast<unsigned>(tw);
+                    }
+                    if (hit && oh < static_cast<unsigned>(g.OH) && ow < static_cast<unsigned>(g.OW))
+                        av = __ldg(go_n + (static_cast<long long>(o) * g.OH + oh) * g.OW + ow);
+                }
+                if (ckk >= 0) {
+                    bv = __ldg(dx + __ldg(widx + static_cast<long long>(o) * K + ckk + ij));
+                    if (gs != nullptr) bv *= __ldg(gs + o);
+                }
+            }
+            ra[q] = av;
+            rb[q] = bv;
+        }
     }
 };
 
@@ -185,20 +272,255 @@ struct ConvGradW {
         if (gs != nullptr) v *= __ldg(gs + o);
         atomicAdd(gw + static_cast<long long>(o) * K + k, v);
     }
+    // Every thread fetches for ONE output pixel p = r0 + (tid & 7) per slice and for four fixed channels
+    // o = m0 + (tid >> 3) + 32 q and four fixed taps k = n0 + (tid >> 3) + 32 q: the tap decompositions are done
+    // once per block tile, the pixel decomposition once per slice.
+    int o_off[4];             // o * OH * OW, or -1 when o is past the end
+    int k_off[4];             // (c * H + (i*DH - PH)) * W + (j*DW - PW): offset of the tap from the pixel's window origin
+    short k_dh[4], k_dw[4];   // i*DH - PH, j*DW - PW; k_dh = -32768 when k is past the end
+    __device__ void prep(int tid, int m0, int n0)
+    {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int o = m0 + (tid >> 3) + 32 * q;
+            o_off[q] = o < O ? o * (g.OH * g.OW) : -1;
+            const int k = n0 + (tid >> 3) + 32 * q;
+            k_off[q] = 0; k_dh[q] = -32768; k_dw[q] = 0;
+            if (k < K) {
+                const unsigned c = fdiv(k, divKK);
+                const unsigned ij = k - c * (g.KH * g.KW);
+                const unsigned i = fdiv(ij, divKW);
+                const unsigned j = ij - i * g.KW;
+                const int dh = static_cast<int>(i) * g.DH - g.PH, dw_ = static_cast<int>(j) * g.DW - g.PW;
+                k_dh[q] = static_cast<short>(dh); k_dw[q] = static_cast<short>(dw_);
+                k_off[q] = (static_cast<int>(c) * g.H + dh) * g.W + dw_;
+            }
+        }
+    }
+    __device__ void fetch(int tid, int, int, int r0, int rend, float (&ra)[4], float (&rb)[4]) const
+    {
+        const int pp = r0 + (tid & 7);
+        if (pp >= rend) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { ra[q] = 0.0f; rb[q] = 0.0f; }
+            return;
+        }
+        const unsigned n = fdiv(pp, divL);
+        const unsigned l = pp - n * (g.OH * g.OW);
+        const unsigned oh = fdiv(l, divOW);
+        const int ih0 = static_cast<int>(oh) * g.SH, iw0 = static_cast<int>(l - oh * g.OW) * g.SW;
+        const float* go_p = go + static_cast<long long>(n) * O * (g.OH * g.OW) + l;
+        const long long x_p = static_cast<long long>(n) * g.C * g.H * g.W + static_cast<long long>(ih0) * g.W + iw0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            ra[q] = o_off[q] >= 0 ? __ldg(go_p + o_off[q]) : 0.0f;
+            float bv = 0.0f;
+            if (k_dh[q] != -32768) {
+                const int ih = ih0 + k_dh[q], iw = iw0 + k_dw[q];
+                int idx = pad_index;
+                if (static_cast<unsigned>(ih) < static_cast<unsigned>(g.H) && static_cast<unsigned>(iw) < static_cast<unsigned>(g.W))
+                    idx = index_rt(x, x_p + k_off[q], x_dtype);
+                bv = __ldg(dw + idx);
+            }
+            rb[q] = bv;
+        }
+    }
+};
+
+
+// ------------------------------------------------------------------------------------------------
+// Lean conv problems (32-bit offsets, branch-free operand fetch).  Used whenever every tensor has fewer
+// than 2^31 elements and the kernel window has at most 128 taps; the two descriptions above stay as the
+// general fallback.
+// ------------------------------------------------------------------------------------------------
+constexpr int kMaxTaps = 128;
+
+// image space, grad_x, tap-major and split by stride class.
+// A pixel (h, w) only receives from taps with (h + PH - i*DH) % SH == 0 and (w + PW - j*DW) % SW == 0, so the
+// pixels are grouped by class (a, b) = ((h + PH) % SH, (w + PW) % SW) = blockIdx.z and every block runs over
+// the taps of its class only: with stride 2 a 3 x 3 window costs 9/4 tap-passes per pixel instead of 9.
+// The contraction index runs tap-major, r = tap * O8 + o (O8 = O rounded up to the slice length), so one
+// slice of 8 belongs to one tap and the window arithmetic is done once per slice, not once per element.
+struct ConvGradXTaps {
+    const float* go; const uint8_t* widx; const float* dx; const float* gs; float* gx;
+    int Nb, O, K, O8; ConvGeom g;
+    FastDiv divSH, divSW;
+    static constexpr bool kAtomic = false, kARFast = false, kBRFast = false;
+    // block state
+    int Mc, Hc, Wc, h0, w0, ntaps;
+    // thread state
+    int hp, wp, go_n, ckk, tap, o0;
+    __device__ int M() const { return Mc; }
+    __device__ int N() const { return g.C; }
+    __device__ void setup(int zz, int, int& rbeg, int& rend)
+    {
+        __shared__ int s_dh[kMaxTaps], s_dw[kMaxTaps], s_ij[kMaxTaps], s_n;
+        const int a = zz / g.SW, b = zz - a * g.SW;
+        h0 = ((a - g.PH) % g.SH + g.SH) % g.SH;            // first row of the class
+        w0 = ((b - g.PW) % g.SW + g.SW) % g.SW;
+        Hc = h0 < g.H ? (g.H - h0 + g.SH - 1) / g.SH : 0;
+        Wc = w0 < g.W ? (g.W - w0 + g.SW - 1) / g.SW : 0;
+        Mc = Nb * Hc * Wc;
+        if (threadIdx.x == 0) {
+            int n = 0;
+            for (int i = 0; i < g.KH; ++i) {
+                if (((a - i * g.DH) % g.SH + g.SH) % g.SH != 0) continue;
+                for (int j = 0; j < g.KW; ++j) {
+                    if (((b - j * g.DW) % g.SW + g.SW) % g.SW != 0) continue;
+                    s_dh[n] = i * g.DH; s_dw[n] = j * g.DW; s_ij[n] = i * g.KW + j; ++n;
+                }
+            }
+            s_n = n;
+        }
+        __syncthreads();
+        ntaps = s_n;
+        tap_dh = s_dh; tap_dw = s_dw; tap_ij = s_ij;
+        rbeg = 0; rend = ntaps * O8;
+    }
+    const int* tap_dh; const int* tap_dw; const int* tap_ij;
+    __device__ void pixel_of(int m, int& n, int& h, int& w) const
+    {
+        const int hw = Hc * Wc;
+        n = m / hw;
+        const int rem = m - n * hw;
+        const int t = rem / Wc;
+        h = h0 + g.SH * t;
+        w = w0 + g.SW * (rem - t * Wc);
+    }
+    __device__ void prep(int tid, int m0, int n0)
+    {
+        const int m = m0 + (tid & 127);
+        hp = wp = -(1 << 28);
+        go_n = 0;
+        if (m < Mc) {
+            int n, h, w;
+            pixel_of(m, n, h, w);
+            hp = h + g.PH; wp = w + g.PW;
+            go_n = n * O * g.OH * g.OW;
+        }
+        const int c = n0 + (tid & 127);
+        ckk = c < g.C ? c * (g.KH * g.KW) : -1;
+        tap = 0; o0 = 0;
+    }
+    // called for consecutive slices r0 = 0, 8, 16, ...
+    __device__ void fetch(int tid, int, int, int, int, float (&ra)[4], float (&rb)[4])
+    {
+        const int th = hp - tap_dh[tap], tw = wp - tap_dw[tap], ij = tap_ij[tap];
+        unsigned oh = th, ow = tw;
+        if (g.SH != 1) oh = fdiv(th < 0 ? 0 : th, divSH);
+        if (g.SW != 1) ow = fdiv(tw < 0 ? 0 : tw, divSW);
+        const bool hit = th >= 0 && tw >= 0 && oh < static_cast<unsigned>(g.OH) && ow < static_cast<unsigned>(g.OW);
+        const int a_off = hit ? go_n + static_cast<int>(oh) * g.OW + static_cast<int>(ow) : 0;
+        const int ohw = g.OH * g.OW;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int o = o0 + (tid >> 7) + 2 * q;
+            const bool o_ok = o < O;
+            const float av = __ldg(go + (hit && o_ok ? a_off + o * ohw : 0));
+            ra[q] = hit && o_ok ? av : 0.0f;
+            const bool b_ok = o_ok && ckk >= 0;
+            const int wi = __ldg(widx + (b_ok ? o * K + ckk + ij : 0));
+            float bv = __ldg(dx + wi);
+            if (gs != nullptr) bv *= __ldg(gs + (o_ok ? o : 0));
+            rb[q] = b_ok ? bv : 0.0f;
+        }
+        o0 += TK;
+        if (o0 >= O8) { o0 = 0; ++tap; }
+    }
+    __device__ void store(int m, int c, float v) const
+    {
+        int n, h, w;
+        pixel_of(m, n, h, w);
+        gx[((n * g.C + c) * g.H + h) * g.W + w] = v;
+    }
+};
+
+// image space, grad_w with the pixel decomposition done once per slice, 32-bit offsets and the operand type
+// of the saved image fixed at compile time.
+template <int XDT>
+struct ConvGradWLean {
+    const float* go; const void* x; const float* dw; const float* gs; float* gw;
+    int O, K, pad_index; long long P; ConvGeom g;
+    FastDiv divL, divOW, divKK, divKW;
+    static constexpr bool kAtomic = true, kARFast = true, kBRFast = true;
+    int o_off[4], k_off[4], k_dhw[4];       // k_dhw: (i*DH - PH) in the high half, (j*DW - PW) in the low half
+    unsigned ok_mask;                       // bit q: channel slot q valid; bit 4 + q: tap slot q valid
+    __device__ int M() const { return O; }
+    __device__ int N() const { return K; }
+    __device__ void setup(int zz, int nz, int& rbeg, int& rend)
+    {
+        const long long per = ((P + nz - 1) / nz + TK - 1) / TK * TK;
+        const long long b0 = per * zz;
+        rbeg = static_cast<int>(b0 < P ? b0 : P);
+        rend = static_cast<int>(b0 + per < P ? b0 + per : P);
+    }
+    __device__ void prep(int tid, int m0, int n0)
+    {
+        ok_mask = 0u;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int o = m0 + (tid >> 3) + 32 * q;
+            o_off[q] = o < O ? o * (g.OH * g.OW) : 0;
+            if (o < O) ok_mask |= 1u << q;
+            const int k = n0 + (tid >> 3) + 32 * q;
+            k_off[q] = 0; k_dhw[q] = 0;
+            if (k < K) {
+                const unsigned c = fdiv(k, divKK);
+                const unsigned ij = k - c * (g.KH * g.KW);
+                const unsigned i = fdiv(ij, divKW);
+                const unsigned j = ij - i * g.KW;
+                const int dh = static_cast<int>(i) * g.DH - g.PH, dw_ = static_cast<int>(j) * g.DW - g.PW;
+                k_dhw[q] = (dh << 16) | (dw_ & 0xffff);
+                k_off[q] = (static_cast<int>(c) * g.H + dh) * g.W + dw_;
+                ok_mask |= 16u << q;
+            }
+        }
+    }
+    __device__ void fetch(int tid, int, int, int r0, int rend, float (&ra)[4], float (&rb)[4]) const
+    {
+        const int pp = r0 + (tid & 7);
+        const bool p_ok = pp < rend;
+        const unsigned pc = p_ok ? pp : 0;
+        const unsigned n = fdiv(pc, divL);
+        const unsigned l = pc - n * (g.OH * g.OW);
+        const unsigned oh = fdiv(l, divOW);
+        const int ih0 = static_cast<int>(oh) * g.SH, iw0 = static_cast<int>(l - oh * g.OW) * g.SW;
+        const int go_off = static_cast<int>(n) * O * (g.OH * g.OW) + static_cast<int>(l);
+        const int x_off = (static_cast<int>(n) * g.C * g.H + ih0) * g.W + iw0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const bool a_ok = p_ok && ((ok_mask >> q) & 1u);
+            const float av = __ldg(go + (a_ok ? go_off + o_off[q] : 0));
+            ra[q] = a_ok ? av : 0.0f;
+            const bool b_ok = p_ok && ((ok_mask >> (4 + q)) & 1u);
+            const int ih = ih0 + (k_dhw[q] >> 16), iw = iw0 + static_cast<short>(k_dhw[q] & 0xffff);
+            const bool inside = b_ok && static_cast<unsigned>(ih) < static_cast<unsigned>(g.H) &&
+                                static_cast<unsigned>(iw) < static_cast<unsigned>(g.W);
+            const int xi = index_of<XDT>(x, inside ? x_off + k_off[q] : 0);
+            const float bv = __ldg(dw + (inside ? xi : pad_index));
+            rb[q] = b_ok ? bv : 0.0f;
+        }
+    }
+    __device__ void store(int o, int k, float v) const
+    {
+        if (gs != nullptr) v *= __ldg(gs + o);
+        atomicAdd(gw + o * K + k, v);
+    }
 };
 
 // ------------------------------------------------------------------------------------------------
 // the tiled kernel
 // ------------------------------------------------------------------------------------------------
 template <class Prob>
-__global__ void __launch_bounds__(256) fused_sgemm_kernel(const Prob prob_in)
+__global__ void __launch_bounds__(256, 2) fused_sgemm_kernel(const Prob prob_in)
 {
-    __shared__ float As[2][TK][PITCH];
-    __shared__ float Bs[2][TK][PITCH];
+    __shared__ __align__(16) float As[2][TK][PITCH];
+    __shared__ __align__(16) float Bs[2][TK][PITCH];
     Prob p = prob_in;
     int rbeg, rend;
     p.setup(blockIdx.z, gridDim.z, rbeg, rend);
     const int M = p.M(), N = p.N();
+    if (static_cast<int>(blockIdx.x) * TM >= M) return;        // stride classes differ in size: surplus blocks leave
     const int tid = threadIdx.x;
     const int m0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
     const int tx = tid & 15, ty = tid >> 4;
@@ -213,20 +535,8 @@ __global__ void __launch_bounds__(256) fused_sgemm_kernel(const Prob prob_in)
     }
 
     float ra[4], rb[4];
-    auto fetch = [&](int r0) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int e = tid + 256 * q;
-            const int ml = Prob::kARFast ? (e >> 3) : (e & 127);
-            const int rl = Prob::kARFast ? (e & 7) : (e >> 7);
-            const int m = m0 + ml, r = r0 + rl;
-            ra[q] = (m < M && r < rend) ? p.a(m, r) : 0.0f;
-            const int nl = Prob::kBRFast ? (e >> 3) : (e & 127);
-            const int sl = Prob::kBRFast ? (e & 7) : (e >> 7);
-            const int n = n0 + nl, s = r0 + sl;
-            rb[q] = (n < N && s < rend) ? p.b(s, n) : 0.0f;
-        }
-    };
+    p.prep(tid, m0, n0);
+    auto fetch = [&](int r0) { p.fetch(tid, m0, n0, r0, rend, ra, rb); };
     auto stash = [&](int buf) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -353,19 +663,35 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
     const long long Mx = static_cast<long long>(N) * H * W;
     const long long P = static_cast<long long>(N) * OH * OW;
     ATB_REQUIRE(Mx < 2147483647LL && P < 2147483647LL && K < 2147483647LL &&
-                static_cast<long long>(O) * kh * kw < 2147483647LL, "dimensions too large");
+                static_cast<long long>(O) * kh * kw < 2147483647LL &&
+                static_cast<long long>(C) * H * W < 2147483647LL && static_cast<long long>(O) * OH * OW < 2147483647LL,
+                "dimensions too large");
+    ATB_REQUIRE(static_cast<long long>(kh) * dh < 30000 && static_cast<long long>(kw) * dw_ < 30000 && ph < 30000 && pw < 30000,
+                "kernel extent or padding too large");
+    // every tensor addressable with 32-bit offsets and a window the tap table can hold: the lean problems apply
+    const bool lean = static_cast<long long>(N) * O * OH * OW < 2147483647LL && Mx * C < 2147483647LL &&
+                      static_cast<long long>(O) * K < 2147483647LL && kh * kw <= kMaxTaps;
     int rc = ATB_OK;
     if (grad_x != nullptr && Mx * C > 0) {
         if (O == 0) {
             zero_kernel<<<grid_for(Mx * C, 256, 4096), 256, 0, s>>>(grad_x, Mx * C);
         } else {
             ATB_REQUIRE(go && widx && dx, "null pointer");
-            ConvGradX p{go, widx, dx, go_scale, grad_x, N, O, static_cast<int>(K), g,
-                        make_fastdiv(H * W), make_fastdiv(W), make_fastdiv(kh * kw), make_fastdiv(kw),
-                        make_fastdiv(sh), make_fastdiv(sw)};
-            dim3 grid(ceil_div(Mx, TM), ceil_div(C, TN), 1);
-            ATB_REQUIRE(grid.y <= 65535, "C too large");
-            fused_sgemm_kernel<ConvGradX><<<grid, 256, 0, s>>>(p);
+            if (lean && sh * sw <= 64) {
+                ConvGradXTaps p{go, widx, dx, go_scale, grad_x, N, O, static_cast<int>(K), (O + TK - 1) / TK * TK, g,
+                                make_fastdiv(sh), make_fastdiv(sw)};
+                const long long max_class = static_cast<long long>(N) * ((H + sh - 1) / sh) * ((W + sw - 1) / sw);
+                dim3 grid(ceil_div(max_class, TM), ceil_div(C, TN), sh * sw);
+                ATB_REQUIRE(grid.y <= 65535, "C too large");
+                fused_sgemm_kernel<ConvGradXTaps><<<grid, 256, 0, s>>>(p);
+            } else {
+                ConvGradX p{go, widx, dx, go_scale, grad_x, N, O, static_cast<int>(K), g,
+                            make_fastdiv(H * W), make_fastdiv(W), make_fastdiv(kh * kw), make_fastdiv(kw),
+                            make_fastdiv(sh), make_fastdiv(sw)};
+                dim3 grid(ceil_div(Mx, TM), ceil_div(C, TN), 1);
+                ATB_REQUIRE(grid.y <= 65535, "C too large");
+                fused_sgemm_kernel<ConvGradX><<<grid, 256, 0, s>>>(p);
+            }
         }
         rc = check_launch("conv grad_x");
         if (rc != ATB_OK) return rc;
@@ -376,12 +702,26 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
         if (rc != ATB_OK) return rc;
         if (P > 0) {
             ATB_REQUIRE(go && x && dw, "null pointer");
-            ConvGradW p{go, x, x_dtype, dw, go_scale, grad_w, O, static_cast<int>(K), pad_index, P, g,
-                        make_fastdiv(OH * OW), make_fastdiv(OW), make_fastdiv(kh * kw), make_fastdiv(kw)};
             dim3 grid(ceil_div(O, TM), ceil_div(K, TN), 1);
             ATB_REQUIRE(grid.y <= 65535, "K too large");
             grid.z = split_factor(static_cast<long long>(grid.x) * grid.y, P);
-            fused_sgemm_kernel<ConvGradW><<<grid, 256, 0, s>>>(p);
+            if (lean) {
+                const FastDiv dL = make_fastdiv(OH * OW), dOW = make_fastdiv(OW), dKK = make_fastdiv(kh * kw), dKW = make_fastdiv(kw);
+                if (x_dtype == ATB_U8) {
+                    ConvGradWLean<ATB_U8> p{go, x, dw, go_scale, grad_w, O, static_cast<int>(K), pad_index, P, g, dL, dOW, dKK, dKW};
+                    fused_sgemm_kernel<ConvGradWLean<ATB_U8>><<<grid, 256, 0, s>>>(p);
+                } else if (x_dtype == ATB_I8) {
+                    ConvGradWLean<ATB_I8> p{go, x, dw, go_scale, grad_w, O, static_cast<int>(K), pad_index, P, g, dL, dOW, dKK, dKW};
+                    fused_sgemm_kernel<ConvGradWLean<ATB_I8>><<<grid, 256, 0, s>>>(p);
+                } else {
+                    ConvGradWLean<ATB_F32> p{go, x, dw, go_scale, grad_w, O, static_cast<int>(K), pad_index, P, g, dL, dOW, dKK, dKW};
+                    fused_sgemm_kernel<ConvGradWLean<ATB_F32>><<<grid, 256, 0, s>>>(p);
+                }
+            } else {
+                ConvGradW p{go, x, x_dtype, dw, go_scale, grad_w, O, static_cast<int>(K), pad_index, P, g,
+                            make_fastdiv(OH * OW), make_fastdiv(OW), make_fastdiv(kh * kw), make_fastdiv(kw)};
+                fused_sgemm_kernel<ConvGradW><<<grid, 256, 0, s>>>(p);
+            }
             rc = check_launch("conv grad_w");
         }
     }

@@ -679,11 +679,18 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
 template <int NW, bool DP2A>
 static int launch_one(dim3 grid, const GemmArgs& a, cudaStream_t stream)
 {
-    static bool attr_set = false;      // the opt-in shared-memory size is a per-function attribute
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(lut_gemm_kernel<NW, DP2A>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    // the opt-in shared-memory size is an attribute of the function on ONE device: set it once per device
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        set_error("cudaGetDevice: %s", e != cudaSuccess ? cudaGetErrorString(e) : "device index out of range");
+        return ATB_ERR_CUDA;
+    }
+    if (!attr_set[dev]) {
+        e = cudaFuncSetAttribute(lut_gemm_kernel<NW, DP2A>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
-        attr_set = true;
+        attr_set[dev] = true;
     }
     lut_gemm_kernel<NW, DP2A><<<grid, NW * 32, kSmemTotal, stream>>>(a);
     return ATB_OK;
