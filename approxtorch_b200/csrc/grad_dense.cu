@@ -42,7 +42,7 @@ __device__ __forceinline__ int index_rt(const void* base, long long i, int dtype
     return index_of<ATB_F32>(base, i);
 }
 
-constexpr int TM = 128, TN = 128, TK = 8, PITCH = 132;
+constexpr int TK = 8;        // contraction slice per shared-memory stage
 
 // ------------------------------------------------------------------------------------------------
 // problem descriptions: a(m, r), b(r, n), store(m, n, v)
@@ -511,25 +511,30 @@ struct ConvGradWLean {
 // ------------------------------------------------------------------------------------------------
 // the tiled kernel
 // ------------------------------------------------------------------------------------------------
-template <class Prob>
+// TMv x TNv outputs per block (128 or 64 each): 16 x 16 threads, (TMv / 16) x (TNv / 16) outputs per thread.  The
+// operand fetch always covers 128 rows / columns; with a 64-wide tile the upper half is not kept (the
+// problems mask it out anyway when M or N is at most 64, which is when the launcher picks the narrow tile).
+template <class Prob, int TMv, int TNv>
 __global__ void __launch_bounds__(256, 2) fused_sgemm_kernel(const Prob prob_in)
 {
-    __shared__ __align__(16) float As[2][TK][PITCH];
-    __shared__ __align__(16) float Bs[2][TK][PITCH];
+    static_assert((TMv == 64 || TMv == 128) && (TNv == 64 || TNv == 128), "tile sides are 64 or 128");
+    constexpr int RM = TMv / 16, RN = TNv / 16;
+    __shared__ __align__(16) float As[2][TK][TMv + 4];
+    __shared__ __align__(16) float Bs[2][TK][TNv + 4];
     Prob p = prob_in;
     int rbeg, rend;
     p.setup(blockIdx.z, gridDim.z, rbeg, rend);
     const int M = p.M(), N = p.N();
-    if (static_cast<int>(blockIdx.x) * TM >= M) return;        // stride classes differ in size: surplus blocks leave
+    if (static_cast<int>(blockIdx.x) * TMv >= M) return;        // stride classes differ in size: surplus blocks leave
     const int tid = threadIdx.x;
-    const int m0 = blockIdx.x * TM, n0 = blockIdx.y * TN;
+    const int m0 = blockIdx.x * TMv, n0 = blockIdx.y * TNv;
     const int tx = tid & 15, ty = tid >> 4;
 
-    float acc[8][8];
+    float acc[RM][RN];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < RM; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < RN; ++j) acc[i][j] = 0.0f;
     if (rbeg >= rend) {
         if (Prob::kAtomic) return;     // nothing to add
     }
@@ -543,10 +548,10 @@ __global__ void __launch_bounds__(256, 2) fused_sgemm_kernel(const Prob prob_in)
             const int e = tid + 256 * q;
             const int ml = Prob::kARFast ? (e >> 3) : (e & 127);
             const int rl = Prob::kARFast ? (e & 7) : (e >> 7);
-            As[buf][rl][ml] = ra[q];
+            if (TMv == 128 || ml < TMv) As[buf][rl][ml] = ra[q];
             const int nl = Prob::kBRFast ? (e >> 3) : (e & 127);
             const int sl = Prob::kBRFast ? (e & 7) : (e >> 7);
-            Bs[buf][sl][nl] = rb[q];
+            if (TNv == 128 || nl < TNv) Bs[buf][sl][nl] = rb[q];
         }
     };
 
@@ -558,30 +563,54 @@ __global__ void __launch_bounds__(256, 2) fused_sgemm_kernel(const Prob prob_in)
         if (t + 1 < ntiles) fetch(rbeg + (t + 1) * TK);
 #pragma unroll
         for (int kk = 0; kk < TK; ++kk) {
+            float av[RM], bv[RN];
             const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
-            const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
+            av[0] = a0.x; av[1] = a0.y; av[2] = a0.z; av[3] = a0.w;
+            if constexpr (RM == 8) {
+                const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
+                av[4] = a1.x; av[5] = a1.y; av[6] = a1.z; av[7] = a1.w;
+            }
             const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
-            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
-            const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            bv[0] = b0.x; bv[1] = b0.y; bv[2] = b0.z; bv[3] = b0.w;
+            if constexpr (RN == 8) {
+                const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
+                bv[4] = b1.x; bv[5] = b1.y; bv[6] = b1.z; bv[7] = b1.w;
+            }
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < RM; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+                for (int j = 0; j < RN; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
         }
         if (t + 1 < ntiles) stash(buf ^ 1);
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < RM; ++i) {
         const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
         if (m >= M) continue;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < RN; ++j) {
             const int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
             if (n < N) p.store(m, n, acc[i][j]);
         }
     }
+}
+
+static long long sgemm_tiles(long long M, long long N)
+{
+    return ((M + (M <= 64 ? 63 : 127)) / (M <= 64 ? 64 : 128)) * ((N + (N <= 64 ? 63 : 127)) / (N <= 64 ? 64 : 128));
+}
+
+// narrow tiles when the whole M (or N) extent fits in 64
+template <class Prob>
+static void launch_sgemm(const Prob& p, long long M, long long N, unsigned gz, cudaStream_t s)
+{
+    const bool m64 = M <= 64, n64 = N <= 64;
+    dim3 grid(ceil_div(M, m64 ? 64 : 128), ceil_div(N, n64 ? 64 : 128), gz);
+    if (m64 && n64) fused_sgemm_kernel<Prob, 64, 64><<<grid, 256, 0, s>>>(p);
+    else if (m64) fused_sgemm_kernel<Prob, 64, 128><<<grid, 256, 0, s>>>(p);
+    else if (n64) fused_sgemm_kernel<Prob, 128, 64><<<grid, 256, 0, s>>>(p);
+    else fused_sgemm_kernel<Prob, 128, 128><<<grid, 256, 0, s>>>(p);
 }
 
 __global__ void zero_kernel(float* p, long long n)
@@ -622,9 +651,8 @@ extern "C" int atb_lre_bwd(const float* go, const void* x, int x_dtype, const vo
             ATB_REQUIRE(go && w && dx, "null pointer");
             ATB_REQUIRE(N <= 65535, "batch above 65535 is not supported");
             ColGradX p{go, w, w_dtype, w_ok_layout, dx, grad_x, K, L, O, 0};
-            dim3 grid(ceil_div(K, TM), ceil_div(L, TN), N);
-            ATB_REQUIRE(grid.y <= 65535, "L too large");
-            fused_sgemm_kernel<ColGradX><<<grid, 256, 0, s>>>(p);
+            ATB_REQUIRE(ceil_div(L, 64) <= 65535, "L too large");
+            launch_sgemm(p, K, L, N, s);
         }
         rc = check_launch("lre grad_x");
         if (rc != ATB_OK) return rc;
@@ -636,10 +664,8 @@ extern "C" int atb_lre_bwd(const float* go, const void* x, int x_dtype, const vo
         if (P > 0) {
             ATB_REQUIRE(go && x && dw, "null pointer");
             ColGradW p{go, x, x_dtype, dw, grad_w, w_ok_layout, K, L, O, P, make_fastdiv(L)};
-            dim3 grid(ceil_div(O, TM), ceil_div(K, TN), 1);
-            ATB_REQUIRE(grid.y <= 65535, "K too large");
-            grid.z = split_factor(static_cast<long long>(grid.x) * grid.y, P);
-            fused_sgemm_kernel<ColGradW><<<grid, 256, 0, s>>>(p);
+            ATB_REQUIRE(ceil_div(K, 64) <= 65535, "K too large");
+            launch_sgemm(p, O, K, split_factor(sgemm_tiles(O, K), P), s);
             rc = check_launch("lre grad_w");
         }
     }
@@ -681,16 +707,14 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
                 ConvGradXTaps p{go, widx, dx, go_scale, grad_x, N, O, static_cast<int>(K), (O + TK - 1) / TK * TK, g,
                                 make_fastdiv(sh), make_fastdiv(sw)};
                 const long long max_class = static_cast<long long>(N) * ((H + sh - 1) / sh) * ((W + sw - 1) / sw);
-                dim3 grid(ceil_div(max_class, TM), ceil_div(C, TN), sh * sw);
-                ATB_REQUIRE(grid.y <= 65535, "C too large");
-                fused_sgemm_kernel<ConvGradXTaps><<<grid, 256, 0, s>>>(p);
+                ATB_REQUIRE(ceil_div(C, 64) <= 65535, "C too large");
+                launch_sgemm(p, max_class, C, sh * sw, s);
             } else {
                 ConvGradX p{go, widx, dx, go_scale, grad_x, N, O, static_cast<int>(K), g,
                             make_fastdiv(H * W), make_fastdiv(W), make_fastdiv(kh * kw), make_fastdiv(kw),
                             make_fastdiv(sh), make_fastdiv(sw)};
-                dim3 grid(ceil_div(Mx, TM), ceil_div(C, TN), 1);
-                ATB_REQUIRE(grid.y <= 65535, "C too large");
-                fused_sgemm_kernel<ConvGradX><<<grid, 256, 0, s>>>(p);
+                ATB_REQUIRE(ceil_div(C, 64) <= 65535, "C too large");
+                launch_sgemm(p, Mx, C, 1, s);
             }
         }
         rc = check_launch("conv grad_x");
@@ -702,25 +726,24 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
         if (rc != ATB_OK) return rc;
         if (P > 0) {
             ATB_REQUIRE(go && x && dw, "null pointer");
-            dim3 grid(ceil_div(O, TM), ceil_div(K, TN), 1);
-            ATB_REQUIRE(grid.y <= 65535, "K too large");
-            grid.z = split_factor(static_cast<long long>(grid.x) * grid.y, P);
+            ATB_REQUIRE(ceil_div(K, 64) <= 65535, "K too large");
+            const unsigned gz = split_factor(sgemm_tiles(O, K), P);
             if (lean) {
                 const FastDiv dL = make_fastdiv(OH * OW), dOW = make_fastdiv(OW), dKK = make_fastdiv(kh * kw), dKW = make_fastdiv(kw);
                 if (x_dtype == ATB_U8) {
                     ConvGradWLean<ATB_U8> p{go, x, dw, go_scale, grad_w, O, static_cast<int>(K), pad_index, P, g, dL, dOW, dKK, dKW};
-                    fused_sgemm_kernel<ConvGradWLean<ATB_U8>><<<grid, 256, 0, s>>>(p);
+                    launch_sgemm(p, O, K, gz, s);
                 } else if (x_dtype == ATB_I8) {
                     ConvGradWLean<ATB_I8> p{go, x, dw, go_scale, grad_w, O, static_cast<int>(K), pad_index, P, g, dL, dOW, dKK, dKW};
-                    fused_sgemm_kernel<ConvGradWLean<ATB_I8>><<<grid, 256, 0, s>>>(p);
+                    launch_sgemm(p, O, K, gz, s);
                 } else {
                     ConvGradWLean<ATB_F32> p{go, x, dw, go_scale, grad_w, O, static_cast<int>(K), pad_index, P, g, dL, dOW, dKK, dKW};
-                    fused_sgemm_kernel<ConvGradWLean<ATB_F32>><<<grid, 256, 0, s>>>(p);
+                    launch_sgemm(p, O, K, gz, s);
                 }
             } else {
                 ConvGradW p{go, x, x_dtype, dw, go_scale, grad_w, O, static_cast<int>(K), pad_index, P, g,
                             make_fastdiv(OH * OW), make_fastdiv(OW), make_fastdiv(kh * kw), make_fastdiv(kw)};
-                fused_sgemm_kernel<ConvGradW><<<grid, 256, 0, s>>>(p);
+                launch_sgemm(p, O, K, gz, s);
             }
             rc = check_launch("conv grad_w");
         }
