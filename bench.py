@@ -366,13 +366,17 @@ def run_gpu_arm(args):
     b_in = torch.empty_like(b_dev)
 
     copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    compute = [torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)]
 
     def step_e2e():
         """All 16 items through the public operator; H2D of item i+1 and D2H of item i-1 overlap the compute of
-        item i (three streams, events between them).  Everything is joined back into the current stream."""
+        item i, and consecutive items alternate between two compute streams so that the next item's blocks fill
+        the SMs the current item's last wave leaves idle.  Everything is joined back into the current stream."""
         main = torch.cuda.current_stream(dev)
         copy_in.wait_stream(main)
         copy_out.wait_stream(main)
+        for c in compute:
+            c.wait_stream(main)
         ready = []
         with torch.cuda.stream(copy_in):
             for i in range(BATCH):
@@ -382,15 +386,19 @@ def run_gpu_arm(args):
                 ev_in.record(copy_in)
                 ready.append(ev_in)
         for i in range(BATCH):
-            main.wait_event(ready[i])
-            yi = ops.gemm_fake_int8_claude(a_in[i], b_in[i], lut)        # the reference's public operator
+            c = compute[i & 1]
+            c.wait_event(ready[i])
+            with torch.cuda.stream(c):
+                yi = ops.gemm_fake_int8_claude(a_in[i], b_in[i], lut)        # the reference's public operator
             done = torch.cuda.Event()
-            done.record(main)
+            done.record(c)
             copy_out.wait_event(done)
             with torch.cuda.stream(copy_out):
                 y_host[i].copy_(yi, non_blocking=True)
             yi.record_stream(copy_out)
         main.wait_stream(copy_out)
+        for c in compute:
+            main.wait_stream(c)
     for _ in range(2):
         step_e2e()
     barrier()
