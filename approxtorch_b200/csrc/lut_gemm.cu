@@ -76,18 +76,43 @@ struct GemmArgs {
     const int* wsum;
 };
 
-__device__ __forceinline__ float finalize_output(double total, long long xsum, int o, const GemmArgs& a)
+// Epilogue arithmetic.  Integer tables: the sum, the zero-point terms and their combination are exact integers,
+// converted to fp32 once (round to nearest even), then scaled and shifted.  Without zero points the sum fits
+// 32 bits (|sum| <= 32768 * K, K <= 32768), with them it needs 64.
+__device__ __forceinline__ float scale_shift(float v, int o, const GemmArgs& a)
 {
+    if (a.alpha != nullptr) v = v * __ldg(a.alpha + o);
+    if (a.beta != nullptr) v = v + __ldg(a.beta + o);
+    return v;
+}
+
+__device__ __forceinline__ float finalize_output(long long total, long long xsum, int o, const GemmArgs& a)
+{
+    float v;
     if (a.zero_x != nullptr) {
         const long long zx = llrintf(__ldg(a.zero_x));
         const long long zw = llrintf(__ldg(a.zero_w + o));
         const long long ws = __ldg(a.wsum + o);
-        total += static_cast<double>(-zw * xsum - zx * ws + static_cast<long long>(a.K) * zx * zw);
+        v = __ll2float_rn(total - zw * xsum - zx * ws + static_cast<long long>(a.K) * zx * zw);
+    } else {
+        v = __int2float_rn(static_cast<int>(total));
     }
-    float v = static_cast<float>(total);
-    if (a.alpha != nullptr) v = v * __ldg(a.alpha + o);
-    if (a.beta != nullptr) v = v + __ldg(a.beta + o);
-    return v;
+    return scale_shift(v, o, a);
+}
+
+// Tables that are not 16-bit exact: the sum is already fp32; the zero-point terms (integers) are added in
+// double so that they are not rounded before the one conversion back to fp32.
+__device__ __forceinline__ float finalize_output(float total, long long xsum, int o, const GemmArgs& a)
+{
+    float v = total;
+    if (a.zero_x != nullptr) {
+        const long long zx = llrintf(__ldg(a.zero_x));
+        const long long zw = llrintf(__ldg(a.zero_w + o));
+        const long long ws = __ldg(a.wsum + o);
+        v = static_cast<float>(static_cast<double>(total) +
+                               static_cast<double>(-zw * xsum - zx * ws + static_cast<long long>(a.K) * zx * zw));
+    }
+    return scale_shift(v, o, a);
 }
 
 __device__ __forceinline__ long long output_offset(long long r, int o, const GemmArgs& a)
@@ -423,7 +448,7 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
         return static_cast<long long>(v) - remove;
     };
     write_tile<true>(a, smem, r0, r_end, c0, warp, lane, xsum,
-                     [&](int j, int t) { return static_cast<double>(total(j, t)); },
+                     [&](int j, int t) { return total(j, t); },
                      [&](int j, int t) { return static_cast<int>(total(j, t)); });
 }
 
@@ -470,7 +495,7 @@ __device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, 
         __syncthreads();
     }
     write_tile<false>(a, smem, r0, r_end, c0, warp, lane, xsum,
-               [&](int j, int t) { return static_cast<double>(acc[j][t]); },
+               [&](int j, int t) { return acc[j][t]; },
                [&](int j, int t) { return __float_as_int(acc[j][t]); });
 }
 
@@ -556,20 +581,20 @@ __global__ void lut_gemm_reduce_kernel(const GemmArgs a)
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const long long rs = i / a.O;
         const int o = static_cast<int>(i - rs * a.O);
-        double sum = 0.0;
-        if (cls == LUT_F32) {
-            float f = 0.0f;
-            for (int s = 0; s < a.splits; ++s) f += __int_as_float(a.scratch[static_cast<long long>(s) * total + i]);
-            sum = f;
-        } else {
-            long long t = 0;
-            for (int s = 0; s < a.splits; ++s) t += a.scratch[static_cast<long long>(s) * total + i];
-            sum = static_cast<double>(t);
-        }
         long long xs = 0;
         if (a.zero_x != nullptr)
             for (int s = 0; s < a.splits; ++s) xs += a.scratch[a.splits * total + static_cast<long long>(s) * a.srows + rs];
-        a.y[output_offset(a.srow0 + rs, o, a)] = finalize_output(sum, xs, o, a);
+        float v;
+        if (cls == LUT_F32) {
+            float f = 0.0f;
+            for (int s = 0; s < a.splits; ++s) f += __int_as_float(a.scratch[static_cast<long long>(s) * total + i]);
+            v = finalize_output(f, xs, o, a);
+        } else {
+            long long t = 0;
+            for (int s = 0; s < a.splits; ++s) t += a.scratch[static_cast<long long>(s) * total + i];
+            v = finalize_output(t, xs, o, a);
+        }
+        a.y[output_offset(a.srow0 + rs, o, a)] = v;
     }
 }
 
@@ -581,7 +606,7 @@ __global__ void lut_gemm_empty_k_kernel(const GemmArgs a)
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const long long r = i / a.O;
         const int o = static_cast<int>(i - r * a.O);
-        a.y[output_offset(r, o, a)] = finalize_output(0.0, 0, o, a);
+        a.y[output_offset(r, o, a)] = finalize_output(0LL, 0, o, a);
     }
 }
 
