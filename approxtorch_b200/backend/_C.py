@@ -63,7 +63,7 @@ _SIGNATURES = {
     "atb_lut_map": (_i, [_vp, _i, _vp, _vp, _ll, _vp]),
     "atb_lut_map_pad": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "atb_lre_bwd": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
-    "atb_lre_conv_bwd": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 13 + [_i, _vp]),
+    "atb_lre_conv_bwd": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 13 + [_i, _vp]),
     "atb_custom_bwd_dx": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "atb_custom_bwd_dw": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "atb_lut_dwconv_fwd": (_i, [_vp, _i, _vp, _vp, _vp] + [_i] * 12 + [_i, _vp]),

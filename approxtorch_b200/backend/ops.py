@@ -201,8 +201,10 @@ def quantize_weight(w: Tensor, scale: Tensor, zero_point: Tensor | None, qmin: i
 
 
 def lre_conv_backward(go: Tensor, x8: Tensor, w_idx: Tensor | None, dx: Tensor | None, dw: Tensor | None,
-                      geom, pad_index: int, go_scale: Tensor | None = None, need_x: bool = True, need_w: bool = True):
-    """Image-space STE/LRE backward: (grad wrt the quantised image [B,C,H,W], grad_w [O,K])."""
+                      geom, pad_index: int, go_scale: Tensor | None = None, need_x: bool = True, need_w: bool = True,
+                      w_zero: Tensor | None = None):
+    """Image-space STE/LRE backward: (grad wrt the quantised image [B,C,H,W], grad_w [O,K]).
+    pad_index 256 selects a 257th entry of ``dw``; ``w_zero[o]`` is subtracted from the mapped weight."""
     (kh, kw), (sh, sw), (ph, pw), (dh, dw_) = geom
     B, C, H, W = x8.shape
     go = go.contiguous()
@@ -211,7 +213,7 @@ def lre_conv_backward(go: Tensor, x8: Tensor, w_idx: Tensor | None, dx: Tensor |
     gw = torch.empty((O, C * kh * kw), dtype=torch.float32, device=go.device) if need_w else None
     with _Guard(go):
         _check(_lib.atb_lre_conv_bwd(_ptr(go), _ptr(x8), _DTYPE_CODE[x8.dtype], _ptr(w_idx), _ptr(dx), _ptr(dw),
-                                     _ptr(go_scale), _ptr(gx), _ptr(gw), B, C, H, W, O, kh, kw, sh, sw, ph, pw,
+                                     _ptr(go_scale), _ptr(w_zero), _ptr(gx), _ptr(gw), B, C, H, W, O, kh, kw, sh, sw, ph, pw,
                                      dh, dw_, pad_index, _stream(go)), "atb_lre_conv_bwd")
     return gx, gw
 

@@ -134,7 +134,7 @@ struct ColGradW {
 
 // image space, grad_x:  C[m=(n,h,w), c] = sum_{r=(o,i,j)} go[n,o,oh,ow] * gs[o] * dx[widx[o,(c,i,j)]]
 struct ConvGradX {
-    const float* go; const uint8_t* widx; const float* dx; const float* gs; float* gx;
+    const float* go; const uint8_t* widx; const float* dx; const float* gs; const float* wz; float* gx;
     int Nb, O, K; ConvGeom g;
     FastDiv divHW, divW, divKK, divKW, divSH, divSW;
     static constexpr bool kAtomic = false, kARFast = false, kBRFast = false;
@@ -164,6 +164,7 @@ struct ConvGradX {
         const unsigned o = fdiv(r, divKK);
         const unsigned ij = r - o * (g.KH * g.KW);
         float v = __ldg(dx + __ldg(widx + static_cast<long long>(o) * K + c * (g.KH * g.KW) + ij));
+        if (wz != nullptr) v -= __ldg(wz + o);
         if (gs != nullptr) v *= __ldg(gs + o);
         return v;
     }
@@ -220,6 +221,7 @@ struct ConvGradX {
                 }
                 if (ckk >= 0) {
                     bv = __ldg(dx + __ldg(widx + static_cast<long long>(o) * K + ckk + ij));
+                    if (wz != nullptr) bv -= __ldg(wz + o);
                     if (gs != nullptr) bv *= __ldg(gs + o);
                 }
             }
@@ -342,7 +344,7 @@ constexpr int kMaxTaps = 128;
 // The contraction index runs tap-major, r = tap * O8 + o (O8 = O rounded up to the slice length), so one
 // slice of 8 belongs to one tap and the window arithmetic is done once per slice, not once per element.
 struct ConvGradXTaps {
-    const float* go; const uint8_t* widx; const float* dx; const float* gs; float* gx;
+    const float* go; const uint8_t* widx; const float* dx; const float* gs; const float* wz; float* gx;
     int Nb, O, K, O8; ConvGeom g;
     FastDiv divSH, divSW;
     static constexpr bool kAtomic = false, kARFast = false, kBRFast = false;
@@ -421,6 +423,7 @@ struct ConvGradXTaps {
             const bool b_ok = o_ok && ckk >= 0;
             const int wi = __ldg(widx + (b_ok ? o * K + ckk + ij : 0));
             float bv = __ldg(dx + wi);
+            if (wz != nullptr) bv -= __ldg(wz + (o_ok ? o : 0));
             if (gs != nullptr) bv *= __ldg(gs + (o_ok ? o : 0));
             rb[q] = b_ok ? bv : 0.0f;
         }
@@ -673,14 +676,14 @@ extern "C" int atb_lre_bwd(const float* go, const void* x, int x_dtype, const vo
 }
 
 extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t* widx,
-                                const float* dx, const float* dw, const float* go_scale,
+                                const float* dx, const float* dw, const float* go_scale, const float* w_zero,
                                 float* grad_x, float* grad_w,
                                 int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
                                 int dh, int dw_, int pad_index, void* stream)
 {
     ATB_REQUIRE(N >= 0 && C >= 0 && H >= 0 && W >= 0 && O >= 0, "negative dimension");
     ATB_REQUIRE(x_dtype >= 0 && x_dtype <= 2, "bad dtype");
-    ATB_REQUIRE(pad_index >= 0 && pad_index <= 255, "pad_index out of range");
+    ATB_REQUIRE(pad_index >= 0 && pad_index <= 256, "pad_index out of range");
     int OH = 0, OW = 0;
     ATB_REQUIRE(conv_out_shape(H, W, kh, kw, sh, sw, ph, pw, dh, dw_, &OH, &OW), "conv geometry yields empty output");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -704,13 +707,13 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
         } else {
             ATB_REQUIRE(go && widx && dx, "null pointer");
             if (lean && sh * sw <= 64) {
-                ConvGradXTaps p{go, widx, dx, go_scale, grad_x, N, O, static_cast<int>(K), (O + TK - 1) / TK * TK, g,
+                ConvGradXTaps p{go, widx, dx, go_scale, w_zero, grad_x, N, O, static_cast<int>(K), (O + TK - 1) / TK * TK, g,
                                 make_fastdiv(sh), make_fastdiv(sw)};
                 const long long max_class = static_cast<long long>(N) * ((H + sh - 1) / sh) * ((W + sw - 1) / sw);
                 ATB_REQUIRE(ceil_div(C, 64) <= 65535, "C too large");
                 launch_sgemm(p, max_class, C, sh * sw, s);
             } else {
-                ConvGradX p{go, widx, dx, go_scale, grad_x, N, O, static_cast<int>(K), g,
+                ConvGradX p{go, widx, dx, go_scale, w_zero, grad_x, N, O, static_cast<int>(K), g,
                             make_fastdiv(H * W), make_fastdiv(W), make_fastdiv(kh * kw), make_fastdiv(kw),
                             make_fastdiv(sh), make_fastdiv(sw)};
                 ATB_REQUIRE(ceil_div(C, 64) <= 65535, "C too large");

@@ -12,12 +12,16 @@ z_x (the image of real 0), so padded taps cancel in the correction.
 Buffers, parameters and state_dict behaviour match the reference (min/max statistics, explicit
 scale / zero-point buffers, legacy min/max-only checkpoints, integer-valued zero-point validation).
 
-Two execution routes, numerically the same function:
+Execution routes, numerically the same function:
 * no gradient needed (inference): one fused sequence — uint8 index image, weight indices with their
   row sums, im2col-free LUT conv whose epilogue applies the correction in integer arithmetic, the
   scale and the bias;
-* training: the reference's decoupled chain (fake-quant -> pad with z_x -> unfold -> LUT-BGEMM
-  Function -> differentiable correction), so autograd supplies the -z terms of all three estimators.
+* training with the STE or LRE estimator (``fused_training``, the default): the same fused forward keeping
+  the uint8 image, and an image-space backward that folds the -z terms into its operand maps
+  (``bgemm_uint8.approx_conv2d_uint8``) — no unfolded fp32 operand, no unfold;
+* training with the custom estimator, or ``fused_training = False``: the reference's decoupled chain
+  (fake-quant -> pad with z_x -> unfold -> LUT-BGEMM Function -> differentiable correction), where
+  autograd supplies the -z terms.
 """
 
 from __future__ import annotations
@@ -76,6 +80,8 @@ class Conv2d_uint8(nn.Module):
         self.qmin, self.qmax = 0, 255
         self.scale_momentum = scale_momentum
         self.update_scale = update_scale
+        # route STE / LRE training through the fused image-space Function (False: the reference's decoupled chain)
+        self.fused_training = True
 
         self.register_buffer('lut', lut)
         self.weight = nn.Parameter(torch.empty(out_channels, in_channels, *self.kernel_size))
@@ -227,6 +233,11 @@ class Conv2d_uint8(nn.Module):
             x.requires_grad or self.weight.requires_grad or (self.bias is not None and self.bias.requires_grad))
         if not wants_grad and x.is_cuda and x.dtype == torch.float32:
             return self._forward_fused(x)
+        if self.fused_training and self.grad in ('ste', 'lre') and x.is_cuda and x.dtype == torch.float32:
+            g4 = (tuple(self.kernel_size), tuple(self.stride), tuple(self.padding), tuple(self.dilation))
+            return bgemm_uint8.approx_conv2d_uint8(x, self.weight, self.bias, self.scale_x, self.zero_x, self.scale_w,
+                                                   self.zero_w, self.lut, self.dx, self.dw, g4, self.grad,
+                                                   self.qmin, self.qmax)
 
         scale_x, zero_x, scale_w, zero_w = self.scale_x, self.zero_x, self.scale_w, self.zero_w
         xq = quantization.static_quantize_uint8(x, scale_x, zero_x, self.qmin, self.qmax)

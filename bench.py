@@ -203,12 +203,24 @@ def build_resnet50_uint8(dev, calib_images=8):
 
 
 def resnet50_inference_leg(dev, world, rank, steps, batch_per_gpu=128):
-    """img/s of ResNet-50 approximate-conv inference, data-parallel replicas with a fixed batch per GPU (weak
-    scaling, like the headline line); device-resident and end-to-end (pinned host images in, logits out)."""
+    """img/s of ResNet-50 approximate-conv inference on data-parallel replicas: with a fixed batch of 128 per GPU
+    (weak scaling, like the headline line) and, on more than one GPU, also with one batch of 128 split evenly
+    over the ranks (strong scaling).  Device-resident and end-to-end (pinned host images in, logits out)."""
     import torch
-    import torch.distributed as dist
     per_rank = int(os.environ.get("ATB_BENCH_RESNET_BATCH", batch_per_gpu))
     model = build_resnet50_uint8(dev)
+    out = _resnet50_timed(model, dev, world, rank, steps, per_rank, "resnet50")
+    if world > 1 and per_rank // world >= 1:
+        strong = _resnet50_timed(model, dev, world, rank, steps, per_rank // world, "resnet50_split128")
+        out.update({k: v for k, v in strong.items() if k.startswith("resnet50_split128")})
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
+def _resnet50_timed(model, dev, world, rank, steps, per_rank, tag):
+    import torch
+    import torch.distributed as dist
     g = torch.Generator().manual_seed(1 + rank)
     x_host = torch.randn(per_rank, 3, 224, 224, generator=g).pin_memory()
     x_dev = x_host.to(dev)
@@ -267,13 +279,11 @@ def resnet50_inference_leg(dev, world, rank, steps, batch_per_gpu=128):
         torch.cuda.synchronize()
         res["eager"] = per_rank / (t0.elapsed_time(t1) / steps * 1e-3)
         del graph
-    del model
-    torch.cuda.empty_cache()
-    return {"resnet50_uint8_infer_img_s": res["resident"], "resnet50_uint8_infer_img_s_e2e": res["e2e"],
-            "resnet50_uint8_infer_img_s_eager_one_gpu": res["eager"],
-            "resnet50_cuda_graph_matches_eager": res["graph_matches_eager"],
-            "resnet50_batch_per_gpu": per_rank, "resnet50_lut_macs_per_img": 3.969e9,
-            "resnet50_lut_mac_s_per_gpu": res["resident"] * 3.969e9 / world}
+    return {f"{tag}_uint8_infer_img_s": res["resident"], f"{tag}_uint8_infer_img_s_e2e": res["e2e"],
+            f"{tag}_uint8_infer_img_s_eager_one_gpu": res["eager"],
+            f"{tag}_cuda_graph_matches_eager": res["graph_matches_eager"],
+            f"{tag}_batch_per_gpu": per_rank, f"{tag}_lut_macs_per_img": 3.969e9,
+            f"{tag}_lut_mac_s_per_gpu": res["resident"] * 3.969e9 / world}
 
 
 # ----------------------------------------------------------------------------------------------- GPU arm

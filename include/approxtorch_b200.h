@@ -168,10 +168,14 @@ int atb_lre_bwd(const float* go, const void* x, int x_dtype, const void* w, int 
                 int N, int K, int L, int O, void* stream);
 /* Image-space form used by the conv Functions: x is the quantised image [N,C,H,W]; grad_x is the
  * gradient w.r.t. that image (the fold is fused), grad_w is [O, C*kh*kw]; taps outside the image
- * contribute dw[pad_index] to grad_w.  `go_scale` (optional, [O]) multiplies go per output channel.
+ * contribute dw[pad_index] to grad_w (pad_index 0..256: 256 addresses a 257th entry the caller appended to
+ * dw, for a pad value that is only known on the device).  `go_scale` (optional, [O]) multiplies go per output
+ * channel.  `w_zero` (optional, [O]) is subtracted from the mapped weight, grad_x uses dx[widx[o,k]] - w_zero[o]:
+ * the weight zero point of the asymmetric layer, whose correction term -z_w[o] * sum_k q_x has that derivative
+ * (approxtorch/nn/Conv2d_uint8.py:308-315).
  * Replaces the cuDNN convolution_backward calls of approxtorch/nn/bgemm_int8.py:165-212, 259-295. */
 int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t* widx /*[O,K]*/,
-                     const float* dx, const float* dw, const float* go_scale,
+                     const float* dx, const float* dw, const float* go_scale, const float* w_zero,
                      float* grad_x /*[N,C,H,W]*/, float* grad_w /*[O,K]*/,
                      int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
                      int dh, int dw_, int pad_index, void* stream);

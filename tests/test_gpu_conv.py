@@ -306,6 +306,41 @@ def test_uint8_layer_inference_and_training_routes(dev, geom):
     _close(layer.weight.grad, gws.cpu().numpy().astype(np.float64))
 
 
+@pytest.mark.parametrize("mode", ["ste", "lre"])
+@pytest.mark.parametrize("geom", [(2, 6, 9, 9, 10, 3, 1, 1, 1), (2, 4, 10, 8, 7, 3, 2, 1, 1), (3, 8, 6, 6, 70, 1, 2, 0, 1),
+                                  (2, 5, 7, 9, 6, (3, 2), (1, 2), (2, 1), 1)])
+def test_uint8_fused_training_matches_decoupled_chain(dev, mode, geom):
+    """The fused image-space training route against the reference's decoupled chain (fake-quant -> pad with z_x ->
+    unfold -> LUT-BGEMM Function -> differentiable correction) on the same layer: outputs and all three
+    gradients, including the padded taps' contribution to grad_w under LRE slopes."""
+    import approxtorch_b200 as at
+    B, C, H, W, O, k, s, p, d = geom
+    rng = np.random.default_rng(23)
+    torch.manual_seed(7)
+    lut = lo.lut_unsigned_truncated(6)
+    dx = _t(rng.uniform(20, 200, 256).astype(np.float32), dev) if mode == "lre" else None
+    dw = _t(rng.uniform(20, 200, 256).astype(np.float32), dev) if mode == "lre" else None
+    layer = at.nn.Conv2d_uint8(C, O, _pair(k), _t(lut.reshape(-1), dev), grad=mode, dx=dx, dw=dw, bias=True,
+                               stride=_pair(s), padding=_pair(p), update_scale=False).to(dev).train()
+    with torch.no_grad():
+        layer.x_min.fill_(-1.5)            # narrower than the data: some activations clip, so masks matter
+        layer.x_max.fill_(2.0)
+    layer._reset_qparams_from_stats()
+    x = (rng.standard_normal((B, C, H, W)) * 1.2).astype(np.float32)
+    outs = {}
+    for fused in (True, False):
+        layer.fused_training = fused
+        layer.zero_grad(set_to_none=True)
+        xt = _t(x, dev).requires_grad_(True)
+        y = layer(xt)
+        torch.manual_seed(11)
+        go = torch.randn_like(y)
+        y.backward(go)
+        outs[fused] = (y.detach(), xt.grad.clone(), layer.weight.grad.clone(), layer.bias.grad.clone())
+    for got, ref in zip(outs[True], outs[False]):
+        _close(got, ref.double().cpu().numpy())
+
+
 def test_ema_statistics_on_device(dev):
     import approxtorch_b200 as at
     rng = np.random.default_rng(23)
