@@ -410,6 +410,8 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
         __syncthreads();
     }
 
+    // a warp whose 32 pixel rows all lie past the end of a ragged last row tile still stages, but looks nothing up
+    const bool has_rows = r0 + warp * TM < r_end;
     int step = 0;
     for (int ci = 0; ci < nch; ++ci) {
         const int k0 = kbeg + ci * kChunk;
@@ -431,11 +433,11 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
             if constexpr (kPipelined) {
                 QuadWords v;
                 if (wnext != nullptr && warp < kQuadRows) fetch_quad(s_tab, wnext, warp, lane, v);
-                lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
+                if (has_rows) lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
                 if (wnext != nullptr && warp < kQuadRows) store_quad(stage_next, warp, lane, v);
             } else {
                 if (wnext != nullptr) stage_quads(stage_next, s_tab, wnext, warp, lane, NW);
-                lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
+                if (has_rows) lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
             }
             __syncthreads();
         }
@@ -671,20 +673,24 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
                 if (best_s > 1 && best <= 0.95 * base) { splits = best_s; tail_rt = t_rt; }
             }
         }
-        // (2) Otherwise split-K over all tiles, chosen from whole waves of `sms` equal blocks: time ~
-        // ceil(tiles * S / sms) / S tile times, with a few percent per extra split for the reduction pass and
-        // the repeated prologues.  Grids that already fill the GPU only split for a modelled gain of 10 % or
-        // more (the partial sums need S times the output in scratch).
+        // (2) Otherwise split-K over all tiles, by the same model: S_eff equal parts of ceil(chunks / S) chunks
+        // each, whole waves of `sms` blocks, a fixed cost per block and a reduction pass.  Grids that already
+        // fill the GPU only split for a modelled gain of 10 % or more (the partial sums need S times the output
+        // in scratch).
         if (tail_rt == 0 && tiles > 0 && tiles < 4LL * sms && nchunks > 1) {
-            const double base = static_cast<double>((tiles + sms - 1) / sms);
+            const double base = wave_cost(tiles, K, sms);
             double best = base;
             int best_s = 1;
             for (int s = 2; s <= 16 && s <= nchunks; ++s) {
-                const double waves = static_cast<double>((tiles * s + sms - 1) / sms) / s;
-                const double cost = waves * (1.0 + 0.03 * (s - 1));
+                const int cps = ceil_div(nchunks, s);
+                const int s_eff = ceil_div(nchunks, cps);
+                if (s_eff != s) continue;                       // same launch as a smaller s
+                // partial sums: S_eff * R * O int32 written and read back, ~2e-6 k-step times per element
+                const double traffic = 2.1e-6 * s_eff * static_cast<double>(R) * O;
+                const double cost = wave_cost(tiles * s_eff, cps * kChunk, sms) + 6.0 + traffic;
                 if (cost < best - 1e-9) { best = cost; best_s = s; }
             }
-            if (tiles < sms || best <= 0.9 * base) splits = best_s;
+            if (best_s > 1 && (tiles < sms ? best <= 0.97 * base : best <= 0.9 * base)) splits = best_s;
         }
     }
     if (splits > nchunks) splits = nchunks;

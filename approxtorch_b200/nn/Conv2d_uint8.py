@@ -236,7 +236,8 @@ class Conv2d_uint8(nn.Module):
         if self.fused_training and self.grad in ('ste', 'lre') and x.is_cuda and x.dtype == torch.float32:
             g4 = (tuple(self.kernel_size), tuple(self.stride), tuple(self.padding), tuple(self.dilation))
             return bgemm_uint8.approx_conv2d_uint8(x, self.weight, self.bias, self.scale_x, self.zero_x, self.scale_w,
-                                                   self.zero_w, self.lut, self.dx, self.dw, g4, self.grad,
+                                                   self.zero_w, self.lut, getattr(self, 'dx', None),
+                                                   getattr(self, 'dw', None), g4, self.grad,
                                                    self.qmin, self.qmax)
 
         scale_x, zero_x, scale_w, zero_w = self.scale_x, self.zero_x, self.scale_w, self.zero_w

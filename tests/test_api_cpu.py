@@ -269,3 +269,17 @@ def test_calibration_matches_reference_fixture(golden, tmp_path):
         at.calib.calibrate_uint8(nn.Sequential(nn.Conv2d(1, 1, 1)), data, None)
     with pytest.raises(TypeError):
         at.calib.calibrate_uint8(model(), data, True)
+
+
+def test_linear_layer_state_dict_uses_flat_names():
+    import approxtorch_b200 as at
+    from oracle import lut_oracle as lo
+    lut = torch.from_numpy(lo.lut_exact_signed().reshape(-1)).float()
+    a = at.nn.Linear_int8(12, 5, lut, bias=True)
+    sd = a.state_dict()
+    assert set(sd) == {"weight", "bias", "lut", "scale_x", "scale_w"} and tuple(sd["weight"].shape) == (5, 12)
+    b = at.nn.Linear_int8(12, 5, lut, bias=True)
+    b.load_state_dict(sd)
+    assert torch.equal(a.weight, b.weight) and torch.equal(a.bias, b.bias)
+    with pytest.raises(RuntimeError):
+        a(torch.zeros(3, 11))
