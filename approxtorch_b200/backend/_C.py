@@ -36,7 +36,7 @@ _vp, _i, _ll, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_s
 
 
 class GemmPlan(ctypes.Structure):
-    _fields_ = [("block_rows", _i), ("splits", _i), ("scratch_bytes", _sz), ("tail_row_tiles", _i)]
+    _fields_ = [("block_rows", _i), ("splits", _i), ("scratch_bytes", _sz), ("tail_row_tiles", _i), ("stream_k_units", _i)]
 
 
 _SIGNATURES = {

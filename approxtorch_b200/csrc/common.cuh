@@ -49,7 +49,8 @@ int sm_count();
 // ---------------------------------------------------------------------------------------------
 struct LutImage {
     int flags[4];
-    // tabTP16: transposed and x-permuted.  A 32-bit word of row w holds the pair i = {x = i (low half),
+    // tabTP16: transposed and x-permuted; for the int16 class stored with bit 15 of every entry flipped
+    // (value + 32768 as an unsigned entry).  A 32-bit word of row w holds the pair i = {x = i (low half),
     // x = i + 128 (high half)}, i = 0..127, and pair i is word 4 * (i & 31) + (i >> 5) of the row, so that lane l
     // of a warp reads the pairs l, l + 32, l + 64, l + 96 with one 16-byte load
     int16_t tabTP16[65536];

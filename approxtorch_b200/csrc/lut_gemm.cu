@@ -59,6 +59,10 @@ struct GemmArgs {
     int* scratch;          // split-K partials [S][srows][O] followed by row sums [S][srows]
     long long srow0, srows;   // pixel rows the split-K scratch covers: [srow0, srow0 + srows)
     int tile0;             // first row tile of this launch (added to blockIdx.x)
+    // stream-K launches (sk_units > 0): the (tile, k-chunk) units, tile-major, are dealt out in equal contiguous
+    // runs of sk_units, one run per block; a block works through the one to three tile segments of its run
+    int sk_units, sk_col_tiles, block_rows;
+    long long sk_total;    // fits 31 bits
     long long R;           // pixel rows
     int K, L, O;
     int wb_rows;           // pixel rows per weight matrix (0: one matrix for all rows)
@@ -320,6 +324,7 @@ __device__ __forceinline__ void store_chunk(uint8_t* s_x, uint8_t* s_w, int buf,
 // contiguous bytes per channel.
 template <bool QUAD, class Total, class Bits>
 __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, long long r0, long long r_end, int c0,
+                                           int split, bool to_scratch,
                                            int warp, int lane, int xsum, Total total, Bits bits)
 {
     constexpr int NJ = QUAD ? 16 : 32;               // row slots per thread
@@ -327,9 +332,8 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
     const int row_base = QUAD ? (lane >> 4) * 16 : 0;        // first of this thread's rows within the warp's 32
     const int col_base = QUAD ? (lane & 15) : lane;          // first of this thread's columns within the 64
     constexpr int col_step = QUAD ? 16 : 32;
-    const int split = blockIdx.z;
     const bool want_xsum = a.zero_x != nullptr;
-    if (a.splits > 1 || a.L == 1) {
+    if (to_scratch || a.L == 1) {
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
             const long long r = r0 + warp * 32 + row_base + j;
@@ -339,10 +343,10 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
             for (int t = 0; t < NT; ++t) {
                 const int o = c0 + col_base + col_step * t;
                 if (o >= a.O) continue;
-                if (a.splits > 1) a.scratch[(static_cast<long long>(split) * a.srows + (r - a.srow0)) * a.O + o] = bits(j, t);
+                if (to_scratch) a.scratch[(static_cast<long long>(split) * a.srows + (r - a.srow0)) * a.O + o] = bits(j, t);
                 else a.y[output_offset(r, o, a)] = finalize_output(total(j, t), xs, o, a);
             }
-            if (a.splits > 1 && want_xsum && blockIdx.y == 0 && col_base == 0)
+            if (to_scratch && want_xsum && c0 == 0 && col_base == 0)
                 a.scratch[static_cast<long long>(a.splits) * a.srows * a.O + static_cast<long long>(split) * a.srows + (r - a.srow0)] = xs;
         }
         return;
@@ -377,7 +381,8 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
 template <int NW, bool DP2A>
 __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
                                               const uint8_t* wcol, bool vec_x, bool vec_w, int pad, int bias,
-                                              long long r0, long long r_end, int c0, int kbeg, int kend)
+                                              long long r0, long long r_end, int c0, int kbeg, int kend,
+                                              int split, bool to_scratch, const volatile int* desc)
 {
     constexpr int TM = 32;                       // pixel rows per warp
     constexpr bool kPipelined = NW >= kQuadRows; // one quad row per warp: keep the next step's table words in registers
@@ -449,7 +454,13 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
         const unsigned v = (t & 1) == 0 ? acc[j][u] - (acc[j][u + 1] << 16) : acc[j][u + 1];
         return static_cast<long long>(v) - remove;
     };
-    write_tile<true>(a, smem, r0, r_end, c0, warp, lane, xsum,
+    if (desc != nullptr) {
+        // stream-K: the tile coordinates were not kept in registers across the main loop; read them back
+        r0 = static_cast<long long>(desc[0]) * bm;
+        c0 = desc[1];
+        split = desc[4];
+    }
+    write_tile<true>(a, smem, r0, r_end, c0, split, to_scratch, warp, lane, xsum,
                      [&](int j, int t) { return total(j, t); },
                      [&](int j, int t) { return static_cast<int>(total(j, t)); });
 }
@@ -459,7 +470,8 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
 template <int TM>
 __device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
                                               const uint8_t* wcol, bool vec_x, bool vec_w, int pad,
-                                              long long r0, long long r_end, int c0, int kbeg, int kend)
+                                              long long r0, long long r_end, int c0, int kbeg, int kend,
+                                              int split, bool to_scratch, const volatile int* desc)
 {
     uint8_t* s_x = smem + kSmemX;
     uint8_t* s_w = smem + kSmemW;
@@ -496,24 +508,29 @@ __device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, 
         }
         __syncthreads();
     }
-    write_tile<false>(a, smem, r0, r_end, c0, warp, lane, xsum,
+    if (desc != nullptr) {
+        r0 = static_cast<long long>(desc[0]) * bm;
+        c0 = desc[1];
+        split = desc[4];
+    }
+    write_tile<false>(a, smem, r0, r_end, c0, split, to_scratch, warp, lane, xsum,
                [&](int j, int t) { return acc[j][t]; },
                [&](int j, int t) { return __float_as_int(acc[j][t]); });
 }
 
-// NW warps per block, 32 pixel rows per warp (one thread per row loads the operand tiles, 64 accumulators
-// per thread).  DP2A selects how the high half of a fetched word is accumulated.
+// One tile segment: rows of row tile `row_tile`, the 64 output channels from c0, k-chunks [ch_beg, ch_end).
+// The result goes to y (to_scratch false) or, as a partial sum, to slot `split` of the scratch.
 template <int NW, bool DP2A>
-__global__ void __launch_bounds__(NW * 32, 1) lut_gemm_kernel(const GemmArgs a)
+__device__ __forceinline__ void run_segment(const GemmArgs& a, uint8_t* smem, int cls, int row_tile, int c0,
+                                            int ch_beg, int ch_end, int split, bool to_scratch,
+                                            const volatile int* desc = nullptr)
 {
     constexpr int TM = 32;
-    extern __shared__ __align__(16) uint8_t smem[];
     const int tid = threadIdx.x;
     constexpr int bm = NW * TM;
 
     long long r0, r_end;
     long long wbatch = 0;
-    const int row_tile = a.tile0 + static_cast<int>(blockIdx.x);
     if (a.wb_rows > 0) {
         wbatch = row_tile / a.tiles_per_batch;
         const int t = row_tile - static_cast<int>(wbatch) * a.tiles_per_batch;
@@ -523,10 +540,6 @@ __global__ void __launch_bounds__(NW * 32, 1) lut_gemm_kernel(const GemmArgs a)
         r0 = static_cast<long long>(row_tile) * bm;
         r_end = a.R;
     }
-    const int c0 = blockIdx.y * kStagedCols;
-    const int nchunks = (a.K + kChunk - 1) / kChunk;
-    const int ch_beg = blockIdx.z * a.chunks_per_split;
-    const int ch_end = min(nchunks, ch_beg + a.chunks_per_split);
     const int kbeg = ch_beg * kChunk;
     const int kend = min(a.K, ch_end * kChunk);
 
@@ -554,23 +567,70 @@ __global__ void __launch_bounds__(NW * 32, 1) lut_gemm_kernel(const GemmArgs a)
     const uint8_t* wcol = a.w + wbatch * a.w_batch_stride + static_cast<long long>(ocol) * a.K;
     const bool vec_w = (a.K % kChunk == 0) && ((reinterpret_cast<uintptr_t>(a.w) & 15) == 0) &&
                        ((a.w_batch_stride & 15) == 0);
-
-    const int cls = lut_class_of(a.img);
     // pad_index < 0: taps outside the image take the activation zero point (an integer-valued device scalar)
     const int pad = a.pad_index >= 0 ? a.pad_index : min(255, max(0, static_cast<int>(llrintf(__ldg(a.zero_x)))));
+    if (cls != LUT_F32)
+        gemm_body_int<NW, DP2A>(a, smem, rc, wcol, vec_x, vec_w, pad, cls == LUT_I16 ? 32768 : 0, r0, r_end, c0, kbeg, kend,
+                                split, to_scratch, desc);
+    else
+        gemm_body_f32<TM>(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend, split, to_scratch, desc);
+}
+
+// NW warps per block, 32 pixel rows per warp (one thread per row loads the operand tiles, 64 accumulators
+// per thread).  DP2A selects how the high half of a fetched word is accumulated.
+// SK: the block works through a run of tile segments (stream-K) instead of one tile or tile split.
+template <int NW, bool DP2A, bool SK>
+__global__ void __launch_bounds__(NW * 32, 1) lut_gemm_kernel(const GemmArgs a)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int tid = threadIdx.x;
+    const int cls = lut_class_of(a.img);
     if (cls != LUT_F32) {
-        // signed entries are stored biased (+32768 == flipping bit 15), so every lookup is an unsigned 16-bit load
-        const uint32_t flip = (cls == LUT_I16) ? 0x80008000u : 0u;
-        const uint4* src = reinterpret_cast<const uint4*>(a.img->tabTP16);
-        uint4* dst = reinterpret_cast<uint4*>(smem);
-        for (int i = tid; i < kTableBytes / 16; i += blockDim.x) {
-            uint4 v = __ldg(src + i);
-            v.x ^= flip; v.y ^= flip; v.z ^= flip; v.w ^= flip;
-            dst[i] = v;
-        }
-        gemm_body_int<NW, DP2A>(a, smem, rc, wcol, vec_x, vec_w, pad, cls == LUT_I16 ? 32768 : 0, r0, r_end, c0, kbeg, kend);
+        // The image holds the table as the lookups want it (signed entries biased by +32768, so every lookup is an
+        // unsigned 16-bit load): asynchronous 16-byte copies straight into shared memory, all in flight at once.
+        const char* src = reinterpret_cast<const char*>(a.img->tabTP16);
+        const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+        for (int i = tid; i < kTableBytes / 16; i += blockDim.x)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * i), "l"(src + 16 * i) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");     // visible to the block after the next barrier
+    }
+    const int nchunks = (a.K + kChunk - 1) / kChunk;
+    if constexpr (!SK) {
+        const int ch_beg = blockIdx.z * a.chunks_per_split;
+        run_segment<NW, DP2A>(a, smem, cls, a.tile0 + static_cast<int>(blockIdx.x), blockIdx.y * kStagedCols,
+                              ch_beg, min(nchunks, ch_beg + a.chunks_per_split), blockIdx.z, a.splits > 1);
     } else {
-        gemm_body_f32<TM>(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend);
+        // This block's run of (tile, k-chunk) units; the table image stays in shared memory throughout.  The main
+        // loop has no register to spare, so the description of the current segment lives in shared memory: thread
+        // 0 writes it, everybody reads it for the prologue, and the epilogue and the loop read it back.
+        __shared__ int s_desc[8];        // row tile, first column, first chunk, end chunk, segment number, next unit
+        int u = static_cast<int>(blockIdx.x) * a.sk_units;
+        while (true) {
+            if (tid == 0) {
+                const int u_end = static_cast<int>(min(a.sk_total, static_cast<long long>(blockIdx.x + 1) * a.sk_units));
+                const int tile = u / nchunks;
+                const int ch_beg = u - tile * nchunks;
+                const int ch_end = min(nchunks, ch_beg + (u_end - u));
+                const int row_tile = tile / a.sk_col_tiles;
+                s_desc[0] = row_tile;
+                s_desc[1] = (tile - row_tile * a.sk_col_tiles) * kStagedCols;
+                s_desc[2] = ch_beg;
+                s_desc[3] = ch_end;
+                // segments of one tile are numbered by the blocks that hold them, in k order
+                s_desc[4] = u / a.sk_units - (tile * nchunks) / a.sk_units;
+                s_desc[5] = u + (ch_end - ch_beg);
+                s_desc[6] = u_end;
+            }
+            __syncthreads();
+            run_segment<NW, DP2A>(a, smem, cls, s_desc[0], s_desc[1], s_desc[2], s_desc[3], s_desc[4], true,
+                                  const_cast<const volatile int*>(s_desc));
+            const volatile int* d = s_desc;
+            u = d[5];
+            const int u_end = d[6];
+            __syncthreads();             // everybody has read the description before thread 0 rewrites it
+            if (u >= u_end) break;
+        }
     }
 }
 
@@ -580,20 +640,29 @@ __global__ void lut_gemm_reduce_kernel(const GemmArgs a)
     const long long total = a.srows * a.O;
     const int cls = lut_class_of(a.img);
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    const int nchunks = (a.K + kChunk - 1) / kChunk;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const long long rs = i / a.O;
         const int o = static_cast<int>(i - rs * a.O);
+        // number of partial sums of this element, and of its row's operand sum (held by the first column tile)
+        int ns = a.splits, nx = a.splits;
+        if (a.sk_units > 0) {
+            const long long t0 = (rs / a.block_rows) * a.sk_col_tiles;                   // first tile of the row tile
+            const long long t1 = t0 + o / kStagedCols;
+            nx = static_cast<int>((t0 * nchunks + nchunks - 1) / a.sk_units - (t0 * nchunks) / a.sk_units) + 1;
+            ns = static_cast<int>((t1 * nchunks + nchunks - 1) / a.sk_units - (t1 * nchunks) / a.sk_units) + 1;
+        }
         long long xs = 0;
         if (a.zero_x != nullptr)
-            for (int s = 0; s < a.splits; ++s) xs += a.scratch[a.splits * total + static_cast<long long>(s) * a.srows + rs];
+            for (int s = 0; s < nx; ++s) xs += a.scratch[a.splits * total + static_cast<long long>(s) * a.srows + rs];
         float v;
         if (cls == LUT_F32) {
             float f = 0.0f;
-            for (int s = 0; s < a.splits; ++s) f += __int_as_float(a.scratch[static_cast<long long>(s) * total + i]);
+            for (int s = 0; s < ns; ++s) f += __int_as_float(a.scratch[static_cast<long long>(s) * total + i]);
             v = finalize_output(f, xs, o, a);
         } else {
             long long t = 0;
-            for (int s = 0; s < a.splits; ++s) t += a.scratch[static_cast<long long>(s) * total + i];
+            for (int s = 0; s < ns; ++s) t += a.scratch[static_cast<long long>(s) * total + i];
             v = finalize_output(t, xs, o, a);
         }
         a.y[output_offset(a.srow0 + rs, o, a)] = v;
@@ -651,8 +720,11 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
     const long long tiles = rt * ct;
     const int nchunks = K > 0 ? ceil_div(K, kChunk) : 1;
     long long tail_rt = 0;
+    int sk_units = 0;
+    bool allow_sk = wb_rows == 0 && (cfg < 0 || (((cfg >> 26) & 1) == 0 && splits == 0));
     if (splits == 0) {
         splits = 1;
+        double classic = wave_cost(tiles, K, sms);      // modelled cost of the plan chosen so far
         // (1) Grids of more than one wave whose last wave is ragged: the whole waves run unsplit, and only
         // the trailing row tiles are split along K so that they fill one more (shorter) wave.  Their partial
         // sums are the only ones that go through scratch.
@@ -670,7 +742,7 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
                     const double cost = wave_cost(main_rt * ct, K, sms) + wave_cost(t_rt * ct * s_eff, cps * kChunk, sms) + 6.0;
                     if (cost < best - 1e-9) { best = cost; best_s = s; }
                 }
-                if (best_s > 1 && best <= 0.95 * base) { splits = best_s; tail_rt = t_rt; }
+                if (best_s > 1 && best <= 0.95 * base) { splits = best_s; tail_rt = t_rt; classic = best; }
             }
         }
         // (2) Otherwise split-K over all tiles, by the same model: S_eff equal parts of ceil(chunks / S) chunks
@@ -690,24 +762,46 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
                 const double cost = wave_cost(tiles * s_eff, cps * kChunk, sms) + 6.0 + traffic;
                 if (cost < best - 1e-9) { best = cost; best_s = s; }
             }
-            if (best_s > 1 && (tiles < sms ? best <= 0.97 * base : best <= 0.9 * base)) splits = best_s;
+            if (best_s > 1 && (tiles < sms ? best <= 0.97 * base : best <= 0.9 * base)) { splits = best_s; classic = best; }
+        }
+        // (3) Stream-K for grids of a few waves at most: the (tile, k-chunk) units, tile-major, are dealt out in
+        // equal contiguous runs, one per SM, so every SM gets the same number of k-steps whatever the tile count.
+        // A block loads the table once and works through the one to three tile segments of its run; every
+        // segment's partial sums go through scratch and the reduction pass finishes all outputs.
+        if (allow_sk && tiles > 0 && (tiles < 4LL * sms || (cfg >= 0 && ((cfg >> 27) & 1))) && nchunks > 1) {
+            const long long total = tiles * nchunks;
+            const long long ctas = total < sms ? total : sms;
+            const long long units = (total + ctas - 1) / ctas;
+            const double segs = static_cast<double>((units + nchunks - 1) / nchunks + 1);
+            const double traffic = 2.1e-6 * 2.5 * static_cast<double>(R) * O;
+            const double cost = static_cast<double>(units) * kChunk + 8.0 * segs + 6.0 + traffic;
+            const bool forced = cfg >= 0 && ((cfg >> 27) & 1);
+            if ((forced || cost <= 0.95 * classic) && total < 2147483647LL / 2) {
+                sk_units = static_cast<int>(units);
+                tail_rt = 0;
+                splits = static_cast<int>((nchunks + units - 2) / units + 1);     // most segments any tile can have
+            }
         }
     }
-    if (splits > nchunks) splits = nchunks;
-    const int cps = ceil_div(nchunks, splits);
-    splits = ceil_div(nchunks, cps);
-    if (splits == 1) tail_rt = 0;
+    if (sk_units == 0) {
+        if (splits > nchunks) splits = nchunks;
+        const int cps = ceil_div(nchunks, splits);
+        splits = ceil_div(nchunks, cps);
+        if (splits == 1) tail_rt = 0;
+    }
     const long long srow0 = tail_rt > 0 ? tile_first_row(rt - tail_rt, bm, wb_rows, tpb) : 0;
     p->block_rows = bm;
     p->splits = splits;
-    p->scratch_bytes = splits > 1 ? static_cast<size_t>(splits) * static_cast<size_t>(R - srow0) * (static_cast<size_t>(O) + 1) * 4u : 0u;
+    p->scratch_bytes = (splits > 1 || sk_units > 0)
+                           ? static_cast<size_t>(splits) * static_cast<size_t>(R - srow0) * (static_cast<size_t>(O) + 1) * 4u : 0u;
     p->tail_row_tiles = static_cast<int>(tail_rt);
+    p->stream_k_units = sk_units;
     if (tiles_per_batch) *tiles_per_batch = tpb;
     if (row_tiles) *row_tiles = rt;
     return ATB_OK;
 }
 
-template <int NW, bool DP2A>
+template <int NW, bool DP2A, bool SK>
 static int launch_one(dim3 grid, const GemmArgs& a, cudaStream_t stream)
 {
     // the opt-in shared-memory size is an attribute of the function on ONE device: set it once per device
@@ -719,21 +813,26 @@ static int launch_one(dim3 grid, const GemmArgs& a, cudaStream_t stream)
         return ATB_ERR_CUDA;
     }
     if (!attr_set[dev]) {
-        e = cudaFuncSetAttribute(lut_gemm_kernel<NW, DP2A>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+        e = cudaFuncSetAttribute(lut_gemm_kernel<NW, DP2A, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
         attr_set[dev] = true;
     }
-    lut_gemm_kernel<NW, DP2A><<<grid, NW * 32, kSmemTotal, stream>>>(a);
+    lut_gemm_kernel<NW, DP2A, SK><<<grid, NW * 32, kSmemTotal, stream>>>(a);
     return ATB_OK;
 }
 
-static int launch_variant(int nwarps, bool dp2a, dim3 grid, const GemmArgs& a, cudaStream_t stream)
+// stream-K launches always accumulate with the dot-product instruction
+static int launch_variant(int nwarps, bool dp2a, bool sk, dim3 grid, const GemmArgs& a, cudaStream_t stream)
 {
     switch (nwarps) {
-        case 16: return dp2a ? launch_one<16, true>(grid, a, stream) : launch_one<16, false>(grid, a, stream);
-        case 8: return dp2a ? launch_one<8, true>(grid, a, stream) : launch_one<8, false>(grid, a, stream);
-        case 4: return dp2a ? launch_one<4, true>(grid, a, stream) : launch_one<4, false>(grid, a, stream);
-        case 2: return dp2a ? launch_one<2, true>(grid, a, stream) : launch_one<2, false>(grid, a, stream);
+        case 16: return sk ? launch_one<16, true, true>(grid, a, stream)
+                           : dp2a ? launch_one<16, true, false>(grid, a, stream) : launch_one<16, false, false>(grid, a, stream);
+        case 8: return sk ? launch_one<8, true, true>(grid, a, stream)
+                          : dp2a ? launch_one<8, true, false>(grid, a, stream) : launch_one<8, false, false>(grid, a, stream);
+        case 4: return sk ? launch_one<4, true, true>(grid, a, stream)
+                          : dp2a ? launch_one<4, true, false>(grid, a, stream) : launch_one<4, false, false>(grid, a, stream);
+        case 2: return sk ? launch_one<2, true, true>(grid, a, stream)
+                          : dp2a ? launch_one<2, true, false>(grid, a, stream) : launch_one<2, false, false>(grid, a, stream);
         default: set_error("block rows must be 64, 128, 256 or 512"); return ATB_ERR_INVALID;
     }
 }
@@ -755,7 +854,7 @@ static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes,
     ATB_REQUIRE(row_tiles <= 2147483647LL, "too many row tiles");
     const int col_tiles = ceil_div(a.O, kStagedCols);
     ATB_REQUIRE(col_tiles <= 65535, "too many output channels");
-    if (plan.splits > 1) {
+    if (plan.scratch_bytes > 0) {
         if (scratch == nullptr || scratch_bytes < plan.scratch_bytes) {
             set_error("split-K needs %zu bytes of scratch, got %zu", plan.scratch_bytes, scratch_bytes);
             return ATB_ERR_SCRATCH;
@@ -765,13 +864,26 @@ static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes,
     a.tiles_per_batch = tpb;
     const bool shift_add = cfg >= 0 && ((cfg >> 24) & 1);      // cfg bit 24: accumulate high halves with shift + add
     const int nchunks = ceil_div(a.K, kChunk);
+    a.block_rows = plan.block_rows;
+    if (plan.stream_k_units > 0) {
+        a.tile0 = 0; a.splits = plan.splits; a.chunks_per_split = nchunks; a.srow0 = 0; a.srows = a.R;
+        a.sk_units = plan.stream_k_units; a.sk_col_tiles = col_tiles;
+        a.sk_total = row_tiles * col_tiles * nchunks;
+        dim3 grid(static_cast<unsigned>((a.sk_total + a.sk_units - 1) / a.sk_units), 1u, 1u);
+        rc = launch_variant(plan.block_rows / 32, true, true, grid, a, stream);
+        if (rc != ATB_OK) return rc;
+        rc = check_launch("lut_gemm_kernel");
+        if (rc != ATB_OK) return rc;
+        lut_gemm_reduce_kernel<<<grid_for(a.srows * a.O, 256, 8 * sm_count()), 256, 0, stream>>>(a);
+        return check_launch("lut_gemm_reduce_kernel");
+    }
     const long long tail_rt = plan.tail_row_tiles;
     const long long main_rt = row_tiles - tail_rt;
     if (tail_rt > 0) {
         // whole waves, unsplit
         a.tile0 = 0; a.splits = 1; a.chunks_per_split = nchunks; a.srow0 = 0; a.srows = a.R;
         dim3 grid(static_cast<unsigned>(main_rt), static_cast<unsigned>(col_tiles), 1u);
-        rc = launch_variant(plan.block_rows / 32, !shift_add, grid, a, stream);
+        rc = launch_variant(plan.block_rows / 32, !shift_add, false, grid, a, stream);
         if (rc != ATB_OK) return rc;
         rc = check_launch("lut_gemm_kernel");
         if (rc != ATB_OK) return rc;
@@ -784,7 +896,7 @@ static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes,
     a.srows = a.R - a.srow0;
     dim3 grid(static_cast<unsigned>(tail_rt > 0 ? tail_rt : row_tiles), static_cast<unsigned>(col_tiles),
               static_cast<unsigned>(plan.splits));
-    rc = launch_variant(plan.block_rows / 32, !shift_add, grid, a, stream);
+    rc = launch_variant(plan.block_rows / 32, !shift_add, false, grid, a, stream);
     if (rc != ATB_OK) return rc;
     rc = check_launch("lut_gemm_kernel");
     if (rc != ATB_OK) return rc;

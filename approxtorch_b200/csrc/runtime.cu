@@ -55,6 +55,17 @@ __global__ void lut_prepare_kernel(const float* __restrict__ lut, LutImage* __re
     img->tabTP16[(wi << 8) + (((pair & 31) << 2) + (pair >> 5)) * 2 + (xi >> 7)] = v16;
 }
 
+// Tables of the int16 class are looked up as unsigned entries carrying a +32768 bias (bit 15 flipped); the
+// staged-lookup image is stored that way so that the GEMM blocks can copy it into shared memory untouched.
+// Runs after lut_prepare_kernel on the same stream, when the class flags are final.
+__global__ void lut_bias_kernel(LutImage* __restrict__ img)
+{
+    if (img->flags[0] != 0) return;                        // not the int16 class
+    uint32_t* words = reinterpret_cast<uint32_t*>(img->tabTP16);
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;   // 32768 words
+    words[i] ^= 0x80008000u;
+}
+
 }  // namespace atb
 
 using namespace atb;
@@ -69,6 +80,10 @@ extern "C" int atb_lut_prepare(const float* lut, void* image, void* stream)
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e = cudaMemsetAsync(image, 0, sizeof(int) * 4, s);
     if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
+    ATB_REQUIRE(aligned_to(image, 16), "image must be 16-byte aligned");
     lut_prepare_kernel<<<256, 256, 0, s>>>(lut, static_cast<LutImage*>(image));
-    return check_launch("lut_prepare_kernel");
+    int rc = check_launch("lut_prepare_kernel");
+    if (rc != ATB_OK) return rc;
+    lut_bias_kernel<<<128, 256, 0, s>>>(static_cast<LutImage*>(image));
+    return check_launch("lut_bias_kernel");
 }

@@ -58,6 +58,11 @@ def cpu_baseline(a, b, lut, budget_s=12.0):
     except Exception:
         use_ref = False
     import torch
+    # every host core this process may run on, whatever the launcher put into OMP_NUM_THREADS (torchrun sets 1)
+    try:
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except Exception:
+        pass
     if use_ref:
         kind, cores = "reference", torch.get_num_threads()
         lut_t = torch.from_numpy(lut).reshape(256, 256).t().contiguous().reshape(-1).to(torch.int32)

@@ -71,7 +71,7 @@ int atb_im2col_u8(const void* x, int dtype, int N, int C, int H, int W, int kh, 
  *
  * cfg: -1 automatic.  Otherwise bits 0-15 pixel rows per block (64, 128, 256 or 512; 0 = automatic),
  * bits 16-23 split-K factor for every tile (0 = automatic), bit 24 accumulate with shift + add instead of the
- * dot-product instruction, bit 25 never split only the trailing row tiles.
+ * dot-product instruction, bit 25 never split only the trailing row tiles, bit 26 never stream-K, bit 27 always stream-K (when the launch can be one).
  *
  * The plan says how the launch will be tiled and how much scratch (bytes) a split-K launch needs. */
 typedef struct {
@@ -80,6 +80,9 @@ typedef struct {
     size_t scratch_bytes;
     int tail_row_tiles;  /* 0: `splits` applies to every tile; n > 0: only the last n row tiles are split (they
                             complete a ragged last wave), the rest run unsplit in a launch of their own */
+    int stream_k_units;  /* 0: tiles are whole blocks; n > 0: stream-K, every block works through n consecutive
+                            (tile, 16-step k-chunk) units and `splits` is the largest number of partial sums of
+                            any tile */
 } atb_gemm_plan;
 
 int atb_lut_gemm_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_plan* plan /*host*/);

@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this folder FROM THE REFERENCE ITSELF.
 
-Run in a container that has the reference checkout (default ``/root/reference``):
+Run where the reference checkout is available (its path is the optional argument):
 
     python tests/golden/make_golden.py [reference_root]
 
@@ -9,7 +9,7 @@ out: only its pure-torch CPU branches are exercised) and runs the reference's
 own CPU LUT-BGEMM operator compiled by ``oracle/build_ref.py``.  Inputs are
 stored next to outputs so the fixtures do not depend on any RNG implementation.
 The fixtures pin the oracle (``tests/test_oracle_golden.py``) and, through the
-same inputs, the CUDA path (``tests/test_gpu_golden.py``).
+same inputs, the CUDA path (``tests/test_gpu_bgemm.py``, ``tests/test_gpu_quant.py``, ``tests/test_gpu_conv.py``).
 """
 
 from __future__ import annotations

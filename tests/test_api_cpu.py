@@ -202,6 +202,12 @@ def test_library_exports_every_declared_symbol():
     assert plan.scratch_bytes == 2 * 17 * 512 * 257 * 4
     assert _C.lib.atb_lut_gemm_plan(65536, 576, 256, 4096, 1 << 25, plan) == 0
     assert (plan.splits, plan.tail_row_tiles, plan.scratch_bytes) == (1, 0, 0)
+    # 112 tiles on 148 SMs (a ResNet-50 stage-3 1x1 layer at batch 16): stream-K deals the 112 x 16 k-chunks out in
+    # runs of 13, and a tile then has at most 3 partial sums
+    assert _C.lib.atb_lut_gemm_plan(3136, 256, 1024, 0, -1, plan) == 0
+    assert (plan.stream_k_units, plan.splits, plan.tail_row_tiles) == (13, 3, 0)
+    assert plan.scratch_bytes == 3 * 3136 * 1025 * 4
+    assert _C.lib.atb_lut_gemm_plan(3136, 256, 1024, 0, 1 << 26, plan) == 0 and plan.stream_k_units == 0
     assert _C.lib.atb_lut_gemm_plan(-1, 1, 1, 0, -1, plan) != 0 and "negative" in _C.last_error()
 
 

@@ -279,3 +279,54 @@ def test_ragged_last_wave_per_batch_weights_and_image_operand(dev):
     yc = ops.lut_conv2d_launch(_t(x8, dev), _t(widx, dev), img, g4, 128)
     np.testing.assert_array_equal(yc.flatten(2).cpu().numpy().astype(np.float64), ref)
     assert torch.equal(yc, ops.lut_conv2d_launch(_t(x8, dev), _t(widx, dev), img, g4, 128, cfg=NO_TAIL))
+
+
+STREAM_K = 1 << 27           # cfg bit 27: stream-K whenever the launch can be one
+
+
+@pytest.mark.parametrize("shape", [(1, 256, 3136, 200), (3, 100, 500, 70), (2, 37, 1300, 64), (1, 600, 70, 130),
+                                   (1, 48, 4000, 1), (7, 40, 9, 5)])
+def test_stream_k_is_bit_identical(dev, shape):
+    """Blocks that work through runs of (tile, k-chunk) units: same integers as the oracle and as whole-tile
+    blocks, with the zero-point epilogue, for L > 1 and L == 1 outputs."""
+    ops = _ops()
+    N, K, L, O = shape
+    rng = np.random.default_rng(sum(shape))
+    x = rng.integers(0, 256, (N, K, L), dtype=np.uint8)
+    w = rng.integers(0, 256, (O, K), dtype=np.uint8)
+    lut = lo.lut_signed_noisy(64, seed=6)
+    img = ops.lut_image(_t(lut.reshape(-1), dev))
+    assert _plan(ops, N * L, K, O, cfg=STREAM_K).stream_k_units > 0
+    ref = c_oracle.bgemm_u8(x, w, lut)
+    y = torch.empty((N, O, L), dtype=torch.float32, device=dev)
+    ops.lut_gemm_launch(_t(x, dev), _t(w, dev), img, y, N, K, L, O, cfg=STREAM_K)
+    np.testing.assert_array_equal(y.cpu().numpy().astype(np.float64), ref)
+    # row-major operand (L == 1) and the asymmetric epilogue
+    xr = np.ascontiguousarray(x.transpose(0, 2, 1).reshape(N * L, K))
+    alpha = _t(rng.uniform(0.5, 2.0, O).astype(np.float32), dev)
+    zx = _t(np.array([91.0], dtype=np.float32), dev)
+    zw = _t(rng.integers(0, 256, O).astype(np.float32), dev)
+    wsum = _t(w.astype(np.int64).sum(axis=1).astype(np.int32), dev)
+    ya = torch.empty((N * L, O), dtype=torch.float32, device=dev)
+    yb = torch.empty_like(ya)
+    for out, cfg in ((ya, STREAM_K), (yb, 1 << 26)):
+        ops.lut_gemm_launch(_t(xr, dev), _t(w, dev), img, out, N * L, K, 1, O, alpha=alpha, zero_x=zx, zero_w=zw,
+                            wsum=wsum, cfg=cfg)
+    assert torch.equal(ya, yb)
+
+
+def test_stream_k_image_operand_and_fp32_table(dev):
+    ops = _ops()
+    rng = np.random.default_rng(90)
+    B, C, H, W, O = 4, 24, 20, 20, 96
+    x8 = rng.integers(-127, 128, (B, C, H, W)).astype(np.int8)
+    widx = rng.integers(0, 256, (O, C * 9), dtype=np.uint8)
+    g4 = ((3, 3), (2, 2), (1, 1), (1, 1))
+    for lut in (lo.lut_affine_asymmetric(), lo.lut_signed_noisy(64, seed=1) + 0.25):     # integer table, fp32-class table
+        img = ops.lut_image(_t(np.asarray(lut, dtype=np.float32).reshape(-1), dev))
+        ya = ops.lut_conv2d_launch(_t(x8, dev), _t(widx, dev), img, g4, 128, cfg=STREAM_K)
+        yb = ops.lut_conv2d_launch(_t(x8, dev), _t(widx, dev), img, g4, 128, cfg=(1 << 26) | (1 << 25))
+        if float(np.asarray(lut).reshape(-1)[0]) == int(np.asarray(lut).reshape(-1)[0]):
+            assert torch.equal(ya, yb)
+        else:                                   # fp32 sums: the partial sums are added in another order
+            assert (ya - yb).abs().max().item() <= 1e-5 * yb.abs().max().item()
