@@ -415,8 +415,6 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
         __syncthreads();
     }
 
-    // a warp whose 32 pixel rows all lie past the end of a ragged last row tile still stages, but looks nothing up
-    const bool has_rows = r0 + warp * TM < r_end;
     int step = 0;
     for (int ci = 0; ci < nch; ++ci) {
         const int k0 = kbeg + ci * kChunk;
@@ -438,11 +436,11 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
             if constexpr (kPipelined) {
                 QuadWords v;
                 if (wnext != nullptr && warp < kQuadRows) fetch_quad(s_tab, wnext, warp, lane, v);
-                if (has_rows) lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
+                lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
                 if (wnext != nullptr && warp < kQuadRows) store_quad(stage_next, warp, lane, v);
             } else {
                 if (wnext != nullptr) stage_quads(stage_next, s_tab, wnext, warp, lane, NW);
-                if (has_rows) lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
+                lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
             }
             __syncthreads();
         }
