@@ -245,7 +245,8 @@ def _resnet50_timed(model, dev, world, rank, steps, per_rank, tag):
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        # thread_local: the NCCL watchdog thread of a multi-rank run must not invalidate the capture
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             y_static = model(x_static)
         for name in ("resident", "e2e"):
             def once():
@@ -369,9 +370,9 @@ def run_gpu_arm(args):
     run_prep, run_gemm, graphed = prep_launches, gemm_launches, False
     try:
         g_prep, g_gemm = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_prep):
+        with torch.cuda.graph(g_prep, capture_error_mode="thread_local"):
             prep_launches()
-        with torch.cuda.graph(g_gemm):
+        with torch.cuda.graph(g_gemm, capture_error_mode="thread_local"):
             gemm_launches()
         g_prep.replay(); g_gemm.replay()
         torch.cuda.synchronize()
@@ -422,6 +423,9 @@ def run_gpu_arm(args):
                 ev_in = torch.cuda.Event()
                 ev_in.record(copy_in)
                 ready.append(ev_in)
+        outs = []        # every result stays allocated until the step has been issued: a result freed early could be
+                         # handed to a later item of the same stream while its device-to-host copy is still pending
+                         # (inside a graph capture the allocator has no record_stream to prevent that)
         for i in range(BATCH):
             c = compute[i & 1]
             c.wait_event(ready[i])
@@ -434,6 +438,7 @@ def run_gpu_arm(args):
                 y_host[i].copy_(yi, non_blocking=True)
             if not capturing:
                 yi.record_stream(copy_out)
+            outs.append(yi)
         main.wait_stream(copy_out)
         for c in compute:
             main.wait_stream(c)
@@ -447,14 +452,27 @@ def run_gpu_arm(args):
     try:
         y_check = y_host.clone()
         g_e2e = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g_e2e):
+        with torch.cuda.graph(g_e2e, capture_error_mode="thread_local"):
             step_e2e(capturing=True)
         y_host.zero_()
         g_e2e.replay()
         torch.cuda.synchronize()
         if torch.equal(y_host, y_check):
             run_e2e, e2e_graphed = g_e2e.replay, True
-    except Exception:
+        else:
+            bad = (y_host != y_check)
+            print(f"[bench] rank {rank}: graph replay differs from direct launches in {int(bad.sum())} of {bad.numel()} "
+                  f"outputs (items {sorted(set(torch.nonzero(bad.flatten(1).any(1)).flatten().tolist()))}); "
+                  "using direct launches", file=sys.stderr, flush=True)
+    except Exception as exc:
+        print(f"[bench] rank {rank}: end-to-end graph capture failed ({type(exc).__name__}: {str(exc)[:200]}); "
+              "using direct launches", file=sys.stderr, flush=True)
+        torch.cuda.synchronize()
+    if not e2e_graphed:
+        # fresh streams: a capture that broke off may have left the old ones unusable
+        copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        compute = [torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)]
+        step_e2e()
         torch.cuda.synchronize()
     e2e_ms = []
     for _ in range(args.steps):
