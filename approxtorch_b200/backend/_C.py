@@ -67,6 +67,7 @@ _SIGNATURES = {
     "atb_custom_bwd_dx": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "atb_custom_bwd_dw": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "atb_lut_dwconv_fwd": (_i, [_vp, _i, _vp, _vp, _vp] + [_i] * 12 + [_i, _vp]),
+    "atb_probe_shared_load": (_i, [_vp, _vp, _i, _i, _vp]),
 }
 
 for _name, (_res, _args) in _SIGNATURES.items():

@@ -75,7 +75,7 @@ _images: dict = {}      # id(lut) -> (weakref to lut, version, image); entries d
 def lut_image(lut: Tensor) -> Tensor:
     """Device image of a 256x256 table (16-bit + fp32, natural + transposed, validity flags).
 
-    Built once per (tensor object, version) and cached; the reference rebuilds its image and makes
+    Built once per (tensor object, version, storage) and cached; the reference rebuilds its image and makes
     three allocations on every call (approxtorch/backend/csrc/claude/bgemm_float_claude.cu:163-192).
     The cache is a derived object keyed on the tensor, never a state_dict entry."""
     _require(lut.is_cuda, "lut must be a CUDA tensor")
@@ -83,13 +83,17 @@ def lut_image(lut: Tensor) -> Tensor:
     _require(lut.numel() == 65536, "lut must have 65536 elements")
     key = id(lut)
     hit = _images.get(key)
-    if hit is not None and hit[0]() is lut and hit[1] == lut._version and hit[2].device == lut.device:
+    same = hit is not None and hit[0]() is lut and hit[2].device == lut.device
+    if same and hit[1] == (lut._version, lut.data_ptr()):
         return hit[2]
     src = lut.detach().contiguous()
-    img = torch.empty(_IMAGE_BYTES, dtype=torch.uint8, device=lut.device)
+    # A tensor that was written in place (DistributedDataParallel re-broadcasts module buffers into the same
+    # storage before every forward) keeps its image buffer: the image is rebuilt into it on the stream, with no
+    # allocation, so every rank does the same work whether or not the bytes changed.
+    img = hit[2] if same else torch.empty(_IMAGE_BYTES, dtype=torch.uint8, device=lut.device)
     with _Guard(lut):
         _check(_lib.atb_lut_prepare(_ptr(src), _ptr(img), _stream(lut)), "atb_lut_prepare")
-    _images[key] = (weakref.ref(lut, lambda _r, k=key: _images.pop(k, None)), lut._version, img)
+    _images[key] = (weakref.ref(lut, lambda _r, k=key: _images.pop(k, None)), (lut._version, lut.data_ptr()), img)
     return img
 
 

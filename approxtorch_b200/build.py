@@ -52,7 +52,22 @@ def _stale(target: str, deps: list[str]) -> bool:
 
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
-    """Compile (if stale) and return the path of the shared library."""
+    """Compile (if stale) and return the path of the shared library.
+
+    Safe to call from several processes at once (every rank of a torchrun job imports the package): the
+    build runs under an exclusive file lock, and the library is linked under a temporary name and moved into
+    place atomically, so no process ever opens a half-written file."""
+    import fcntl
+    os.makedirs(LIB_DIR, exist_ok=True)
+    with open(os.path.join(LIB_DIR, ".build.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            return _build_locked(force, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(force: bool, verbose: bool) -> str:
     srcs = sources()
     headers = glob.glob(os.path.join(SRC_DIR, "*.cuh")) + [HEADER]
     os.makedirs(OBJ_DIR, exist_ok=True)
@@ -79,11 +94,15 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
                 raise RuntimeError(f"nvcc failed on {src}")
     objs = [os.path.join(OBJ_DIR, os.path.basename(s)[:-3] + ".o") for s in srcs]
     if force or jobs or _stale(LIB_PATH, objs):
-        link = [nvcc, "-shared", *ARCH_FLAGS, *_host_compiler_flags(), "-o", LIB_PATH, *objs, "-lcudart"]
+        tmp = f"{LIB_PATH}.{os.getpid()}.tmp"
+        link = [nvcc, "-shared", *ARCH_FLAGS, *_host_compiler_flags(), "-o", tmp, *objs, "-lcudart"]
         proc = subprocess.run(link, capture_output=True, text=True)
         if proc.returncode != 0:
             sys.stderr.write(proc.stdout + proc.stderr)
+            if os.path.exists(tmp):
+                os.remove(tmp)
             raise RuntimeError("link of libapproxtorch_b200.so failed")
+        os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

@@ -24,7 +24,8 @@
 //    lookups.
 //  * Entries are unsigned 16-bit (signed tables carry a +32768 bias removed in the epilogue).  A fetched
 //    word v = lo + 65536*hi is accumulated as S0 += v and S1 += hi; the low channel's sum is
-//    S0 - 65536*S1 (exact modulo 2^32, and all sums are below 2^31 for K <= 32768).
+//    S0 - 65536*S1 (exact modulo 2^32; all sums stay below 2^31 because a block covers at most 32768 k-steps:
+//    longer reductions are split along K and their partial sums added in 64 bits).
 //
 // Integer-valued tables (the int16 / uint16 images) accumulate exactly in int32.  Tables that are
 // not 16-bit exact take the fp32 path: lookups go to the transposed fp32 table in global memory
@@ -46,6 +47,7 @@ constexpr int kQuadPitch = 2056;                         // bytes per quad row (
 constexpr int kStageBytes = kQuadRows * kQuadPitch;      // 32896
 constexpr int kMaxBlockRows = 512;
 constexpr int kTableBytes = 65536 * 2;
+constexpr int kMaxBlockK = 32768;                        // k-steps one block may accumulate in its 32-bit sums
 constexpr int kSmemStage = kTableBytes;
 constexpr int kSmemX = kSmemStage + 2 * kStageBytes;
 constexpr int kSmemW = kSmemX + 2 * kChunk * kMaxBlockRows;
@@ -81,8 +83,8 @@ struct GemmArgs {
 };
 
 // Epilogue arithmetic.  Integer tables: the sum, the zero-point terms and their combination are exact integers,
-// converted to fp32 once (round to nearest even), then scaled and shifted.  Without zero points the sum fits
-// 32 bits (|sum| <= 32768 * K, K <= 32768), with them it needs 64.
+// converted to fp32 once (round to nearest even), then scaled and shifted.  One block's sum fits 32 bits (a block
+// never covers more than 32768 k-steps); sums of split-K partials and the zero-point terms need 64.
 __device__ __forceinline__ float scale_shift(float v, int o, const GemmArgs& a)
 {
     if (a.alpha != nullptr) v = v * __ldg(a.alpha + o);
@@ -99,7 +101,7 @@ __device__ __forceinline__ float finalize_output(long long total, long long xsum
         const long long ws = __ldg(a.wsum + o);
         v = __ll2float_rn(total - zw * xsum - zx * ws + static_cast<long long>(a.K) * zx * zw);
     } else {
-        v = __int2float_rn(static_cast<int>(total));
+        v = __ll2float_rn(total);
     }
     return scale_shift(v, o, a);
 }
@@ -720,6 +722,10 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
     long long tail_rt = 0;
     int sk_units = 0;
     bool allow_sk = wb_rows == 0 && (cfg < 0 || (((cfg >> 26) & 1) == 0 && splits == 0));
+    // A block's 32-bit accumulators hold at most kMaxBlockK looked-up 16-bit entries, so longer reductions are
+    // always split along K (the reduction pass adds the partial sums in 64 bits).
+    const int min_splits = ceil_div(nchunks, kMaxBlockK / kChunk);
+    if (min_splits > 1) { allow_tail = false; allow_sk = false; }
     if (splits == 0) {
         splits = 1;
         double classic = wave_cost(tiles, K, sms);      // modelled cost of the plan chosen so far
@@ -781,6 +787,7 @@ static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_p
             }
         }
     }
+    if (splits < min_splits) splits = min_splits;
     if (sk_units == 0) {
         if (splits > nchunks) splits = nchunks;
         const int cps = ceil_div(nchunks, splits);
@@ -838,7 +845,6 @@ static int launch_variant(int nwarps, bool dp2a, bool sk, dim3 grid, const GemmA
 static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes, cudaStream_t stream)
 {
     if (a.R == 0 || a.O == 0) return ATB_OK;
-    ATB_REQUIRE(a.K <= 32768, "K above 32768 is not supported (int32 accumulators)");
     ATB_REQUIRE(a.wb_rows == 0 || a.R % a.wb_rows == 0, "rows must be a multiple of wb_rows");
     if (a.K == 0) {
         lut_gemm_empty_k_kernel<<<grid_for(a.R * a.O, 256, 4096), 256, 0, stream>>>(a);
@@ -852,6 +858,7 @@ static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes,
     ATB_REQUIRE(row_tiles <= 2147483647LL, "too many row tiles");
     const int col_tiles = ceil_div(a.O, kStagedCols);
     ATB_REQUIRE(col_tiles <= 65535, "too many output channels");
+    ATB_REQUIRE(plan.splits <= 65535, "K too large");
     if (plan.scratch_bytes > 0) {
         if (scratch == nullptr || scratch_bytes < plan.scratch_bytes) {
             set_error("split-K needs %zu bytes of scratch, got %zu", plan.scratch_bytes, scratch_bytes);
@@ -952,7 +959,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[ATB_STATIC_SCRAT
 static int static_scratch_address(void** out)
 {
     // The symbol name is only a host-side handle: the device address has to be asked for, once per
-    // device, while that device is current.
+    // device, while that device is current.  Threads that race here all store the same value.
     static void* cached[64] = {nullptr};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -973,7 +980,14 @@ static int static_scratch_address(void** out)
     return ATB_OK;
 }
 
-extern "C" size_t atb_static_scratch_bytes(void) { return ATB_STATIC_SCRATCH_BYTES; }
+// Also performs the per-device address lookup for the current device, so that a host can get it out of the way
+// before a stream capture without running a GEMM (a failure here is reported again by the GEMM call).
+extern "C" size_t atb_static_scratch_bytes(void)
+{
+    void* unused = nullptr;
+    (void)static_scratch_address(&unused);
+    return ATB_STATIC_SCRATCH_BYTES;
+}
 
 extern "C" int atb_lut_bgemm_fwd_noalloc(const uint8_t* x, const uint8_t* w, const void* lut_image, float* y,
                                          int N, int K, int L, int O, int wb_rows, long long w_batch_stride,
@@ -1013,7 +1027,7 @@ extern "C" int atb_lut_conv2d_fwd(const void* x, int dtype, const uint8_t* w, co
     ATB_REQUIRE(conv_out_shape(H, W, kh, kw, sh, sw, ph, pw, dh, dw, &OH, &OW), "conv geometry yields empty output");
     if (N == 0 || O == 0) return ATB_OK;
     const long long K = static_cast<long long>(C) * kh * kw;
-    ATB_REQUIRE(K <= 32768, "C*kh*kw above 32768 is not supported");
+    ATB_REQUIRE(K <= 2147483647LL - kChunk, "C*kh*kw too large");
     ATB_REQUIRE(y != nullptr && (K == 0 || (x != nullptr && w != nullptr)), "null operand");
     int rc = check_epilogue(zero_x, zero_w, wsum);
     if (rc != ATB_OK) return rc;

@@ -179,18 +179,27 @@ __global__ void stats_init_kernel(float* result)
     result[2] = __int_as_float(0xff800000);    // -inf
 }
 
+// Float min / max through integer atomics.  Non-negative floats order like signed ints, negative floats order
+// in reverse like unsigned ints, so the branch is taken on the SIGN BIT (-0.0 belongs with the negatives; a
+// comparison with 0.0f would send it down the signed path as INT_MIN and wipe out a stored negative minimum).
 __device__ __forceinline__ void atomic_min_float(float* addr, float v)
 {
-    if (v >= 0.0f) atomicMin(reinterpret_cast<int*>(addr), __float_as_int(v));
+    if (__float_as_int(v) >= 0) atomicMin(reinterpret_cast<int*>(addr), __float_as_int(v));
     else atomicMax(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
 }
 __device__ __forceinline__ void atomic_max_float(float* addr, float v)
 {
-    if (v >= 0.0f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+    if (__float_as_int(v) >= 0) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
     else atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
 }
+// NaN markers that no later atomic of the two functions above can displace: the minimum slot takes the NaN
+// with the sign bit set (largest unsigned, negative as an int), the maximum slot the positive NaN (largest int,
+// smaller as an unsigned than any negative float).
+__device__ __forceinline__ void atomic_min_nan(float* addr) { atomicMax(reinterpret_cast<unsigned int*>(addr), 0xffc00000u); }
+__device__ __forceinline__ void atomic_max_nan(float* addr) { atomicMax(reinterpret_cast<int*>(addr), 0x7fc00000); }
 
-// result[0] = max|x| (NaN wins, like torch's max), result[1] = min, result[2] = max
+// result[0] = max|x|, result[1] = min, result[2] = max; a NaN anywhere makes all three NaN, as torch's
+// max / amin / amax do
 template <bool VEC, bool MINMAX>
 __global__ void stats_kernel(const float* __restrict__ x, long long numel, float* __restrict__ result)
 {
@@ -198,7 +207,7 @@ __global__ void stats_kernel(const float* __restrict__ x, long long numel, float
     auto take = [&](float v) {
         const float a = fabsf(v);
         am = (a > am || a != a) ? a : am;
-        if (MINMAX) { mn = fminf(mn, v); mx = fmaxf(mx, v); }
+        if (MINMAX) { mn = (v < mn || v != v) ? v : mn; mx = (v > mx || v != v) ? v : mx; }
     };
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     const long long t0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -215,13 +224,17 @@ __global__ void stats_kernel(const float* __restrict__ x, long long numel, float
         const float o = __shfl_down_sync(0xffffffffu, am, off);
         am = (o > am || o != o) ? o : am;
         if (MINMAX) {
-            mn = fminf(mn, __shfl_down_sync(0xffffffffu, mn, off));
-            mx = fmaxf(mx, __shfl_down_sync(0xffffffffu, mx, off));
+            const float on = __shfl_down_sync(0xffffffffu, mn, off), ox = __shfl_down_sync(0xffffffffu, mx, off);
+            mn = (on < mn || on != on) ? on : mn;
+            mx = (ox > mx || ox != ox) ? ox : mx;
         }
     }
     if ((threadIdx.x & 31) == 0) {
         atomicMax(reinterpret_cast<int*>(result), __float_as_int(am));   // |x| >= 0: int order == float order, NaN highest
-        if (MINMAX) { atomic_min_float(result + 1, mn); atomic_max_float(result + 2, mx); }
+        if (MINMAX) {
+            if (mn != mn) atomic_min_nan(result + 1); else atomic_min_float(result + 1, mn);
+            if (mx != mx) atomic_max_nan(result + 2); else atomic_max_float(result + 2, mx);
+        }
     }
 }
 

@@ -66,9 +66,39 @@ __global__ void lut_bias_kernel(LutImage* __restrict__ img)
     words[i] ^= 0x80008000u;
 }
 
+// Measurement aid: the rate at which an SM serves conflict-free 8-byte shared-memory loads, the instruction
+// the LUT GEMM's lookups are made of.  Every thread issues `iters` x 8 independent loads whose 16 lanes per
+// half-warp cover all 32 banks exactly once (consecutive 8-byte slots), adds the words up and stores the sum so
+// that nothing can be optimised away.  Bank words served = threads x iters x 8 x 2.
+__global__ void __launch_bounds__(1024, 1) shared_load_probe_kernel(const unsigned* __restrict__ seed, unsigned* __restrict__ out,
+                                                                    int iters)
+{
+    __shared__ uint2 buf[4096];                            // 32 KB
+    for (int i = threadIdx.x; i < 4096; i += blockDim.x) buf[i] = make_uint2(seed[i & 255], seed[(i + 1) & 255]);
+    __syncthreads();
+    unsigned a = 0u, b = 0u, idx = threadIdx.x;
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint2 v = buf[(idx + 512u * u) & 4095u];
+            a += v.x;
+            b += v.y;
+        }
+        idx += 32u;
+    }
+    out[blockIdx.x * blockDim.x + threadIdx.x] = a + b;
+}
+
 }  // namespace atb
 
 using namespace atb;
+
+extern "C" int atb_probe_shared_load(const unsigned* seed256, unsigned* out, int blocks, int iters, void* stream)
+{
+    ATB_REQUIRE(seed256 != nullptr && out != nullptr && blocks > 0 && iters >= 0, "bad arguments");
+    shared_load_probe_kernel<<<blocks, 1024, 0, static_cast<cudaStream_t>(stream)>>>(seed256, out, iters);
+    return check_launch("shared_load_probe_kernel");
+}
 
 extern "C" const char* atb_last_error(void) { return g_error; }
 extern "C" int atb_version(void) { return 100; }

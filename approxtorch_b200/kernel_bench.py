@@ -1,0 +1,274 @@
+"""Per-kernel timings of the hot path with their roofline fractions (CUDA events, device-resident operands).
+
+    python -m approxtorch_b200.kernel_bench [--only stream,backward,custom,layers,lds] [--batch 16]
+
+``bench.py`` calls :func:`run_all` and reports the result under ``extra``; each function here can also be run on
+its own (the commands the profiler summaries under ``profiles/`` were captured with).
+
+What is measured, and against what:
+
+* ``lds``      - conflict-free 8-byte shared-memory loads (the instruction the LUT GEMM's lookups are made of):
+                 measured bank words / clk / SM beside the architectural 32;
+* ``stream``   - the HBM-bound kernels (abs-max / min-max statistics, fused fake-quant to a 1-byte image, the
+                 operator-form fake-quant forward and backward) on a 256 MiB fp32 tensor: algorithmic bytes / time
+                 against the measured copy bandwidth;
+* ``backward`` - STE / LRE image-space backward (grad_x, grad_w) on the ResNet-18 layer set: 2*B*L*K*O flop / time;
+* ``custom``   - custom-pair backward and the depthwise forward on the single-layer configuration's shape: lookups/s;
+* ``layers``   - the LUT conv forward per distinct ResNet-50 layer shape (with the unsigned zero-point epilogue):
+                 plan chosen, time, lookups/s, fraction of the lookup roofline, and the multiplicity-weighted total.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+
+import torch
+
+from .backend import _C, ops
+
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# distinct approximate-conv shapes of torchvision's ResNet-50 (all but the stem): (C, H, O, k, stride, pad, count)
+RESNET50_LAYERS = [
+    (64, 56, 64, 1, 1, 0, 1), (64, 56, 64, 3, 1, 1, 3), (64, 56, 256, 1, 1, 0, 4), (256, 56, 64, 1, 1, 0, 2),
+    (256, 56, 128, 1, 1, 0, 1), (128, 56, 128, 3, 2, 1, 1), (128, 28, 512, 1, 1, 0, 4), (256, 56, 512, 1, 2, 0, 1),
+    (512, 28, 128, 1, 1, 0, 3), (128, 28, 128, 3, 1, 1, 3),
+    (512, 28, 256, 1, 1, 0, 1), (256, 28, 256, 3, 2, 1, 1), (256, 14, 1024, 1, 1, 0, 6), (512, 28, 1024, 1, 2, 0, 1),
+    (1024, 14, 256, 1, 1, 0, 5), (256, 14, 256, 3, 1, 1, 5),
+    (1024, 14, 512, 1, 1, 0, 1), (512, 14, 512, 3, 2, 1, 1), (512, 7, 2048, 1, 1, 0, 3), (1024, 14, 2048, 1, 2, 0, 1),
+    (2048, 7, 512, 1, 1, 0, 2), (512, 7, 512, 3, 1, 1, 2),
+]
+# approximate-conv shapes of the CIFAR-stem ResNet-18: (C, H, O, k, stride, pad, count)
+RESNET18_CIFAR_LAYERS = [
+    (64, 32, 64, 3, 1, 1, 4), (64, 32, 128, 3, 2, 1, 1), (128, 16, 128, 3, 1, 1, 3), (64, 32, 128, 1, 2, 0, 1),
+    (128, 16, 256, 3, 2, 1, 1), (256, 8, 256, 3, 1, 1, 3), (128, 16, 256, 1, 2, 0, 1),
+    (256, 8, 512, 3, 2, 1, 1), (512, 4, 512, 3, 1, 1, 3), (256, 8, 512, 1, 2, 0, 1),
+]
+
+
+def peaks(dev):
+    """Roofline denominators: measured HBM copy bandwidth and max SM clock when the measurement file is present."""
+    out = {"hbm_gbs": 6650.0, "sm_max_mhz": 1965.0, "source": "fallback"}
+    try:
+        with open(os.path.join(_REPO, "MEASURED_PEAKS.json")) as f:
+            m = json.load(f)
+        out.update(hbm_gbs=float(m["hbm_gbs"]), sm_max_mhz=float(m["sm_max_mhz"]), source="MEASURED_PEAKS.json")
+    except Exception:
+        pass
+    out["sms"] = torch.cuda.get_device_properties(dev).multi_processor_count
+    out["lookup_peak"] = out["sms"] * 32 * out["sm_max_mhz"] * 1e6
+    return out
+
+
+def _time_ms(fn, iters=10, warmup=3, flush=None):
+    """Mean device time of fn() in ms.  ``flush``: a buffer larger than L2 rewritten before every timed call (outside
+    the event pair) for kernels whose operands would otherwise stay in L2."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / iters
+
+
+# ----------------------------------------------------------------------------------------------- shared-memory peak
+def lds_peak(dev, pk=None):
+    pk = pk or peaks(dev)
+    blocks, iters = pk["sms"], 4096
+    seed = torch.randint(0, 2 ** 31 - 1, (256,), dtype=torch.int32, device=dev)
+    out = torch.empty(blocks * 1024, dtype=torch.int32, device=dev)
+    st = ops._stream(out)
+
+    def fn():
+        _C.check(_C.lib.atb_probe_shared_load(ops._ptr(seed), ops._ptr(out), blocks, iters, st), "probe")
+    ms = _time_ms(fn, iters=5)
+    words = blocks * 1024 * iters * 8 * 2
+    per_clk_sm = words / (ms * 1e-3) / (pk["sms"] * pk["sm_max_mhz"] * 1e6)
+    return {"bank_words_per_clk_per_sm_measured": per_clk_sm, "architectural": 32,
+            "measured_lookup_peak": per_clk_sm * pk["sms"] * pk["sm_max_mhz"] * 1e6,
+            "note": "conflict-free 8-byte ld.shared, 32 warps/SM, 8 independent loads in flight per thread; "
+                    "clock taken as the max SM clock"}
+
+
+# ----------------------------------------------------------------------------------------------- HBM-bound kernels
+def stream_kernels(dev, pk=None, mib=256):
+    pk = pk or peaks(dev)
+    n = mib * (1 << 20) // 4
+    x = torch.randn(n, device=dev)
+    scale = torch.tensor(0.03, device=dev)
+    zero = torch.tensor(117.0, device=dev)
+    q8, mask = ops.quantize_image(x, scale, None, -127, 127)
+    go = torch.randn(n, device=dev)
+    cases = {
+        "stats_kernel(absmax)": (lambda: ops.absmax(x), 4),
+        "stats_kernel(absmax+min+max)": (lambda: ops.absmax(x, want_minmax=True), 4),
+        "quantize_image_kernel(int8+mask)": (lambda: ops.quantize_image(x, scale, None, -127, 127), 6),
+        "quantize_image_kernel(uint8,no mask)": (lambda: ops.quantize_image(x, scale, zero, 0, 255, want_mask=False), 5),
+        "fakequant_fwd_kernel": (lambda: ops._fakequant(x, scale, None, -127, 127), 9),
+        "fakequant_bwd_kernel": (lambda: ops._fakequant_backward(go, mask, scale), 9),
+    }
+    out = {}
+    for name, (fn, bytes_per_elem) in cases.items():
+        ms = _time_ms(fn)
+        gbs = n * bytes_per_elem / (ms * 1e-3) / 1e9
+        out[name] = {"ms": ms, "bytes_per_elem": bytes_per_elem, "gbs": gbs, "frac_of_hbm_peak": gbs / pk["hbm_gbs"]}
+    out["tensor_mib"] = mib
+    out["peak_gbs"] = pk["hbm_gbs"]
+    out["peak_source"] = pk["source"]
+    return out
+
+
+# ----------------------------------------------------------------------------------------------- dense backward
+def backward_kernels(dev, batch=256, layers=None, mode="ste"):
+    """grad_x and grad_w of the image-space STE / LRE backward per layer shape; flop = 2 * B*OH*OW * C*k*k * O."""
+    layers = layers or RESNET18_CIFAR_LAYERS
+    rows, tot = [], {"gx_ms": 0.0, "gw_ms": 0.0, "flop": 0.0}
+    table = ops.decode_table(dev, 128) if mode == "ste" else torch.randn(256, device=dev)
+    for (C, H, O, k, s, p, count) in layers:
+        x8 = torch.randint(-127, 128, (batch, C, H, H), dtype=torch.int8, device=dev)
+        widx = torch.randint(0, 256, (O, C * k * k), dtype=torch.uint8, device=dev)
+        g4 = ((k, k), (s, s), (p, p), (1, 1))
+        OH = (H + 2 * p - k) // s + 1
+        go = torch.randn(batch, O, OH, OH, device=dev)
+        gs = torch.rand(O, device=dev)
+        gx_ms = _time_ms(lambda: ops.lre_conv_backward(go, x8, widx, table, table, g4, 128, go_scale=gs, need_w=False), iters=5, warmup=2)
+        gw_ms = _time_ms(lambda: ops.lre_conv_backward(go, x8, widx, table, table, g4, 128, go_scale=gs, need_x=False), iters=5, warmup=2)
+        flop = 2.0 * batch * OH * OH * C * k * k * O
+        rows.append({"C": C, "H": H, "O": O, "k": k, "stride": s, "count": count, "grad_x_ms": gx_ms, "grad_w_ms": gw_ms,
+                     "grad_x_tflops": flop / gx_ms / 1e9, "grad_w_tflops": flop / gw_ms / 1e9})
+        tot["gx_ms"] += gx_ms * count
+        tot["gw_ms"] += gw_ms * count
+        tot["flop"] += flop * count
+    return {"batch": batch, "mode": mode, "layers": rows,
+            "total_grad_x_ms": tot["gx_ms"], "total_grad_w_ms": tot["gw_ms"],
+            "total_grad_x_tflops": tot["flop"] / tot["gx_ms"] / 1e9, "total_grad_w_tflops": tot["flop"] / tot["gw_ms"] / 1e9,
+            "fp32_fma_peak_tflops": 74.4}
+
+
+# ----------------------------------------------------------------------------------------------- custom pair / depthwise
+def custom_kernels(dev, pk=None):
+    """The single-layer configuration's GEMM shape (N=8, K=576, L=1024, O=64): custom-pair dX / dW as lookups/s
+    (each touches every (x, w) pair once), and a depthwise 3x3 forward on [64,128,56,56]."""
+    pk = pk or peaks(dev)
+    N, K, L, O = 8, 576, 1024, 64
+    x = torch.randint(0, 256, (N, K, L), dtype=torch.uint8, device=dev)
+    w = torch.randint(0, 256, (O, K), dtype=torch.uint8, device=dev)
+    dy = torch.randn(N, O, L, device=dev)
+    tab = torch.randn(65536, device=dev)
+    out = {}
+    pairs = float(N) * K * L * O
+    for name, fn in (("custom_dx", lambda: ops.bgemm_custom_grad_uint8_dx(x, w, dy, tab)),
+                     ("custom_dw", lambda: ops.bgemm_custom_grad_uint8_dw(x, w, dy, tab))):
+        ms = _time_ms(fn, iters=5, warmup=2)
+        out[name] = {"ms": ms, "lookups_per_s": pairs / (ms * 1e-3), "frac_of_lookup_peak": pairs / (ms * 1e-3) / pk["lookup_peak"]}
+    B, C, H = 64, 128, 56
+    lut = torch.round(torch.randn(65536, device=dev) * 100)
+    x8 = torch.randint(-127, 128, (B, C, H, H), dtype=torch.int8, device=dev)
+    wd = torch.randint(-127, 128, (C, 9), device=dev).float()
+    ms = _time_ms(lambda: ops.dwconv_fake_int8_claude(x8, wd, lut, 3, 1, 1, 1), iters=5, warmup=2)
+    taps = float(B) * C * H * H * 9
+    out["dwconv_3x3"] = {"ms": ms, "lookups_per_s": taps / (ms * 1e-3), "shape": [B, C, H, H],
+                         "hbm_gbs": B * C * H * H * 5 / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": B * C * H * H * 5 / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+    return out
+
+
+# ----------------------------------------------------------------------------------------------- LUT conv per layer
+def _plan_name(R, K, O):
+    plan = _C.GemmPlan()
+    _C.check(_C.lib.atb_lut_gemm_plan(R, K, O, 0, -1, ctypes.byref(plan)), "plan")
+    if plan.stream_k_units:
+        kind = f"stream-K({plan.stream_k_units})"
+    elif plan.tail_row_tiles:
+        kind = f"waves+tail x{plan.splits}"
+    elif plan.splits > 1:
+        kind = f"split-K x{plan.splits}"
+    else:
+        kind = "whole tiles"
+    return f"{plan.block_rows} rows, {kind}"
+
+
+def lut_conv_layers(dev, batch, pk=None, layers=None):
+    """Unsigned LUT conv forward (zero-point epilogue, scale) per distinct ResNet-50 layer shape at ``batch`` images."""
+    pk = pk or peaks(dev)
+    layers = layers or RESNET50_LAYERS
+    lut = (torch.arange(256, device=dev).view(-1, 1) * torch.arange(256, device=dev).view(1, -1) // 64 * 64).float().reshape(-1)
+    img = ops.lut_image(lut)
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev)
+    rows, tot_ms, tot_macs = [], 0.0, 0.0
+    for (C, H, O, k, s, p, count) in layers:
+        x = torch.randint(0, 256, (batch, C, H, H), dtype=torch.uint8, device=dev)
+        w = torch.randint(0, 256, (O, C * k * k), dtype=torch.uint8, device=dev)
+        g4 = ((k, k), (s, s), (p, p), (1, 1))
+        zx, zw = torch.tensor(117.0, device=dev), torch.full((O,), 120.0, device=dev)
+        ws = w.sum(dim=1, dtype=torch.int32)
+        al = torch.rand(O, device=dev)
+        OH = (H + 2 * p - k) // s + 1
+        R, K = batch * OH * OH, C * k * k
+        ms = _time_ms(lambda: ops.lut_conv2d_launch(x, w, img, g4, -1, alpha=al, zero_x=zx, zero_w=zw, wsum=ws),
+                      iters=5, warmup=2, flush=flush)
+        macs = float(R) * K * O
+        rows.append({"C": C, "H": H, "O": O, "k": k, "stride": s, "count": count, "R": R, "K": K, "plan": _plan_name(R, K, O),
+                     "ms": ms, "lookups_per_s": macs / (ms * 1e-3), "frac_of_lookup_peak": macs / (ms * 1e-3) / pk["lookup_peak"]})
+        tot_ms += ms * count
+        tot_macs += macs * count
+    return {"batch": batch, "layers": rows, "total_ms": tot_ms, "total_lut_macs": tot_macs,
+            "lookups_per_s": tot_macs / (tot_ms * 1e-3), "frac_of_lookup_peak": tot_macs / (tot_ms * 1e-3) / pk["lookup_peak"],
+            "l2": "a 160 MiB buffer is rewritten before every timed call"}
+
+
+def run_all(dev, which=("lds", "stream", "backward", "custom", "layers"), batches=(128, 16)):
+    pk = peaks(dev)
+    out = {"peaks": pk}
+    for name in which:
+        try:
+            if name == "lds":
+                out["lds"] = lds_peak(dev, pk)
+            elif name == "stream":
+                out["stream"] = stream_kernels(dev, pk)
+            elif name == "backward":
+                out["backward_ste_resnet18_cifar_b256"] = backward_kernels(dev)
+            elif name == "custom":
+                out["custom"] = custom_kernels(dev, pk)
+            elif name == "layers":
+                for b in batches:
+                    out[f"resnet50_lut_conv_layers_b{b}"] = lut_conv_layers(dev, b, pk)
+        except Exception as exc:                       # a measurement aid must not take the headline line down
+            out[name + "_error"] = f"{type(exc).__name__}: {exc}"[:300]
+        torch.cuda.empty_cache()
+    return out
+
+
+def _print_table(res):
+    for key, val in res.items():
+        if isinstance(val, dict) and "layers" in val:
+            print(f"== {key}")
+            for r in val["layers"]:
+                print("  " + "  ".join(f"{k}={v:.4g}" if isinstance(v, float) else f"{k}={v}" for k, v in r.items()))
+            print("  " + "  ".join(f"{k}={v:.4g}" if isinstance(v, float) else f"{k}={v}" for k, v in val.items() if k != "layers"))
+        else:
+            print(f"== {key}: {json.dumps(val)}")
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="lds,stream,backward,custom,layers")
+    ap.add_argument("--batch", default="128,16")
+    ap.add_argument("--json", action="store_true")
+    a = ap.parse_args()
+    device = torch.device("cuda:0")
+    result = run_all(device, tuple(a.only.split(",")), tuple(int(b) for b in a.batch.split(",")))
+    if a.json:
+        print(json.dumps(result))
+    else:
+        _print_table(result)

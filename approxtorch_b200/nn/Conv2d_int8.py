@@ -156,6 +156,28 @@ class Conv2d_int8(nn.Module):
             self.scale_w.copy_(torch.where(absmax > 0, absmax / self._qmax_w, torch.ones_like(absmax)))
 
     # ------------------------------------------------------------------ forward
+    def _frozen_operands(self):
+        """(weight indices, alpha = s_x * s_w[o]) for the no-gradient forward, rebuilt only when the weights or the
+        scales have changed (in-place versions and storage are the key): a frozen eval model quantises its weights
+        once, not once per forward."""
+        srcs = (self.weight, self.scale_x, self.scale_w)
+        key = tuple((t._version, t.data_ptr(), t.device) for t in srcs)
+        hit = getattr(self, "_frozen", None)
+        if hit is None or hit[0] != key:
+            widx, _, _, _ = _ops.quantize_weight(self.weight.detach(), self.scale_w, None, -self._qmax_w, self._qmax_w,
+                                                 128, want_mask=False)
+            hit = (key, widx, (self.scale_x * self.scale_w).contiguous())
+            self._frozen = hit
+        return hit[1:]
+
+    def _forward_no_grad(self, x, g4):
+        """Inference: int8 image, cached weight indices, LUT conv with the dequantisation in its epilogue.  The same
+        arithmetic, bit for bit, as the fused training route."""
+        xq8, _ = _ops.quantize_image(x, self.scale_x, None, self.qmin, self.qmax, want_mask=False)
+        widx, alpha = self._frozen_operands()
+        beta = None if self.bias is None else self.bias.detach().contiguous()
+        return _ops.lut_conv2d_launch(xq8, widx, _ops.lut_image(self.lut), g4, 128, alpha=alpha, beta=beta)
+
     def forward(self, x: torch.Tensor):
         if self.training and self.update_scale:
             self._update_scale(x)
@@ -163,6 +185,10 @@ class Conv2d_int8(nn.Module):
 
         g4 = (tuple(self.kernel_size), tuple(self.stride), tuple(self.padding), tuple(self.dilation))
         fused = self.groups == 1 and self.grad in ('ste', 'lre') and x.is_cuda and x.dtype == torch.float32
+        wants_grad = torch.is_grad_enabled() and (
+            x.requires_grad or self.weight.requires_grad or (self.bias is not None and self.bias.requires_grad))
+        if fused and not wants_grad:
+            return self._forward_no_grad(x, g4)
         if fused:
             return bgemm_int8.approx_conv2d_int8(
                 x, self.weight, self.bias, self.scale_x, self.scale_w, self.lut,

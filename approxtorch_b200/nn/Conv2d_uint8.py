@@ -207,15 +207,28 @@ class Conv2d_uint8(nn.Module):
             self.zero_w.copy_(zw)
 
     # ------------------------------------------------------------------ forward
+    def _frozen_operands(self):
+        """(weight indices, their row sums, alpha = s_x * s_w, zero_w) for the no-gradient forward, rebuilt only when
+        the weights or the quantisation buffers they derive from have changed (in-place versions and storage are
+        the key): a frozen eval model quantises its weights once, not once per forward."""
+        srcs = (self.weight, self.scale_x, self.scale_w, self.zero_w)
+        key = tuple((t._version, t.data_ptr(), t.device) for t in srcs)
+        hit = getattr(self, "_frozen", None)
+        if hit is None or hit[0] != key:
+            widx, _, _, wsum = _ops.quantize_weight(self.weight.detach(), self.scale_w, self.zero_w, self.qmin,
+                                                    self.qmax, 0, want_mask=False, want_sum=True)
+            alpha = (self.scale_x * self.scale_w).contiguous()
+            hit = (key, widx, wsum, alpha, self.zero_w.contiguous())
+            self._frozen = hit
+        return hit[1:]
+
     def _forward_fused(self, x):
         xq8, _ = _ops.quantize_image(x, self.scale_x, self.zero_x, self.qmin, self.qmax, want_mask=False)
-        widx, _, _, wsum = _ops.quantize_weight(self.weight.detach(), self.scale_w, self.zero_w, self.qmin,
-                                                self.qmax, 0, want_mask=False, want_sum=True)
-        alpha = (self.scale_x * self.scale_w).contiguous()
+        widx, wsum, alpha, zero_w = self._frozen_operands()
         beta = None if self.bias is None else self.bias.detach().contiguous()
         g4 = (tuple(self.kernel_size), tuple(self.stride), tuple(self.padding), tuple(self.dilation))
         return _ops.lut_conv2d_launch(xq8, widx, _ops.lut_image(self.lut), g4, -1, alpha=alpha, beta=beta,
-                                      zero_x=self.zero_x, zero_w=self.zero_w.contiguous(), wsum=wsum)
+                                      zero_x=self.zero_x, zero_w=zero_w, wsum=wsum)
 
     def forward(self, x: torch.Tensor):
         B, C, H, W = x.shape

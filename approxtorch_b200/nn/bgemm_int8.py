@@ -262,7 +262,9 @@ class _approx_conv2d_int8(Function):
         beta = None if bias is None else bias.detach().contiguous()
         y = _ops.lut_conv2d_launch(xq8, widx, _ops.lut_image(lut), g4, _PAD_INDEX, alpha=alpha, beta=beta)
         if need_gx or need_gw or (bias is not None and ctx.needs_input_grad[2]):
-            keep = [xq8, widx, alpha, scale_x, scale_w]
+            # copies of the scale buffers: the module updates them in place on its next training forward, which may
+            # come before this backward (the reference keeps a clamped copy for the same reason)
+            keep = [xq8, widx, alpha, scale_x.clone(), scale_w.clone()]
             keep += [t for t in (xmask, wmask) if t is not None]
             if mode == 'lre':
                 keep += [dx, dw]

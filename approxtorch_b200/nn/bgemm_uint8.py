@@ -128,6 +128,9 @@ class _approx_conv2d_uint8(Function):
         alpha = (scale_x * scale_w).contiguous()
         beta = None if bias is None else bias.detach().contiguous()
         zw = zero_w.contiguous()
+        if need_gx or need_gw:
+            # private copies: the module rewrites these buffers in place on its next training forward
+            scale_x, zero_x, scale_w, zw = scale_x.clone(), zero_x.clone(), scale_w.clone(), zw.clone()
         y = _ops.lut_conv2d_launch(xq8, widx, _ops.lut_image(lut), g4, -1, alpha=alpha, beta=beta,
                                    zero_x=zero_x, zero_w=zw, wsum=wsum)
         if need_gx or need_gw or (bias is not None and ctx.needs_input_grad[2]):

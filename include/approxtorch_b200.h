@@ -106,8 +106,11 @@ int atb_lut_bgemm_fwd(const uint8_t* x, const uint8_t* w, const void* lut_image,
  * global memory that is part of the library image: every GPU that loads the library holds it until the
  * process exits.  Arguments and results are those of atb_lut_bgemm_fwd; shapes whose plan needs more
  * scratch than the area holds are refused with ATB_ERR_SCRATCH (atb_lut_gemm_plan reports the need, and
- * cfg can force fewer splits).  The first call on a device looks the area's address up, so make that
- * call before starting any stream capture.  All calls on a device share the area and it keeps what the
+ * cfg can force fewer splits).  The area's device address is looked up once per device, by the first of
+ * atb_static_scratch_bytes() or atb_lut_bgemm_fwd_noalloc() called while that device is current: call
+ * atb_static_scratch_bytes() on every device you will use before starting any stream capture.  The
+ * address is remembered per device ordinal for the life of the process (a cudaDeviceReset invalidates it;
+ * do not reset a device between calls).  All calls on a device share the area and it keeps what the
  * last call left; the kernels overwrite every element they later read, so nothing has to be cleared,
  * but two such calls that overlap in time on one GPU (different streams) race on it. */
 #define ATB_STATIC_SCRATCH_BYTES (32u << 20)
@@ -197,6 +200,13 @@ int atb_custom_bwd_dw(const uint8_t* x, const uint8_t* w, const float* dy, const
 int atb_lut_dwconv_fwd(const void* x, int dtype, const uint8_t* widx /*[C, kh*kw]*/, const void* lut_image,
                        float* y, int N, int C, int H, int W, int kh, int kw, int sh, int sw, int ph, int pw,
                        int dh, int dw, int pad_index, void* stream);
+
+/* ---- measurement aid (no counterpart in the reference) ---------------------------------------------
+ * Launches `blocks` blocks of 1024 threads that each issue iters x 8 conflict-free 8-byte shared-memory loads
+ * per thread (2 bank words each) and store a checksum to out[blocks * 1024]; timed by the caller, it gives the
+ * shared-memory load rate an SM really sustains, the denominator of the LUT GEMM's roofline.
+ * seed256: 256 arbitrary words. */
+int atb_probe_shared_load(const unsigned* seed256, unsigned* out, int blocks, int iters, void* stream);
 
 #ifdef __cplusplus
 }

@@ -22,6 +22,16 @@ _NAME = "ref_cpu_bgemm"
 _loaded = False
 
 
+def reference_root() -> str | None:
+    """Where the reference checkout lies: ``$APPROXTORCH_REF`` when set, else a directory named ``reference``
+    beside this repository; None when neither exists."""
+    env = os.environ.get("APPROXTORCH_REF")
+    if env:
+        return env if os.path.isdir(env) else None
+    sibling = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return sibling if os.path.isdir(sibling) else None
+
+
 def _source(reference_root: str) -> str:
     return os.path.join(reference_root, "approxtorch", "backend", "csrc", "cpu", "bgemm.cpp")
 
@@ -31,11 +41,12 @@ def built_library() -> str | None:
     return hits[0] if hits else None
 
 
-def build(reference_root: str = "/root/reference") -> str | None:
-    """Compile the reference CPU operator; returns the library path or None when
-    the reference checkout is absent."""
-    src = _source(reference_root)
-    if not os.path.exists(src):
+def build(root: str | None = None) -> str | None:
+    """Compile the reference CPU operator; returns the library path (a prebuilt one when the reference
+    checkout is absent) or None."""
+    root = root or reference_root()
+    src = _source(root) if root else None
+    if src is None or not os.path.exists(src):
         return built_library()
     lib = built_library()
     if lib and os.path.getmtime(lib) >= os.path.getmtime(src):

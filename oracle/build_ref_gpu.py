@@ -37,9 +37,14 @@ def built_library() -> str | None:
     return hits[0] if hits else None
 
 
-def build(reference_root: str = "/root/reference") -> str | None:
-    srcs = [os.path.join(reference_root, s) for s in SOURCES]
-    if not all(os.path.exists(s) for s in srcs):
+def build(root: str | None = None) -> str | None:
+    repo = os.path.dirname(_HERE)
+    if repo not in sys.path:
+        sys.path.insert(0, repo)
+    from oracle.build_ref import reference_root
+    root = root or reference_root()
+    srcs = [os.path.join(root, s) for s in SOURCES] if root else []
+    if not srcs or not all(os.path.exists(s) for s in srcs):
         return built_library()
     lib = built_library()
     if lib and all(os.path.getmtime(lib) >= os.path.getmtime(s) for s in srcs):

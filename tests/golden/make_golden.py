@@ -24,9 +24,12 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-
 sys.path.insert(0, REPO)
+from oracle.build_ref import reference_root        # noqa: E402
+
+REF = sys.argv[1] if len(sys.argv) > 1 else reference_root()
+if not REF:
+    sys.exit("usage: make_golden.py <reference checkout>  (or set APPROXTORCH_REF)")
 sys.path.insert(0, REF)
 sys.modules["approxtorch.backend._C"] = types.ModuleType("approxtorch.backend._C")
 
