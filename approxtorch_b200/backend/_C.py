@@ -36,12 +36,14 @@ _vp, _i, _ll, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_s
 
 
 class GemmPlan(ctypes.Structure):
-    _fields_ = [("block_rows", _i), ("splits", _i), ("scratch_bytes", _sz), ("tail_row_tiles", _i), ("stream_k_units", _i)]
+    _fields_ = [("block_rows", _i), ("blocks", _i), ("units_per_block", _i), ("chunks_per_tile", _i), ("cut_tiles", _i),
+                ("scratch_bytes", _sz)]
 
 
 _SIGNATURES = {
     "atb_last_error": (ctypes.c_char_p, []),
     "atb_version": (_i, []),
+    "atb_device_status": (_i, [ctypes.POINTER(ctypes.c_int)]),
     "atb_lut_image_bytes": (_sz, []),
     "atb_lut_prepare": (_i, [_vp, _vp, _vp]),
     "atb_quantize_u8": (_i, [_vp, _vp, _ll, _i, _vp]),
@@ -64,9 +66,14 @@ _SIGNATURES = {
     "atb_lut_map_pad": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "atb_lre_bwd": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "atb_lre_conv_bwd": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 13 + [_i, _vp]),
-    "atb_custom_bwd_dx": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
-    "atb_custom_bwd_dw": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "atb_pair_table_bytes": (_sz, []),
+    "atb_pair_table_prepare": (_i, [_vp, _vp, _vp]),
+    "atb_pair_status": (_i, [ctypes.POINTER(ctypes.c_int)]),
+    "atb_custom_bwd_dx": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "atb_custom_bwd_dw": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "atb_custom_conv_bwd": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 13 + [_i, _i, _vp]),
     "atb_lut_dwconv_fwd": (_i, [_vp, _i, _vp, _vp, _vp] + [_i] * 12 + [_i, _vp]),
+    "atb_lut_dwconv_bwd": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 12 + [_i, _vp]),
     "atb_probe_shared_load": (_i, [_vp, _vp, _i, _i, _vp]),
 }
 

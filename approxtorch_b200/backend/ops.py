@@ -97,6 +97,49 @@ def lut_image(lut: Tensor) -> Tensor:
     return img
 
 
+_PAIR_BYTES = int(_lib.atb_pair_table_bytes())
+_pair_tables: dict = {}   # id(table) -> (weakref, (version, data_ptr), prepared)
+PAIR_MODE = 0             # 0: table held across a two-block cluster's shared memory; 1: staging reads from global memory
+
+
+def pair_table(table: Tensor) -> Tensor:
+    """Prepared copy of a 256x256 custom-gradient table (transposed, lane-permuted) that the custom-pair backward
+    kernels stage their columns from; built once per (tensor, version, storage) and cached like the LUT image."""
+    _require(table.is_cuda and table.dtype == torch.float32, "gradient LUT must be a float32 CUDA tensor")
+    _require(table.numel() == 65536, "gradient LUT must have 65536 elements")
+    key = id(table)
+    hit = _pair_tables.get(key)
+    same = hit is not None and hit[0]() is table and hit[2].device == table.device
+    if same and hit[1] == (table._version, table.data_ptr()):
+        return hit[2]
+    src = table.detach().contiguous()
+    out = hit[2] if same else torch.empty(_PAIR_BYTES // 4, dtype=torch.float32, device=table.device)
+    with _Guard(table):
+        _check(_lib.atb_pair_table_prepare(_ptr(src), _ptr(out), _stream(table)), "atb_pair_table_prepare")
+    _pair_tables[key] = (weakref.ref(table, lambda _r, k=key: _pair_tables.pop(k, None)),
+                         (table._version, table.data_ptr()), out)
+    return out
+
+
+def custom_conv_backward(go: Tensor, x8: Tensor, w_idx: Tensor, dx_lut: Tensor | None, dw_lut: Tensor | None, geom,
+                         pad_index: int, need_x: bool = True, need_w: bool = True):
+    """Image-space custom-pair backward: (grad wrt the quantised image [B,C,H,W], grad_w [O,K]); the gather of the
+    taps and the fold back to the image happen inside the kernels."""
+    (kh, kw), (sh, sw), (ph, pw), (dh, dw_) = geom
+    B, C, H, W = x8.shape
+    go = go.contiguous()
+    O = go.shape[1]
+    gx = torch.empty((B, C, H, W), dtype=torch.float32, device=go.device) if need_x else None
+    gw = torch.empty((O, C * kh * kw), dtype=torch.float32, device=go.device) if need_w else None
+    tx = pair_table(dx_lut) if need_x else None
+    tw = pair_table(dw_lut) if need_w else None
+    with _Guard(go):
+        _check(_lib.atb_custom_conv_bwd(_ptr(x8), _DTYPE_CODE[x8.dtype], _ptr(w_idx), _ptr(go), _ptr(tx), _ptr(tw),
+                                        _ptr(gx), _ptr(gw), B, C, H, W, O, kh, kw, sh, sw, ph, pw, dh, dw_, pad_index,
+                                        PAIR_MODE, _stream(go)), "atb_custom_conv_bwd")
+    return gx, gw
+
+
 # --------------------------------------------------------------------------- raw launch helpers
 def quantize_u8(x: Tensor, offset: int) -> Tensor:
     x = x.contiguous()
@@ -107,15 +150,15 @@ def quantize_u8(x: Tensor, offset: int) -> Tensor:
 
 
 def _normalise_cfg(cfg: int) -> int:
-    """cfg < 0: automatic.  Otherwise bits 0-15 = pixel rows per block (64, 128, 256 or 512; 0 = automatic) and
-    bits 16-23 = split-K factor; the reference's tile ids (0..18, 100..118) do not name a tiling of
-    this kernel and select the automatic plan."""
+    """cfg < 0: automatic.  Otherwise bits 0-15 = pixel rows per tile (a multiple of 32 up to 512; 0 = automatic) and
+    bits 16-23 = the cutting rule (0 automatic, 1 whole tiles only, S > 1 every tile in about S k-segments); the
+    reference's tile ids (0..18, 100..118) do not name a tiling of this kernel and select the automatic plan."""
     if cfg < 0:
         return -1
     rows = cfg & 0xFFFF
-    if rows not in (0, 64, 128, 256, 512):
+    if rows % 32 != 0 or rows > 512:
         return -1
-    return cfg
+    return cfg & 0xFFFFFF
 
 
 def lut_gemm_launch(x_idx: Tensor, w_idx: Tensor, image: Tensor, y: Tensor, N: int, K: int, L: int, O: int,
@@ -219,6 +262,22 @@ def lre_conv_backward(go: Tensor, x8: Tensor, w_idx: Tensor | None, dx: Tensor |
         _check(_lib.atb_lre_conv_bwd(_ptr(go), _ptr(x8), _DTYPE_CODE[x8.dtype], _ptr(w_idx), _ptr(dx), _ptr(dw),
                                      _ptr(go_scale), _ptr(w_zero), _ptr(gx), _ptr(gw), B, C, H, W, O, kh, kw, sh, sw, ph, pw,
                                      dh, dw_, pad_index, _stream(go)), "atb_lre_conv_bwd")
+    return gx, gw
+
+
+def dwconv_backward(go: Tensor, x8: Tensor, w_idx: Tensor, dx: Tensor, dw: Tensor, geom, pad_index: int,
+                    go_scale: Tensor | None = None, need_x: bool = True, need_w: bool = True):
+    """Depthwise STE / LRE backward on the saved 8-bit tensors: (grad wrt the quantised image [B,C,H,W],
+    grad_w [C, kh*kw])."""
+    (kh, kw), (sh, sw), (ph, pw), (dh, dw_) = geom
+    B, C, H, W = x8.shape
+    go = go.contiguous()
+    gx = torch.empty((B, C, H, W), dtype=torch.float32, device=go.device) if need_x else None
+    gw = torch.empty((C, kh * kw), dtype=torch.float32, device=go.device) if need_w else None
+    with _Guard(go):
+        _check(_lib.atb_lut_dwconv_bwd(_ptr(go), _ptr(x8), _DTYPE_CODE[x8.dtype], _ptr(w_idx), _ptr(dx), _ptr(dw),
+                                       _ptr(go_scale), _ptr(gx), _ptr(gw), B, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw_,
+                                       pad_index, _stream(go)), "atb_lut_dwconv_bwd")
     return gx, gw
 
 
@@ -443,12 +502,12 @@ def _custom_grad(X: Tensor, W: Tensor, dY: Tensor, table: Tensor, want: str, exp
     _require(dY.dtype == torch.float32 and table.dtype == torch.float32, "dY and the gradient LUT must be float32")
     _require(X.dim() == 3 and W.dim() == 2 and dY.dim() == 3, "expected X [N,K,L], W [O,K], dY [N,O,L]")
     Xc, Wc, dYc = X.contiguous(), W.contiguous(), dY.contiguous()
-    tab = table.contiguous().view(-1)
     N, K, L = Xc.shape
     O = Wc.shape[0]
     _require(Wc.shape[1] == K, "W.size(1) must equal X.size(1)")
     _require(tuple(dYc.shape) == (N, O, L), "dY shape must be [N, O, L]")
-    _require(tab.numel() == 65536, "gradient LUT must have 65536 elements")
+    _require(table.numel() == 65536, "gradient LUT must have 65536 elements")
+    tab = pair_table(table)
     if expect == torch.int8:     # signed values -> LUT indices
         Xc = (Xc.view(torch.uint8) ^ 0x80)
         Wc = (Wc.view(torch.uint8) ^ 0x80)
@@ -457,12 +516,12 @@ def _custom_grad(X: Tensor, W: Tensor, dY: Tensor, table: Tensor, want: str, exp
             out = torch.empty((N, K, L), dtype=torch.float32, device=X.device)
             if out.numel():
                 _check(_lib.atb_custom_bwd_dx(_ptr(Xc), _ptr(Wc), _ptr(dYc), _ptr(tab), _ptr(out), N, K, L, O,
-                                              _stream(X)), "atb_custom_bwd_dx")
+                                              PAIR_MODE, _stream(X)), "atb_custom_bwd_dx")
         else:
             out = torch.empty((O, K), dtype=torch.float32, device=X.device)
             if out.numel():
                 _check(_lib.atb_custom_bwd_dw(_ptr(Xc), _ptr(Wc), _ptr(dYc), _ptr(tab), _ptr(out), N, K, L, O,
-                                              _stream(X)), "atb_custom_bwd_dw")
+                                              PAIR_MODE, _stream(X)), "atb_custom_bwd_dw")
     return out
 
 

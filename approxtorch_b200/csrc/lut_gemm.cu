@@ -10,11 +10,12 @@
 //
 //  * The whole transposed 16-bit table (128 KB) is resident in shared memory, stored so that a 32-bit word
 //    of row w holds the entries {x = i, x = i + 128} and a lane's 16-byte load yields the four such pairs
-//    (i = lane + 32 j) that the lane will write out.
+//    (i = lane + 32 j) that the lane will write out.  It arrives as ONE bulk asynchronous copy
+//    (cp.async.bulk completing on an mbarrier) that overlaps the first operand gather, once per thread block.
 //  * For every k-step the block STAGES the 64 table columns its 64 output channels need as 16 QUAD rows:
 //    quad row p interleaves the columns of output channels p, p + 16, p + 32 and p + 48, its 8-byte entry x
 //    being {T[w_p][x], T[w_p+16][x]} {T[w_p+32][x], T[w_p+48][x]}.  Building a quad row is four 16-byte
-//    reads, 16 byte-permutes and eight conflict-free 8-byte writes per lane.
+//    reads, 16 byte-permutes and eight conflict-free 8-byte writes per lane; warp p builds quad row p.
 //  * The quad-row pitch is 2056 bytes (514 words, 2 mod 32).  An 8-byte shared load is served half a warp
 //    at a time, and the 16 lanes of a half - one quad row each, the same activation value x (that of the
 //    pixel row the half works on) - hit all 32 banks once: bank = (2 q + 2 x + {0, 1}) mod 32.  So a lookup
@@ -24,13 +25,25 @@
 //    lookups.
 //  * Entries are unsigned 16-bit (signed tables carry a +32768 bias removed in the epilogue).  A fetched
 //    word v = lo + 65536*hi is accumulated as S0 += v and S1 += hi; the low channel's sum is
-//    S0 - 65536*S1 (exact modulo 2^32; all sums stay below 2^31 because a block covers at most 32768 k-steps:
-//    longer reductions are split along K and their partial sums added in 64 bits).
+//    S0 - 65536*S1 (exact modulo 2^32 for reductions of up to 65536 steps).
 //
-// Integer-valued tables (the int16 / uint16 images) accumulate exactly in int32.  Tables that are
-// not 16-bit exact take the fp32 path: lookups go to the transposed fp32 table in global memory
-// (L1/L2 resident) and are summed in fp32 in ascending k, as the reference does
-// (approxtorch/backend/csrc/claude/bgemm_lut_kernels.cuh:278-281).
+// Scheduling is persistent stream-K.  The work is cut into units of (tile, 16-step k-chunk), tile-major with
+// the column tile fastest, and dealt out in equal contiguous runs, one run per thread block (one block per SM).
+// A block loads the table once and works through the tile segments of its run.  A segment that covers a
+// whole tile is finished and written straight to y.  A tile that is cut between blocks is finished by
+// whichever of its blocks arrives LAST: every other block parks its accumulators in its own scratch slot
+// (16-byte stores in the thread's own register order, so the finisher reads them back with the same
+// mapping), bumps the tile's arrival counter after a fence, and moves on; the block whose bump completes
+// the count adds the parked partial sums to its own registers and runs the normal epilogue.  Nobody ever
+// waits for anybody, so any grid size is safe, no reduction kernel is needed, and partial sums of whole
+// tiles never touch memory.
+//
+// Integer-valued tables (the int16 / uint16 images) accumulate exactly in int32, so the result does not
+// depend on how a tile was cut.  Tables that are not 16-bit exact take the fp32 path: lookups go to the
+// transposed fp32 table in global memory (L1/L2 resident) and are summed in fp32 in ascending k inside a
+// segment, and the segments of a cut tile are added in ascending k order, whoever finishes
+// (approxtorch/backend/csrc/claude/bgemm_lut_kernels.cuh:278-281 sums ascending k, :148-163 adds its split-K
+// partials in ascending order).
 //
 // The pixel operand is either a column matrix x[N,K,L] (L == 1: row-major A[M,K]) or the quantised
 // image itself with the im2col gather done in the tile loader, so the conv never materialises the
@@ -40,37 +53,41 @@
 
 namespace atb {
 
-constexpr int kStagedCols = 64;                          // output channels per thread block
-constexpr int kChunk = 16;                               // k-steps per operand tile
+constexpr int kStagedCols = 64;                          // output channels per tile
+constexpr int kChunk = 16;                               // k-steps per operand tile = one scheduling unit
 constexpr int kQuadRows = kStagedCols / 4;               // staged quad rows per k-step
 constexpr int kQuadPitch = 2056;                         // bytes per quad row (256 x 4 x uint16 + 8 B skew)
 constexpr int kStageBytes = kQuadRows * kQuadPitch;      // 32896
 constexpr int kMaxBlockRows = 512;
+constexpr int kThreads = 512;                            // 16 warps: warp p stages quad row p
 constexpr int kTableBytes = 65536 * 2;
-constexpr int kMaxBlockK = 32768;                        // k-steps one block may accumulate in its 32-bit sums
+constexpr int kMaxK = 65536;                             // longest reduction the modulo-2^32 sums keep exact
 constexpr int kSmemStage = kTableBytes;
 constexpr int kSmemX = kSmemStage + 2 * kStageBytes;
 constexpr int kSmemW = kSmemX + 2 * kChunk * kMaxBlockRows;
 constexpr int kSmemTotal = kSmemW + 2 * kChunk * kStagedCols;   // 215552 bytes
+// one parked partial tile: 16 uint4 per thread (its 64 accumulators) + one int per thread (operand row sum)
+constexpr int kSlotVecs = 16 * kThreads + kThreads / 4;  // in 16-byte vectors: 133120 bytes
+
+// device-side error word of the library (0 = none); see atb_device_status
+__device__ int g_device_status = 0;
+constexpr int kStatusTableCopyTimeout = 1;
 
 struct GemmArgs {
     const uint8_t* x;
     const uint8_t* w;
     const LutImage* img;
     float* y;
-    int* scratch;          // split-K partials [S][srows][O] followed by row sums [S][srows]
-    long long srow0, srows;   // pixel rows the split-K scratch covers: [srow0, srow0 + srows)
-    int tile0;             // first row tile of this launch (added to blockIdx.x)
-    // stream-K launches (sk_units > 0): the (tile, k-chunk) units, tile-major, are dealt out in equal contiguous
-    // runs of sk_units, one run per block; a block works through the one to three tile segments of its run
-    int sk_units, sk_col_tiles, block_rows;
-    long long sk_total;    // fits 31 bits
+    int* counters;         // arrival counter per tile, zero when the launch starts
+    uint4* slots;          // two parking slots per block (first / last segment of its run), kSlotVecs each
+    int units_per_cta;     // (tile, k-chunk) units per block
+    long long total_units;
+    int col_tiles, nchunks, block_rows;
     long long R;           // pixel rows
     int K, L, O;
     int wb_rows;           // pixel rows per weight matrix (0: one matrix for all rows)
     long long w_batch_stride;
     int tiles_per_batch;   // row tiles per weight batch (wb_rows != 0)
-    int chunks_per_split, splits;
     int image_mode;        // 1: x is the quantised image, gather taps in the loader
     int x_xor;             // 0x80 when the image holds int8 values (idx = v + 128), else 0
     int pad_index;
@@ -82,9 +99,19 @@ struct GemmArgs {
     const int* wsum;
 };
 
+// description of the segment a block is working on, kept in shared memory (the main loop has no register to spare)
+struct SegDesc {
+    int row_tile, c0, ch_beg, ch_end;
+    int tile;              // tile index (arrival counter)
+    int nsegs, seg;        // segments this tile is cut into (1: whole), and which of them this is
+    int first_cta;         // block that holds segment 0
+    int which;             // parking slot of this block used for this segment (0 / 1)
+    long long next_u;
+};
+
 // Epilogue arithmetic.  Integer tables: the sum, the zero-point terms and their combination are exact integers,
-// converted to fp32 once (round to nearest even), then scaled and shifted.  One block's sum fits 32 bits (a block
-// never covers more than 32768 k-steps); sums of split-K partials and the zero-point terms need 64.
+// converted to fp32 once (round to nearest even), then scaled and shifted.  A signed table's sum fits 32 bits, an
+// unsigned table's 33, the zero-point terms need 64.
 __device__ __forceinline__ float scale_shift(float v, int o, const GemmArgs& a)
 {
     if (a.alpha != nullptr) v = v * __ldg(a.alpha + o);
@@ -188,10 +215,9 @@ __device__ __forceinline__ void load_x_words(const uint8_t* xrow, uint32_t (&xw)
 
 // Lookups of one k-step.  Lane (h, q) = (lane / 16, lane % 16) works on 16 pixel rows (h * 16 + j of the
 // warp's 32) and the four output channels of quad row q: per row ONE 8-byte load, then per word S0 += word
-// and S1 += high half (a dot-product-accumulate that multiplies the halves by {0, 1}, or shift + add).
+// and S1 += high half (a dot-product-accumulate that multiplies the halves by {0, 1}).
 // An 8-byte shared load is served half a warp at a time, and the 16 lanes of a half (one quad row each, the
 // same activation value x) hit all 32 banks once: bank = (2 q + 2 x + {0, 1}) mod 32.
-template <bool DP2A>
 __device__ __forceinline__ void lookup_step(const uint8_t* stage, const uint8_t* xrow16, int q, unsigned (&acc)[16][4])
 {
     uint32_t xw[4];
@@ -202,13 +228,8 @@ __device__ __forceinline__ void lookup_step(const uint8_t* stage, const uint8_t*
         const uint2 v = base[__byte_perm(xw[j >> 2], 0, 0x4440 | (j & 3))];
         acc[j][0] += v.x;
         acc[j][2] += v.y;
-        if constexpr (DP2A) {
-            acc[j][1] = __dp2a_lo(v.x, 0x00000100u, acc[j][1]);
-            acc[j][3] = __dp2a_lo(v.y, 0x00000100u, acc[j][3]);
-        } else {
-            acc[j][1] += v.x >> 16;
-            acc[j][3] += v.y >> 16;
-        }
+        acc[j][1] = __dp2a_lo(v.x, 0x00000100u, acc[j][1]);
+        acc[j][3] = __dp2a_lo(v.y, 0x00000100u, acc[j][3]);
     }
 }
 
@@ -320,22 +341,23 @@ __device__ __forceinline__ void store_chunk(uint8_t* s_x, uint8_t* s_w, int buf,
 // QUAD = false (fp32 path): thread (warp, lane) holds pixel rows warp*32 + j (j = 0..31) of output channels
 // lane and lane + 32.  QUAD = true (integer path): thread (warp, h, q) holds pixel rows warp*32 + h*16 + j
 // (j = 0..15) of output channels q + 16 t (t = 0..3).  `xsum` is the operand sum of pixel row warp*32 + lane.
-// Split-K partials and the L == 1 layout are written directly (lanes span consecutive channels, which is
-// the fast axis there).  For L > 1 the fast axis of y[n, o, l] is the pixel, so each warp first turns its
-// 32 x 64 tile around in shared memory (the table / stage area is free by now) and then stores 128
-// contiguous bytes per channel.
-template <bool QUAD, class Total, class Bits>
+// The L == 1 layout is written directly (lanes span consecutive channels, the fast axis there).  For L > 1 the
+// fast axis of y[n, o, l] is the pixel, so each warp turns its 32 x 64 tile around in shared memory, 32 channels
+// at a time, and stores 128 contiguous bytes per channel.  The turning space is the stage / operand area, which
+// every warp has left by the time the main loop's last barrier is passed; the table image stays intact for the
+// block's next segment.  `active` is uniform over a warp (warps beyond the tile's rows hold nothing).
+template <bool QUAD, class Total>
 __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, long long r0, long long r_end, int c0,
-                                           int split, bool to_scratch,
-                                           int warp, int lane, int xsum, Total total, Bits bits)
+                                           int warp, int lane, int xsum, bool active, Total total)
 {
     constexpr int NJ = QUAD ? 16 : 32;               // row slots per thread
     constexpr int NT = QUAD ? 4 : 2;                 // column slots per thread
+    constexpr int TH = NT / 2;                       // column slots per 32-channel half
     const int row_base = QUAD ? (lane >> 4) * 16 : 0;        // first of this thread's rows within the warp's 32
     const int col_base = QUAD ? (lane & 15) : lane;          // first of this thread's columns within the 64
     constexpr int col_step = QUAD ? 16 : 32;
-    const bool want_xsum = a.zero_x != nullptr;
-    if (to_scratch || a.L == 1) {
+    if (!active) return;
+    if (a.L == 1) {
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
             const long long r = r0 + warp * 32 + row_base + j;
@@ -344,50 +366,154 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
                 const int o = c0 + col_base + col_step * t;
-                if (o >= a.O) continue;
-                if (to_scratch) a.scratch[(static_cast<long long>(split) * a.srows + (r - a.srow0)) * a.O + o] = bits(j, t);
-                else a.y[output_offset(r, o, a)] = finalize_output(total(j, t), xs, o, a);
+                if (o < a.O) a.y[r * a.O + o] = finalize_output(total(j, t), xs, o, a);
             }
-            if (to_scratch && want_xsum && c0 == 0 && col_base == 0)
-                a.scratch[static_cast<long long>(a.splits) * a.srows * a.O + static_cast<long long>(split) * a.srows + (r - a.srow0)] = xs;
         }
         return;
     }
-    __syncthreads();                                   // every warp has left the main loop
     constexpr int kPitch = 33;                         // words per channel row of the turned tile
-    float* tile = reinterpret_cast<float*>(smem) + warp * (kStagedCols * kPitch);
-#pragma unroll
-    for (int j = 0; j < NJ; ++j) {
-        const int xs = __shfl_sync(0xffffffffu, xsum, row_base + j);
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-            const int oc = col_base + col_step * t;
-            tile[oc * kPitch + row_base + j] = (c0 + oc < a.O) ? finalize_output(total(j, t), xs, c0 + oc, a) : 0.0f;
-        }
-    }
-    __syncwarp();
+    float* tile = reinterpret_cast<float*>(smem + kSmemStage) + warp * (32 * kPitch);
     const long long r = r0 + warp * 32 + lane;         // this lane's pixel row
-    if (r < r_end) {
-        const long long n = r / a.L;
-        const long long l = r - n * a.L;
-        float* dst = a.y + (n * a.O + c0) * a.L + l;
-        const int ncols = min(kStagedCols, a.O - c0);
-        for (int c = 0; c < ncols; ++c) dst[static_cast<long long>(c) * a.L] = tile[c * kPitch + lane];
+    const long long n = r / a.L;
+    const long long l = r - n * a.L;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+            const int xs = __shfl_sync(0xffffffffu, xsum, row_base + j);
+#pragma unroll
+            for (int tt = 0; tt < TH; ++tt) {
+                const int t = half * TH + tt;
+                const int oc = col_base + col_step * t;            // channel within the 64
+                tile[(oc - 32 * half) * kPitch + row_base + j] =
+                    (c0 + oc < a.O) ? finalize_output(total(j, t), xs, c0 + oc, a) : 0.0f;
+            }
+        }
+        __syncwarp();
+        if (r < r_end) {
+            float* dst = a.y + (n * a.O + c0 + 32 * half) * a.L + l;
+            const int ncols = min(32, a.O - c0 - 32 * half);
+            for (int c = 0; c < ncols; ++c) dst[static_cast<long long>(c) * a.L] = tile[c * kPitch + lane];
+        }
+        __syncwarp();
     }
 }
 
+// ---- cut tiles: park or finish --------------------------------------------------------------------------------
+// `vec(e)` gives access to the thread's e-th group of four accumulators (e = 0..15) as a uint4.  Returns true when
+// this block is the last of the tile's blocks to arrive: its registers then hold the complete sums.
+// FLOAT: the partial sums are fp32 and are added in ascending segment order (deterministic whoever finishes);
+// otherwise they are integers modulo 2^32 and the order does not matter.
+template <bool FLOAT, class Get, class Set>
+__device__ __forceinline__ bool park_or_finish(const GemmArgs& a, const volatile SegDesc* d, volatile int* s_flag,
+                                               bool active, int& xsum, Get get, Set set)
+{
+    const int tid = threadIdx.x;
+    const int nsegs = d->nsegs;
+    int* ctr = a.counters + d->tile;
+    if (tid == 0) {
+        int seen;
+        asm volatile("ld.acquire.gpu.s32 %0, [%1];" : "=r"(seen) : "l"(ctr) : "memory");
+        *s_flag = (seen == nsegs - 1);                 // everybody else is already in: nothing to park
+    }
+    __syncthreads();
+    bool last = *s_flag != 0;
+    if (!last) {
+        uint4* slot = a.slots + (2LL * blockIdx.x + d->which) * kSlotVecs;
+        if (active) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) slot[e * kThreads + tid] = get(e);
+            reinterpret_cast<int*>(slot + 16 * kThreads)[tid] = xsum;
+        }
+        __threadfence();                               // the parked sums are visible device-wide before the bump
+        __syncthreads();
+        if (tid == 0) *s_flag = (atomicAdd(ctr, 1) == nsegs - 1);
+        __syncthreads();
+        last = *s_flag != 0;
+        if (!last) return false;
+    }
+    __threadfence();
+    if (active) {
+        const long long tile_u0 = static_cast<long long>(d->tile) * a.nchunks;
+        const int first = d->first_cta, mine = d->seg;
+        if (a.zero_x != nullptr) {
+            for (int s = 0; s < nsegs; ++s) {
+                if (s == mine) continue;
+                const long long b = first + s;
+                const uint4* slot = a.slots + (2LL * b + (tile_u0 > b * a.units_per_cta ? 1 : 0)) * kSlotVecs;
+                xsum += __ldcg(reinterpret_cast<const int*>(slot + 16 * kThreads) + tid);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+            uint4 own = get(e);
+            uint4 sum = FLOAT ? make_uint4(0u, 0u, 0u, 0u) : own;
+            for (int s = 0; s < nsegs; ++s) {
+                uint4 p;
+                if (s == mine) {
+                    if (!FLOAT) continue;
+                    p = own;
+                } else {
+                    const long long b = first + s;
+                    const uint4* slot = a.slots + (2LL * b + (tile_u0 > b * a.units_per_cta ? 1 : 0)) * kSlotVecs;
+                    p = __ldcg(slot + e * kThreads + tid);
+                }
+                if (FLOAT) {
+                    sum.x = __float_as_uint(__uint_as_float(sum.x) + __uint_as_float(p.x));
+                    sum.y = __float_as_uint(__uint_as_float(sum.y) + __uint_as_float(p.y));
+                    sum.z = __float_as_uint(__uint_as_float(sum.z) + __uint_as_float(p.z));
+                    sum.w = __float_as_uint(__uint_as_float(sum.w) + __uint_as_float(p.w));
+                } else {
+                    sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+                }
+            }
+            set(e, sum);
+        }
+    }
+    return true;
+}
+
+// ---- table image into shared memory: one bulk asynchronous copy completing on an mbarrier ---------------------
+__device__ __forceinline__ void table_copy_start(uint8_t* smem, const LutImage* img, uint64_t* bar)
+{
+    const uint32_t bar_a = static_cast<uint32_t>(__cvta_generic_to_shared(bar));
+    const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const char* src = reinterpret_cast<const char*>(img->tabTP16);
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(kTableBytes) : "memory");
+    constexpr int kPiece = 32768;
+#pragma unroll
+    for (int i = 0; i < kTableBytes / kPiece; ++i)
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dst + i * kPiece), "l"(src + i * kPiece), "r"(kPiece), "r"(bar_a) : "memory");
+}
+
+// Bounded wait for the copy (phase 0 of the barrier).  false: gave up.
+__device__ __forceinline__ bool table_copy_wait(uint64_t* bar)
+{
+    const uint32_t bar_a = static_cast<uint32_t>(__cvta_generic_to_shared(bar));
+    for (int i = 0; i < (1 << 20); ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar_a) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 // 16-bit table classes: staged conflict-free lookups, exact integer accumulation.
-// Software pipeline per k-step: issue the table reads for the NEXT step's quad rows, do this step's
-// lookups (which hides the latency of those reads), permute and store the next step's quad rows into the
+// Software pipeline per k-step: issue the table reads for the NEXT step's quad row, do this step's
+// lookups (which hides the latency of those reads), permute and store the next step's quad row into the
 // other stage buffer, one barrier.
-template <int NW, bool DP2A>
-__device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
+// Returns false when the table copy did not arrive (the block gives up).
+template <bool RAGGED>
+__device__ __forceinline__ bool gemm_body_int(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
                                               const uint8_t* wcol, bool vec_x, bool vec_w, int pad, int bias,
-                                              long long r0, long long r_end, int c0, int kbeg, int kend,
-                                              int split, bool to_scratch, const volatile int* desc)
+                                              long long r_end, int kbeg, int kend,
+                                              const volatile SegDesc* desc, volatile int* s_flag, uint64_t* bar, bool wait_table)
 {
     constexpr int TM = 32;                       // pixel rows per warp
-    constexpr bool kPipelined = NW >= kQuadRows; // one quad row per warp: keep the next step's table words in registers
     uint8_t* s_tab = smem;
     uint8_t* s_stage = smem + kSmemStage;
     uint8_t* s_x = smem + kSmemX;
@@ -398,7 +524,8 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
     const int q = lane & 15;                     // this lane's quad row
     const int h = lane >> 4;                     // which 16 of the warp's 32 pixel rows
     const int nch = (kend - kbeg + kChunk - 1) / kChunk;
-    constexpr int bm = NW * TM;
+    const int bm = a.block_rows;
+    const bool active = !RAGGED || warp * TM < bm;
 
     unsigned acc[16][4];
 #pragma unroll
@@ -407,80 +534,114 @@ __device__ __forceinline__ void gemm_body_int(const GemmArgs& a, uint8_t* smem, 
     const bool want_xsum = a.zero_x != nullptr;
 
     uint32_t xr[4], wr[4];
-    if (nch > 0) {
-        load_chunk(a, rc, wcol, vec_x, vec_w, kbeg, kend, tid, pad, xr, wr, bm);
-        store_chunk(s_x, s_w, 0, tid, xr, wr, bm);
+    load_chunk(a, rc, wcol, vec_x, vec_w, kbeg, kend, tid, pad, xr, wr, bm);
+    store_chunk(s_x, s_w, 0, tid, xr, wr, bm);
+    if (wait_table) {
+        const bool ok = table_copy_wait(bar);
+        if (!__syncthreads_and(ok)) {
+            if (tid == 0) atomicExch(&g_device_status, kStatusTableCopyTimeout);
+            return false;
+        }
+    } else {
+        __syncthreads();      // first operand tile is in shared memory
     }
-    __syncthreads();          // table image and first operand tile are in shared memory
-    if (nch > 0) {
-        stage_quads(s_stage, s_tab, s_w, warp, lane, NW);
-        __syncthreads();
-    }
+    stage_quads(s_stage, s_tab, s_w, warp, lane, kThreads / 32);
+    __syncthreads();
 
     int step = 0;
-    for (int ci = 0; ci < nch; ++ci) {
-        const int k0 = kbeg + ci * kChunk;
-        const int kc = min(kChunk, kend - k0);
-        const int cur = ci & 1;
-        const bool has_next = ci + 1 < nch;
-        if (has_next) load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr, bm);
-        for (int kk = 0; kk < kc; ++kk, ++step) {
-            if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr, bm);
-            const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * TM;
-            const uint8_t* wstep = s_w + (cur * kChunk + kk) * kStagedCols;
-            const uint8_t* wnext = nullptr;
-            if (kk + 1 < kc) wnext = wstep + kStagedCols;
-            else if (has_next) wnext = s_w + ((cur ^ 1) * kChunk) * kStagedCols;
-            uint8_t* stage_next = s_stage + ((step + 1) & 1) * kStageBytes;
-            const uint8_t* stage_cur = s_stage + (step & 1) * kStageBytes;
-            if (want_xsum) xsum += static_cast<int>(xrow[lane]);
-
-            if constexpr (kPipelined) {
-                QuadWords v;
-                if (wnext != nullptr && warp < kQuadRows) fetch_quad(s_tab, wnext, warp, lane, v);
-                lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
-                if (wnext != nullptr && warp < kQuadRows) store_quad(stage_next, warp, lane, v);
-            } else {
-                if (wnext != nullptr) stage_quads(stage_next, s_tab, wnext, warp, lane, NW);
-                lookup_step<DP2A>(stage_cur, xrow + h * 16, q, acc);
+    if (RAGGED && !active) {
+        // Warps beyond the tile's rows hold no accumulators: they only build their quad row of every k-step (and pass
+        // the same barriers), in a loop of their own so that the working warps' loop carries no predicate.
+        for (int ci = 0; ci < nch; ++ci) {
+            const int k0 = kbeg + ci * kChunk;
+            const int kc = min(kChunk, kend - k0);
+            const int cur = ci & 1;
+            const bool has_next = ci + 1 < nch;
+            // the weight tile is loaded by the block's first 64 threads, which may belong to a warp without rows
+            if (has_next && tid < kStagedCols) load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr, bm);
+            for (int kk = 0; kk < kc; ++kk, ++step) {
+                if (has_next && kk == 4 && tid < kStagedCols) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr, bm);
+                const uint8_t* wstep = s_w + (cur * kChunk + kk) * kStagedCols;
+                const uint8_t* wnext = nullptr;
+                if (kk + 1 < kc) wnext = wstep + kStagedCols;
+                else if (has_next) wnext = s_w + ((cur ^ 1) * kChunk) * kStagedCols;
+                if (wnext != nullptr) {
+                    QuadWords v;
+                    fetch_quad(s_tab, wnext, warp, lane, v);
+                    store_quad(s_stage + ((step + 1) & 1) * kStageBytes, warp, lane, v);
+                }
+                __syncthreads();
             }
-            __syncthreads();
+        }
+    } else {
+        for (int ci = 0; ci < nch; ++ci) {
+            const int k0 = kbeg + ci * kChunk;
+            const int kc = min(kChunk, kend - k0);
+            const int cur = ci & 1;
+            const bool has_next = ci + 1 < nch;
+            if (has_next) load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr, bm);
+            for (int kk = 0; kk < kc; ++kk, ++step) {
+                if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr, bm);
+                const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * TM;
+                const uint8_t* wstep = s_w + (cur * kChunk + kk) * kStagedCols;
+                const uint8_t* wnext = nullptr;
+                if (kk + 1 < kc) wnext = wstep + kStagedCols;
+                else if (has_next) wnext = s_w + ((cur ^ 1) * kChunk) * kStagedCols;
+                uint8_t* stage_next = s_stage + ((step + 1) & 1) * kStageBytes;
+                const uint8_t* stage_cur = s_stage + (step & 1) * kStageBytes;
+                if (want_xsum) xsum += static_cast<int>(xrow[lane]);
+
+                QuadWords v;
+                if (wnext != nullptr) fetch_quad(s_tab, wnext, warp, lane, v);
+                lookup_step(stage_cur, xrow + h * 16, q, acc);
+                if (wnext != nullptr) store_quad(stage_next, warp, lane, v);
+                __syncthreads();
+            }
         }
     }
-    const long long remove = static_cast<long long>(bias) * (kend - kbeg);     // +32768 per looked-up entry of a signed table
+    long long ksteps = kend - kbeg;
+    if (desc->nsegs > 1) {
+        const bool finish = park_or_finish<false>(
+            a, desc, s_flag, active, xsum,
+            [&](int e) { return make_uint4(acc[e][0], acc[e][1], acc[e][2], acc[e][3]); },
+            [&](int e, const uint4& s) { acc[e][0] = s.x; acc[e][1] = s.y; acc[e][2] = s.z; acc[e][3] = s.w; });
+        if (!finish) return true;
+        ksteps = a.K;
+    }
+    const long long remove = static_cast<long long>(bias) * ksteps;     // +32768 per looked-up entry of a signed table
     // per word: acc[j][2u] holds sum(lo) + 65536 * sum(hi) modulo 2^32, acc[j][2u + 1] holds sum(hi)
     auto total = [&](int j, int t) -> long long {
         const int u = (t >> 1) * 2;
         const unsigned v = (t & 1) == 0 ? acc[j][u] - (acc[j][u + 1] << 16) : acc[j][u + 1];
         return static_cast<long long>(v) - remove;
     };
-    if (desc != nullptr) {
-        // stream-K: the tile coordinates were not kept in registers across the main loop; read them back
-        r0 = static_cast<long long>(desc[0]) * bm;
-        c0 = desc[1];
-        split = desc[4];
-    }
-    write_tile<true>(a, smem, r0, r_end, c0, split, to_scratch, warp, lane, xsum,
-                     [&](int j, int t) { return total(j, t); },
-                     [&](int j, int t) { return static_cast<int>(total(j, t)); });
+    // the tile coordinates were not kept in registers across the main loop; read them back
+    const int tpb = a.tiles_per_batch;
+    const int row_tile = desc->row_tile;
+    const long long r0 = a.wb_rows > 0 ? static_cast<long long>(row_tile / tpb) * a.wb_rows + static_cast<long long>(row_tile % tpb) * bm
+                                       : static_cast<long long>(row_tile) * bm;
+    write_tile<true>(a, smem, r0, r_end, desc->c0, warp, lane, xsum, active, total);
+    return true;
 }
 
 // Tables that are not 16-bit exact: lookups from the transposed fp32 table in global memory,
 // fp32 accumulation in ascending k.
-template <int TM>
-__device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
+template <bool RAGGED>
+__device__ __forceinline__ bool gemm_body_f32(const GemmArgs& a, uint8_t* smem, const RowCursor& rc,
                                               const uint8_t* wcol, bool vec_x, bool vec_w, int pad,
-                                              long long r0, long long r_end, int c0, int kbeg, int kend,
-                                              int split, bool to_scratch, const volatile int* desc)
+                                              long long r_end, int kbeg, int kend,
+                                              const volatile SegDesc* desc, volatile int* s_flag)
 {
+    constexpr int TM = 32;
     uint8_t* s_x = smem + kSmemX;
     uint8_t* s_w = smem + kSmemW;
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
     const int nch = (kend - kbeg + kChunk - 1) / kChunk;
+    const int bm = a.block_rows;
+    const bool active = !RAGGED || warp * TM < bm;
 
-    const int bm = (blockDim.x >> 5) * TM;
     float acc[TM][2];
 #pragma unroll
     for (int j = 0; j < TM; ++j) { acc[j][0] = 0.0f; acc[j][1] = 0.0f; }
@@ -488,10 +649,8 @@ __device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, 
     const bool want_xsum = a.zero_x != nullptr;
 
     uint32_t xr[4], wr[4];
-    if (nch > 0) {
-        load_chunk(a, rc, wcol, vec_x, vec_w, kbeg, kend, tid, pad, xr, wr, bm);
-        store_chunk(s_x, s_w, 0, tid, xr, wr, bm);
-    }
+    load_chunk(a, rc, wcol, vec_x, vec_w, kbeg, kend, tid, pad, xr, wr, bm);
+    store_chunk(s_x, s_w, 0, tid, xr, wr, bm);
     __syncthreads();
     for (int ci = 0; ci < nch; ++ci) {
         const int k0 = kbeg + ci * kChunk;
@@ -503,31 +662,42 @@ __device__ __forceinline__ void gemm_body_f32(const GemmArgs& a, uint8_t* smem, 
             if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr, bm);
             const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * TM;
             const uint8_t* wstep = s_w + (cur * kChunk + kk) * kStagedCols;
-            if (want_xsum && lane < TM) xsum += static_cast<int>(xrow[lane]);
-            lookup_step_f32<TM>(a.img->tabT32, wstep, xrow, lane, acc);
+            if (want_xsum) xsum += static_cast<int>(xrow[lane]);
+            if (active) lookup_step_f32<TM>(a.img->tabT32, wstep, xrow, lane, acc);
         }
         __syncthreads();
     }
-    if (desc != nullptr) {
-        r0 = static_cast<long long>(desc[0]) * bm;
-        c0 = desc[1];
-        split = desc[4];
+    if (desc->nsegs > 1) {
+        const bool finish = park_or_finish<true>(
+            a, desc, s_flag, active, xsum,
+            [&](int e) {
+                return make_uint4(__float_as_uint(acc[2 * e][0]), __float_as_uint(acc[2 * e][1]),
+                                  __float_as_uint(acc[2 * e + 1][0]), __float_as_uint(acc[2 * e + 1][1]));
+            },
+            [&](int e, const uint4& s) {
+                acc[2 * e][0] = __uint_as_float(s.x); acc[2 * e][1] = __uint_as_float(s.y);
+                acc[2 * e + 1][0] = __uint_as_float(s.z); acc[2 * e + 1][1] = __uint_as_float(s.w);
+            });
+        if (!finish) return true;
     }
-    write_tile<false>(a, smem, r0, r_end, c0, split, to_scratch, warp, lane, xsum,
-               [&](int j, int t) { return acc[j][t]; },
-               [&](int j, int t) { return __float_as_int(acc[j][t]); });
+    const int tpb = a.tiles_per_batch;
+    const int row_tile = desc->row_tile;
+    const long long r0 = a.wb_rows > 0 ? static_cast<long long>(row_tile / tpb) * a.wb_rows + static_cast<long long>(row_tile % tpb) * bm
+                                       : static_cast<long long>(row_tile) * bm;
+    write_tile<false>(a, smem, r0, r_end, desc->c0, warp, lane, xsum, active,
+                      [&](int j, int t) { return acc[j][t]; });
+    return true;
 }
 
 // One tile segment: rows of row tile `row_tile`, the 64 output channels from c0, k-chunks [ch_beg, ch_end).
-// The result goes to y (to_scratch false) or, as a partial sum, to slot `split` of the scratch.
-template <int NW, bool DP2A>
-__device__ __forceinline__ void run_segment(const GemmArgs& a, uint8_t* smem, int cls, int row_tile, int c0,
-                                            int ch_beg, int ch_end, int split, bool to_scratch,
-                                            const volatile int* desc = nullptr)
+template <bool RAGGED>
+__device__ __forceinline__ bool run_segment(const GemmArgs& a, uint8_t* smem, int cls, const volatile SegDesc* desc,
+                                            volatile int* s_flag, uint64_t* bar, bool wait_table)
 {
-    constexpr int TM = 32;
     const int tid = threadIdx.x;
-    constexpr int bm = NW * TM;
+    const int bm = a.block_rows;
+    const int row_tile = desc->row_tile;
+    const int c0 = desc->c0;
 
     long long r0, r_end;
     long long wbatch = 0;
@@ -540,8 +710,8 @@ __device__ __forceinline__ void run_segment(const GemmArgs& a, uint8_t* smem, in
         r0 = static_cast<long long>(row_tile) * bm;
         r_end = a.R;
     }
-    const int kbeg = ch_beg * kChunk;
-    const int kend = min(a.K, ch_end * kChunk);
+    const int kbeg = desc->ch_beg * kChunk;
+    const int kend = min(a.K, desc->ch_end * kChunk);
 
     // this thread's pixel row for the tile loads (clamped: rows past the end are never stored)
     const long long r = min(r0 + min(tid, bm - 1), r_end - 1);
@@ -570,102 +740,57 @@ __device__ __forceinline__ void run_segment(const GemmArgs& a, uint8_t* smem, in
     // pad_index < 0: taps outside the image take the activation zero point (an integer-valued device scalar)
     const int pad = a.pad_index >= 0 ? a.pad_index : min(255, max(0, static_cast<int>(llrintf(__ldg(a.zero_x)))));
     if (cls != LUT_F32)
-        gemm_body_int<NW, DP2A>(a, smem, rc, wcol, vec_x, vec_w, pad, cls == LUT_I16 ? 32768 : 0, r0, r_end, c0, kbeg, kend,
-                                split, to_scratch, desc);
-    else
-        gemm_body_f32<TM>(a, smem, rc, wcol, vec_x, vec_w, pad, r0, r_end, c0, kbeg, kend, split, to_scratch, desc);
+        return gemm_body_int<RAGGED>(a, smem, rc, wcol, vec_x, vec_w, pad, cls == LUT_I16 ? 32768 : 0, r_end, kbeg, kend,
+                                     desc, s_flag, bar, wait_table);
+    return gemm_body_f32<RAGGED>(a, smem, rc, wcol, vec_x, vec_w, pad, r_end, kbeg, kend, desc, s_flag);
 }
 
-// NW warps per block, 32 pixel rows per warp (one thread per row loads the operand tiles, 64 accumulators
-// per thread).  DP2A selects how the high half of a fetched word is accumulated.
-// SK: the block works through a run of tile segments (stream-K) instead of one tile or tile split.
-template <int NW, bool DP2A, bool SK>
-__global__ void __launch_bounds__(NW * 32, 1) lut_gemm_kernel(const GemmArgs a)
+// 16 warps per block, 32 pixel rows per warp (one thread per row loads the operand tiles, 64 accumulators per
+// thread).  RAGGED: tiles are shorter than 512 rows and the warps beyond them only help with the staging.
+template <bool RAGGED>
+__global__ void __launch_bounds__(kThreads, 1) lut_gemm_kernel(const GemmArgs a)
 {
     extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ __align__(8) uint64_t s_bar;
+    __shared__ SegDesc s_desc;
+    __shared__ int s_flag;
     const int tid = threadIdx.x;
     const int cls = lut_class_of(a.img);
-    if (cls != LUT_F32) {
-        // The image holds the table as the lookups want it (signed entries biased by +32768, so every lookup is an
-        // unsigned 16-bit load): asynchronous 16-byte copies straight into shared memory, all in flight at once.
-        const char* src = reinterpret_cast<const char*>(a.img->tabTP16);
-        const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-        for (int i = tid; i < kTableBytes / 16; i += blockDim.x)
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 16u * i), "l"(src + 16 * i) : "memory");
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 0;" ::: "memory");     // visible to the block after the next barrier
-    }
-    const int nchunks = (a.K + kChunk - 1) / kChunk;
-    if constexpr (!SK) {
-        const int ch_beg = blockIdx.z * a.chunks_per_split;
-        run_segment<NW, DP2A>(a, smem, cls, a.tile0 + static_cast<int>(blockIdx.x), blockIdx.y * kStagedCols,
-                              ch_beg, min(nchunks, ch_beg + a.chunks_per_split), blockIdx.z, a.splits > 1);
-    } else {
-        // This block's run of (tile, k-chunk) units; the table image stays in shared memory throughout.  The main
-        // loop has no register to spare, so the description of the current segment lives in shared memory: thread
-        // 0 writes it, everybody reads it for the prologue, and the epilogue and the loop read it back.
-        __shared__ int s_desc[8];        // row tile, first column, first chunk, end chunk, segment number, next unit
-        int u = static_cast<int>(blockIdx.x) * a.sk_units;
-        while (true) {
-            if (tid == 0) {
-                const int u_end = static_cast<int>(min(a.sk_total, static_cast<long long>(blockIdx.x + 1) * a.sk_units));
-                const int tile = u / nchunks;
-                const int ch_beg = u - tile * nchunks;
-                const int ch_end = min(nchunks, ch_beg + (u_end - u));
-                const int row_tile = tile / a.sk_col_tiles;
-                s_desc[0] = row_tile;
-                s_desc[1] = (tile - row_tile * a.sk_col_tiles) * kStagedCols;
-                s_desc[2] = ch_beg;
-                s_desc[3] = ch_end;
-                // segments of one tile are numbered by the blocks that hold them, in k order
-                s_desc[4] = u / a.sk_units - (tile * nchunks) / a.sk_units;
-                s_desc[5] = u + (ch_end - ch_beg);
-                s_desc[6] = u_end;
-            }
-            __syncthreads();
-            run_segment<NW, DP2A>(a, smem, cls, s_desc[0], s_desc[1], s_desc[2], s_desc[3], s_desc[4], true,
-                                  const_cast<const volatile int*>(s_desc));
-            const volatile int* d = s_desc;
-            u = d[5];
-            const int u_end = d[6];
-            __syncthreads();             // everybody has read the description before thread 0 rewrites it
-            if (u >= u_end) break;
+    long long u = static_cast<long long>(blockIdx.x) * a.units_per_cta;
+    const long long u_end = min(a.total_units, u + a.units_per_cta);
+    if (u >= u_end) return;
+    // The image holds the table as the lookups want it (signed entries biased by +32768, so every lookup is an
+    // unsigned 16-bit load); it is copied into shared memory untouched while the first operand tile is gathered.
+    if (cls != LUT_F32 && tid == 0) table_copy_start(smem, a.img, &s_bar);
+    bool wait_table = cls != LUT_F32;
+    while (true) {
+        if (tid == 0) {
+            const int n = a.nchunks;
+            const int U = a.units_per_cta;
+            const int tile = static_cast<int>(u / n);
+            const int ch_beg = static_cast<int>(u - static_cast<long long>(tile) * n);
+            const int ch_end = static_cast<int>(min(static_cast<long long>(n), ch_beg + (u_end - u)));
+            const int row_tile = tile / a.col_tiles;
+            const long long t0 = static_cast<long long>(tile) * n;
+            const int first = static_cast<int>(t0 / U);
+            const int last = static_cast<int>((t0 + n - 1) / U);
+            s_desc.row_tile = row_tile;
+            s_desc.c0 = (tile - row_tile * a.col_tiles) * kStagedCols;
+            s_desc.ch_beg = ch_beg;
+            s_desc.ch_end = ch_end;
+            s_desc.tile = tile;
+            s_desc.nsegs = last - first + 1;
+            s_desc.seg = static_cast<int>(blockIdx.x) - first;
+            s_desc.first_cta = first;
+            s_desc.which = t0 > static_cast<long long>(blockIdx.x) * U ? 1 : 0;
+            s_desc.next_u = u + (ch_end - ch_beg);
         }
-    }
-}
-
-// Split-K: y = finalize(sum_s partial[s]) in ascending split order, over the rows the scratch covers.
-__global__ void lut_gemm_reduce_kernel(const GemmArgs a)
-{
-    const long long total = a.srows * a.O;
-    const int cls = lut_class_of(a.img);
-    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    const int nchunks = (a.K + kChunk - 1) / kChunk;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const long long rs = i / a.O;
-        const int o = static_cast<int>(i - rs * a.O);
-        // number of partial sums of this element, and of its row's operand sum (held by the first column tile)
-        int ns = a.splits, nx = a.splits;
-        if (a.sk_units > 0) {
-            const long long t0 = (rs / a.block_rows) * a.sk_col_tiles;                   // first tile of the row tile
-            const long long t1 = t0 + o / kStagedCols;
-            nx = static_cast<int>((t0 * nchunks + nchunks - 1) / a.sk_units - (t0 * nchunks) / a.sk_units) + 1;
-            ns = static_cast<int>((t1 * nchunks + nchunks - 1) / a.sk_units - (t1 * nchunks) / a.sk_units) + 1;
-        }
-        long long xs = 0;
-        if (a.zero_x != nullptr)
-            for (int s = 0; s < nx; ++s) xs += a.scratch[a.splits * total + static_cast<long long>(s) * a.srows + rs];
-        float v;
-        if (cls == LUT_F32) {
-            float f = 0.0f;
-            for (int s = 0; s < ns; ++s) f += __int_as_float(a.scratch[static_cast<long long>(s) * total + i]);
-            v = finalize_output(f, xs, o, a);
-        } else {
-            long long t = 0;
-            for (int s = 0; s < ns; ++s) t += a.scratch[static_cast<long long>(s) * total + i];
-            v = finalize_output(t, xs, o, a);
-        }
-        a.y[output_offset(a.srow0 + rs, o, a)] = v;
+        __syncthreads();
+        if (!run_segment<RAGGED>(a, smem, cls, &s_desc, &s_flag, &s_bar, wait_table)) return;
+        wait_table = false;
+        u = const_cast<const volatile SegDesc*>(&s_desc)->next_u;
+        __syncthreads();             // everybody is done with the description and the turning space
+        if (u >= u_end) break;
     }
 }
 
@@ -681,133 +806,91 @@ __global__ void lut_gemm_empty_k_kernel(const GemmArgs a)
     }
 }
 
-// First pixel row of row tile t.
-static long long tile_first_row(long long t, int bm, int wb_rows, int tiles_per_batch)
+// ---- host side: the plan -----------------------------------------------------------------------------------------
+// Modelled duration of a block that works through `units` k-chunks cut into `segs` tile segments, in k-steps:
+// every segment pays a prologue (first operand gather, first staging) and an epilogue (finish and store, or
+// park), a block whose run ends inside a tile also pays for parking / collecting the partial sums.
+static double run_cost(long long units, long long segs, bool cut)
 {
-    if (wb_rows > 0) return (t / tiles_per_batch) * wb_rows + (t % tiles_per_batch) * static_cast<long long>(bm);
-    return t * bm;
+    constexpr double kPerSegment = 10.0, kExchange = 6.0, kPerBlock = 6.0;
+    return static_cast<double>(units) * kChunk + kPerSegment * static_cast<double>(segs) + (cut ? kExchange : 0.0) + kPerBlock;
 }
 
-// Modelled duration of `blocks` equal thread blocks of `ksteps` k-steps each, in k-step units: whole waves
-// of `sms` blocks, each paying a fixed prologue (table image into shared memory, first operand tile) and
-// epilogue worth about a dozen k-steps.
-static double wave_cost(long long blocks, int ksteps, int sms)
-{
-    constexpr double kFixed = 12.0;
-    return static_cast<double>((blocks + sms - 1) / sms) * (ksteps + kFixed);
-}
+struct FullPlan {
+    int block_rows, tiles_per_batch, col_tiles, nchunks, ctas, units_per_cta, cut;
+    long long row_tiles, tiles, total_units;
+    size_t counter_bytes, scratch_bytes;
+};
 
-static int make_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_plan* p,
-                     int* tiles_per_batch, long long* row_tiles)
+static int make_plan(long long R, int K, int O, int wb_rows, int cfg, FullPlan* p)
 {
     ATB_REQUIRE(p != nullptr, "plan is null");
     ATB_REQUIRE(R >= 0 && K >= 0 && O >= 0 && wb_rows >= 0, "negative dimension");
+    ATB_REQUIRE(K <= kMaxK, "reductions longer than 65536 steps are not supported");
+    ATB_REQUIRE(wb_rows == 0 || R % wb_rows == 0, "rows must be a multiple of wb_rows");
     const int sms = sm_count();
     const long long span = wb_rows > 0 ? wb_rows : R;
-    int bm = 0, splits = 0;
-    bool allow_tail = true;
-    if (cfg >= 0) { bm = cfg & 0xffff; splits = (cfg >> 16) & 0xff; allow_tail = ((cfg >> 25) & 1) == 0; }
+    int bm = 0, forced = 0;
+    if (cfg >= 0) { bm = cfg & 0xffff; forced = (cfg >> 16) & 0xff; }
     if (bm != 0) {
-        ATB_REQUIRE(bm == 64 || bm == 128 || bm == 256 || bm == 512, "cfg: block rows must be 64, 128, 256 or 512");
+        ATB_REQUIRE(bm % 32 == 0 && bm >= 32 && bm <= kMaxBlockRows, "cfg: block rows must be a multiple of 32 up to 512");
     } else {
-        // 32 staged pair rows divide evenly over 2, 4, 8 or 16 warps; a warp covers 32 pixel rows
-        bm = 64;
-        while (bm < kMaxBlockRows && bm < span) bm *= 2;
+        // Full 512-row tiles whenever there are that many rows.  A k-step costs a block about 0.43 us + 0.023 us per 32
+        // rows (measured: the staging of the 64 columns and the barrier dominate), so a shorter tile is barely
+        // cheaper than a full one and equalising tile heights gains nothing; only operands with fewer than 512 rows
+        // get a shorter tile (whose idle warps then only help with the staging).
+        bm = static_cast<int>(span >= kMaxBlockRows ? kMaxBlockRows : (span > 0 ? (span + 31) / 32 * 32 : 32));
     }
     const int tpb = wb_rows > 0 ? ceil_div(wb_rows, bm) : 0;
-    const long long rt = wb_rows > 0 ? (R / (wb_rows > 0 ? wb_rows : 1)) * tpb : (R + bm - 1) / bm;
+    const long long rt = wb_rows > 0 ? (R / wb_rows) * tpb : (R + bm - 1) / bm;
     const int ct = ceil_div(O > 0 ? O : 1, kStagedCols);
     const long long tiles = rt * ct;
     const int nchunks = K > 0 ? ceil_div(K, kChunk) : 1;
-    long long tail_rt = 0;
-    int sk_units = 0;
-    bool allow_sk = wb_rows == 0 && (cfg < 0 || (((cfg >> 26) & 1) == 0 && splits == 0));
-    // A block's 32-bit accumulators hold at most kMaxBlockK looked-up 16-bit entries, so longer reductions are
-    // always split along K (the reduction pass adds the partial sums in 64 bits).
-    const int min_splits = ceil_div(nchunks, kMaxBlockK / kChunk);
-    if (min_splits > 1) { allow_tail = false; allow_sk = false; }
-    if (splits == 0) {
-        splits = 1;
-        double classic = wave_cost(tiles, K, sms);      // modelled cost of the plan chosen so far
-        // (1) Grids of more than one wave whose last wave is ragged: the whole waves run unsplit, and only
-        // the trailing row tiles are split along K so that they fill one more (shorter) wave.  Their partial
-        // sums are the only ones that go through scratch.
-        if (allow_tail && tiles > sms && tiles % sms != 0 && nchunks > 1) {
-            const long long full = tiles / sms;
-            const long long main_rt = (full * sms) / ct;
-            const long long t_rt = rt - main_rt;
-            if (main_rt > 0 && t_rt > 0) {
-                const double base = wave_cost(tiles, K, sms);
-                double best = base;
-                int best_s = 1;
-                for (int s = 2; s <= 16 && s <= nchunks; ++s) {
-                    const int cps = ceil_div(nchunks, s);
-                    const int s_eff = ceil_div(nchunks, cps);
-                    const double cost = wave_cost(main_rt * ct, K, sms) + wave_cost(t_rt * ct * s_eff, cps * kChunk, sms) + 6.0;
-                    if (cost < best - 1e-9) { best = cost; best_s = s; }
+    const long long total = tiles * nchunks;
+    ATB_REQUIRE(tiles <= 2147483647LL / 2, "too many tiles");
+    long long units = nchunks;
+    if (total > 0) {
+        if (forced == 1) {                                   // whole tiles only
+            units = static_cast<long long>(nchunks) * ((tiles + sms - 1) / sms);
+        } else if (forced > 1) {                             // every tile cut into `forced` segments
+            units = ceil_div(nchunks, forced);
+        } else {
+            // Equal runs for p = 1 .. #SM blocks; the cheapest modelled run wins, fewer blocks on a tie.  Runs of
+            // whole tiles are among the candidates (p such that the run length is a multiple of the tile's chunks).
+            double best = 1e300;
+            for (long long pblocks = 1; pblocks <= sms && pblocks <= total; ++pblocks) {
+                for (int whole = 0; whole < 2; ++whole) {
+                    long long u = (total + pblocks - 1) / pblocks;
+                    if (whole) u = (u + nchunks - 1) / nchunks * nchunks;
+                    const bool cut = u % nchunks != 0;
+                    const long long segs = cut ? (u - 1) / nchunks + 2 : u / nchunks;
+                    const double c = run_cost(u, segs, cut);
+                    if (c < best - 1e-9) { best = c; units = u; }
                 }
-                if (best_s > 1 && best <= 0.95 * base) { splits = best_s; tail_rt = t_rt; classic = best; }
-            }
-        }
-        // (2) Otherwise split-K over all tiles, by the same model: S_eff equal parts of ceil(chunks / S) chunks
-        // each, whole waves of `sms` blocks, a fixed cost per block and a reduction pass.  Grids that already
-        // fill the GPU only split for a modelled gain of 10 % or more (the partial sums need S times the output
-        // in scratch).
-        if (tail_rt == 0 && tiles > 0 && tiles < 4LL * sms && nchunks > 1) {
-            const double base = wave_cost(tiles, K, sms);
-            double best = base;
-            int best_s = 1;
-            for (int s = 2; s <= 16 && s <= nchunks; ++s) {
-                const int cps = ceil_div(nchunks, s);
-                const int s_eff = ceil_div(nchunks, cps);
-                if (s_eff != s) continue;                       // same launch as a smaller s
-                // partial sums: S_eff * R * O int32 written and read back, ~2e-6 k-step times per element
-                const double traffic = 2.1e-6 * s_eff * static_cast<double>(R) * O;
-                const double cost = wave_cost(tiles * s_eff, cps * kChunk, sms) + 6.0 + traffic;
-                if (cost < best - 1e-9) { best = cost; best_s = s; }
-            }
-            if (best_s > 1 && (tiles < sms ? best <= 0.97 * base : best <= 0.9 * base)) { splits = best_s; classic = best; }
-        }
-        // (3) Stream-K for grids of a few waves at most: the (tile, k-chunk) units, tile-major, are dealt out in
-        // equal contiguous runs, one per SM, so every SM gets the same number of k-steps whatever the tile count.
-        // A block loads the table once and works through the one to three tile segments of its run; every
-        // segment's partial sums go through scratch and the reduction pass finishes all outputs.
-        if (allow_sk && tiles > 0 && (tiles < 4LL * sms || (cfg >= 0 && ((cfg >> 27) & 1))) && nchunks > 1) {
-            const long long total = tiles * nchunks;
-            const long long ctas = total < sms ? total : sms;
-            const long long units = (total + ctas - 1) / ctas;
-            const double segs = static_cast<double>((units + nchunks - 1) / nchunks + 1);
-            const double traffic = 2.1e-6 * 2.5 * static_cast<double>(R) * O;
-            const double cost = static_cast<double>(units) * kChunk + 8.0 * segs + 6.0 + traffic;
-            const bool forced = cfg >= 0 && ((cfg >> 27) & 1);
-            if ((forced || cost <= 0.95 * classic) && total < 2147483647LL / 2) {
-                sk_units = static_cast<int>(units);
-                tail_rt = 0;
-                splits = static_cast<int>((nchunks + units - 2) / units + 1);     // most segments any tile can have
             }
         }
     }
-    if (splits < min_splits) splits = min_splits;
-    if (sk_units == 0) {
-        if (splits > nchunks) splits = nchunks;
-        const int cps = ceil_div(nchunks, splits);
-        splits = ceil_div(nchunks, cps);
-        if (splits == 1) tail_rt = 0;
-    }
-    const long long srow0 = tail_rt > 0 ? tile_first_row(rt - tail_rt, bm, wb_rows, tpb) : 0;
+    if (units < 1) units = 1;
+    ATB_REQUIRE(units <= 2147483647LL, "run too long");
+    const long long ctas = total > 0 ? (total + units - 1) / units : 0;
+    ATB_REQUIRE(ctas <= 2147483647LL, "too many blocks");
     p->block_rows = bm;
-    p->splits = splits;
-    p->scratch_bytes = (splits > 1 || sk_units > 0)
-                           ? static_cast<size_t>(splits) * static_cast<size_t>(R - srow0) * (static_cast<size_t>(O) + 1) * 4u : 0u;
-    p->tail_row_tiles = static_cast<int>(tail_rt);
-    p->stream_k_units = sk_units;
-    if (tiles_per_batch) *tiles_per_batch = tpb;
-    if (row_tiles) *row_tiles = rt;
+    p->tiles_per_batch = tpb;
+    p->col_tiles = ct;
+    p->nchunks = nchunks;
+    p->row_tiles = rt;
+    p->tiles = tiles;
+    p->total_units = total;
+    p->units_per_cta = static_cast<int>(units);
+    p->ctas = static_cast<int>(ctas);
+    p->cut = (total > 0 && units % nchunks != 0) ? 1 : 0;
+    p->counter_bytes = p->cut ? (static_cast<size_t>(tiles) * 4u + 255u) / 256u * 256u : 0u;
+    p->scratch_bytes = p->cut ? p->counter_bytes + 2u * static_cast<size_t>(ctas) * kSlotVecs * 16u : 0u;
     return ATB_OK;
 }
 
-template <int NW, bool DP2A, bool SK>
-static int launch_one(dim3 grid, const GemmArgs& a, cudaStream_t stream)
+template <bool RAGGED>
+static int launch_one(int ctas, const GemmArgs& a, cudaStream_t stream)
 {
     // the opt-in shared-memory size is an attribute of the function on ONE device: set it once per device
     static bool attr_set[64] = {false};
@@ -818,98 +901,43 @@ static int launch_one(dim3 grid, const GemmArgs& a, cudaStream_t stream)
         return ATB_ERR_CUDA;
     }
     if (!attr_set[dev]) {
-        e = cudaFuncSetAttribute(lut_gemm_kernel<NW, DP2A, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+        e = cudaFuncSetAttribute(lut_gemm_kernel<RAGGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
         attr_set[dev] = true;
     }
-    lut_gemm_kernel<NW, DP2A, SK><<<grid, NW * 32, kSmemTotal, stream>>>(a);
-    return ATB_OK;
-}
-
-// stream-K launches always accumulate with the dot-product instruction
-static int launch_variant(int nwarps, bool dp2a, bool sk, dim3 grid, const GemmArgs& a, cudaStream_t stream)
-{
-    switch (nwarps) {
-        case 16: return sk ? launch_one<16, true, true>(grid, a, stream)
-                           : dp2a ? launch_one<16, true, false>(grid, a, stream) : launch_one<16, false, false>(grid, a, stream);
-        case 8: return sk ? launch_one<8, true, true>(grid, a, stream)
-                          : dp2a ? launch_one<8, true, false>(grid, a, stream) : launch_one<8, false, false>(grid, a, stream);
-        case 4: return sk ? launch_one<4, true, true>(grid, a, stream)
-                          : dp2a ? launch_one<4, true, false>(grid, a, stream) : launch_one<4, false, false>(grid, a, stream);
-        case 2: return sk ? launch_one<2, true, true>(grid, a, stream)
-                          : dp2a ? launch_one<2, true, false>(grid, a, stream) : launch_one<2, false, false>(grid, a, stream);
-        default: set_error("block rows must be 64, 128, 256 or 512"); return ATB_ERR_INVALID;
-    }
+    lut_gemm_kernel<RAGGED><<<ctas, kThreads, kSmemTotal, stream>>>(a);
+    return check_launch("lut_gemm_kernel");
 }
 
 static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes, cudaStream_t stream)
 {
     if (a.R == 0 || a.O == 0) return ATB_OK;
-    ATB_REQUIRE(a.wb_rows == 0 || a.R % a.wb_rows == 0, "rows must be a multiple of wb_rows");
     if (a.K == 0) {
         lut_gemm_empty_k_kernel<<<grid_for(a.R * a.O, 256, 4096), 256, 0, stream>>>(a);
         return check_launch("lut_gemm_empty_k_kernel");
     }
-    atb_gemm_plan plan;
-    int tpb = 0;
-    long long row_tiles = 0;
-    int rc = make_plan(a.R, a.K, a.O, a.wb_rows, cfg, &plan, &tpb, &row_tiles);
+    FullPlan plan;
+    int rc = make_plan(a.R, a.K, a.O, a.wb_rows, cfg, &plan);
     if (rc != ATB_OK) return rc;
-    ATB_REQUIRE(row_tiles <= 2147483647LL, "too many row tiles");
-    const int col_tiles = ceil_div(a.O, kStagedCols);
-    ATB_REQUIRE(col_tiles <= 65535, "too many output channels");
-    ATB_REQUIRE(plan.splits <= 65535, "K too large");
     if (plan.scratch_bytes > 0) {
         if (scratch == nullptr || scratch_bytes < plan.scratch_bytes) {
-            set_error("split-K needs %zu bytes of scratch, got %zu", plan.scratch_bytes, scratch_bytes);
+            set_error("this plan cuts tiles between blocks and needs %zu bytes of scratch, got %zu", plan.scratch_bytes, scratch_bytes);
             return ATB_ERR_SCRATCH;
         }
+        ATB_REQUIRE(aligned_to(scratch, 16), "scratch must be 16-byte aligned");
+        // arrival counters start at zero; the parking slots need no initialisation (written before they are read)
+        cudaError_t e = cudaMemsetAsync(scratch, 0, plan.counter_bytes, stream);
+        if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
+        a.counters = static_cast<int*>(scratch);
+        a.slots = reinterpret_cast<uint4*>(static_cast<char*>(scratch) + plan.counter_bytes);
     }
-    a.scratch = static_cast<int*>(scratch);
-    a.tiles_per_batch = tpb;
-    const bool shift_add = cfg >= 0 && ((cfg >> 24) & 1);      // cfg bit 24: accumulate high halves with shift + add
-    const int nchunks = ceil_div(a.K, kChunk);
     a.block_rows = plan.block_rows;
-    if (plan.stream_k_units > 0) {
-        a.tile0 = 0; a.splits = plan.splits; a.chunks_per_split = nchunks; a.srow0 = 0; a.srows = a.R;
-        a.sk_units = plan.stream_k_units; a.sk_col_tiles = col_tiles;
-        a.sk_total = row_tiles * col_tiles * nchunks;
-        dim3 grid(static_cast<unsigned>((a.sk_total + a.sk_units - 1) / a.sk_units), 1u, 1u);
-        rc = launch_variant(plan.block_rows / 32, true, true, grid, a, stream);
-        if (rc != ATB_OK) return rc;
-        rc = check_launch("lut_gemm_kernel");
-        if (rc != ATB_OK) return rc;
-        lut_gemm_reduce_kernel<<<grid_for(a.srows * a.O, 256, 8 * sm_count()), 256, 0, stream>>>(a);
-        return check_launch("lut_gemm_reduce_kernel");
-    }
-    const long long tail_rt = plan.tail_row_tiles;
-    const long long main_rt = row_tiles - tail_rt;
-    if (tail_rt > 0) {
-        // whole waves, unsplit
-        a.tile0 = 0; a.splits = 1; a.chunks_per_split = nchunks; a.srow0 = 0; a.srows = a.R;
-        dim3 grid(static_cast<unsigned>(main_rt), static_cast<unsigned>(col_tiles), 1u);
-        rc = launch_variant(plan.block_rows / 32, !shift_add, false, grid, a, stream);
-        if (rc != ATB_OK) return rc;
-        rc = check_launch("lut_gemm_kernel");
-        if (rc != ATB_OK) return rc;
-    }
-    // the split-K part: every tile, or only the trailing row tiles
-    a.tile0 = static_cast<int>(main_rt) * (tail_rt > 0 ? 1 : 0);
-    a.splits = plan.splits;
-    a.chunks_per_split = ceil_div(nchunks, plan.splits);
-    a.srow0 = tail_rt > 0 ? tile_first_row(main_rt, plan.block_rows, a.wb_rows, tpb) : 0;
-    a.srows = a.R - a.srow0;
-    dim3 grid(static_cast<unsigned>(tail_rt > 0 ? tail_rt : row_tiles), static_cast<unsigned>(col_tiles),
-              static_cast<unsigned>(plan.splits));
-    rc = launch_variant(plan.block_rows / 32, !shift_add, false, grid, a, stream);
-    if (rc != ATB_OK) return rc;
-    rc = check_launch("lut_gemm_kernel");
-    if (rc != ATB_OK) return rc;
-    if (plan.splits > 1) {
-        lut_gemm_reduce_kernel<<<grid_for(a.srows * a.O, 256, 8 * sm_count()), 256, 0, stream>>>(a);
-        rc = check_launch("lut_gemm_reduce_kernel");
-    }
-    return rc;
+    a.tiles_per_batch = plan.tiles_per_batch;
+    a.col_tiles = plan.col_tiles;
+    a.nchunks = plan.nchunks;
+    a.units_per_cta = plan.units_per_cta;
+    a.total_units = plan.total_units;
+    return plan.block_rows == kMaxBlockRows ? launch_one<false>(plan.ctas, a, stream) : launch_one<true>(plan.ctas, a, stream);
 }
 
 }  // namespace atb
@@ -918,7 +946,25 @@ using namespace atb;
 
 extern "C" int atb_lut_gemm_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_plan* plan)
 {
-    return make_plan(R, K, O, wb_rows, cfg, plan, nullptr, nullptr);
+    ATB_REQUIRE(plan != nullptr, "plan is null");
+    FullPlan p;
+    const int rc = make_plan(R, K, O, wb_rows, cfg, &p);
+    if (rc != ATB_OK) return rc;
+    plan->block_rows = p.block_rows;
+    plan->blocks = p.ctas;
+    plan->units_per_block = p.units_per_cta;
+    plan->chunks_per_tile = p.nchunks;
+    plan->cut_tiles = p.cut;
+    plan->scratch_bytes = p.scratch_bytes;
+    return ATB_OK;
+}
+
+extern "C" int atb_device_status(int* status /*host*/)
+{
+    ATB_REQUIRE(status != nullptr, "status is null");
+    cudaError_t e = cudaMemcpyFromSymbol(status, g_device_status, sizeof(int));
+    if (e != cudaSuccess) { set_error("cudaMemcpyFromSymbol: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
+    return ATB_OK;
 }
 
 static int check_epilogue(const float* zero_x, const float* zero_w, const int* wsum)
@@ -949,10 +995,10 @@ extern "C" int atb_lut_bgemm_fwd(const uint8_t* x, const uint8_t* w, const void*
 }
 
 // ---- entry point for callers that cannot allocate device memory ------------------------------------
-// Split-K partial sums normally go to a caller-supplied scratch buffer.  Some hosts of this library
-// cannot provide one: code running inside a CUDA-graph capture or under a memory pool that forbids new
-// allocations, and bindings from runtimes whose tensors cannot be created from inside an operator call.
-// For them the library carries its own fixed scratch area in device global memory.  It exists once per
+// Partial sums of tiles that are cut between blocks normally go to a caller-supplied scratch buffer.  Some hosts
+// of this library cannot provide one: code running inside a CUDA-graph capture or under a memory pool that
+// forbids new allocations, and bindings from runtimes whose tensors cannot be created from inside an operator
+// call.  For them the library carries its own fixed scratch area in device global memory.  It exists once per
 // GPU that loads the library and is held until the process exits.
 static __device__ __align__(256) unsigned char g_static_scratch[ATB_STATIC_SCRATCH_BYTES];
 
@@ -995,12 +1041,12 @@ extern "C" int atb_lut_bgemm_fwd_noalloc(const uint8_t* x, const uint8_t* w, con
                                          const float* zero_w, const int* wsum, int cfg, void* stream)
 {
     ATB_REQUIRE(N >= 0 && K >= 0 && L >= 0 && O >= 0, "negative dimension");
-    atb_gemm_plan plan;
-    int rc = make_plan(static_cast<long long>(N) * L, K, O, wb_rows, cfg, &plan, nullptr, nullptr);
+    FullPlan plan;
+    int rc = make_plan(static_cast<long long>(N) * L, K, O, wb_rows, cfg, &plan);
     if (rc != ATB_OK) return rc;
     if (plan.scratch_bytes > ATB_STATIC_SCRATCH_BYTES) {
-        set_error("this shape needs %zu bytes of split-K scratch but the built-in area holds %zu; "
-                  "use atb_lut_bgemm_fwd with a caller buffer, or force fewer splits through cfg",
+        set_error("this shape's plan needs %zu bytes of scratch but the built-in area holds %zu; "
+                  "use atb_lut_bgemm_fwd with a caller buffer, or choose a plan without cut tiles through cfg",
                   plan.scratch_bytes, static_cast<size_t>(ATB_STATIC_SCRATCH_BYTES));
         return ATB_ERR_SCRATCH;
     }
@@ -1027,7 +1073,7 @@ extern "C" int atb_lut_conv2d_fwd(const void* x, int dtype, const uint8_t* w, co
     ATB_REQUIRE(conv_out_shape(H, W, kh, kw, sh, sw, ph, pw, dh, dw, &OH, &OW), "conv geometry yields empty output");
     if (N == 0 || O == 0) return ATB_OK;
     const long long K = static_cast<long long>(C) * kh * kw;
-    ATB_REQUIRE(K <= 2147483647LL - kChunk, "C*kh*kw too large");
+    ATB_REQUIRE(K <= kMaxK, "C*kh*kw above 65536 is not supported");
     ATB_REQUIRE(y != nullptr && (K == 0 || (x != nullptr && w != nullptr)), "null operand");
     int rc = check_epilogue(zero_x, zero_w, wsum);
     if (rc != ATB_OK) return rc;

@@ -1,6 +1,6 @@
 """Per-kernel timings of the hot path with their roofline fractions (CUDA events, device-resident operands).
 
-    python -m approxtorch_b200.kernel_bench [--only stream,backward,custom,layers,lds] [--batch 16]
+    python -m approxtorch_b200.kernel_bench [--only stream,backward,custom,layers,lds,model] [--batch 16]
 
 ``bench.py`` calls :func:`run_all` and reports the result under ``extra``; each function here can also be run on
 its own (the commands the profiler summaries under ``profiles/`` were captured with).
@@ -63,9 +63,11 @@ def peaks(dev):
     return out
 
 
-def _time_ms(fn, iters=10, warmup=3, flush=None):
-    """Mean device time of fn() in ms.  ``flush``: a buffer larger than L2 rewritten before every timed call (outside
-    the event pair) for kernels whose operands would otherwise stay in L2."""
+def _time_ms(fn, iters=10, warmup=3, flush=None, reps=1):
+    """Mean device time of fn() in ms.  ``flush``: a buffer larger than L2 rewritten before every timed event pair
+    (outside it) for kernels whose operands would otherwise stay in L2.  ``reps`` > 1 enqueues that many calls
+    back to back inside one event pair, so that the host's launch latency hides behind the queued work (needed
+    for kernels of a few hundred microseconds launched from Python)."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -75,11 +77,12 @@ def _time_ms(fn, iters=10, warmup=3, flush=None):
             flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        fn()
+        for _ in range(reps):
+            fn()
         e1.record()
         e1.synchronize()
         total += e0.elapsed_time(e1)
-    return total / iters
+    return total / (iters * reps)
 
 
 # ----------------------------------------------------------------------------------------------- shared-memory peak
@@ -142,8 +145,10 @@ def backward_kernels(dev, batch=256, layers=None, mode="ste"):
         OH = (H + 2 * p - k) // s + 1
         go = torch.randn(batch, O, OH, OH, device=dev)
         gs = torch.rand(O, device=dev)
-        gx_ms = _time_ms(lambda: ops.lre_conv_backward(go, x8, widx, table, table, g4, 128, go_scale=gs, need_w=False), iters=5, warmup=2)
-        gw_ms = _time_ms(lambda: ops.lre_conv_backward(go, x8, widx, table, table, g4, 128, go_scale=gs, need_x=False), iters=5, warmup=2)
+        gx_ms = _time_ms(lambda: ops.lre_conv_backward(go, x8, widx, table, table, g4, 128, go_scale=gs, need_w=False),
+                         iters=3, warmup=2, reps=4)
+        gw_ms = _time_ms(lambda: ops.lre_conv_backward(go, x8, widx, table, table, g4, 128, go_scale=gs, need_x=False),
+                         iters=3, warmup=2, reps=4)
         flop = 2.0 * batch * OH * OH * C * k * k * O
         rows.append({"C": C, "H": H, "O": O, "k": k, "stride": s, "count": count, "grad_x_ms": gx_ms, "grad_w_ms": gw_ms,
                      "grad_x_tflops": flop / gx_ms / 1e9, "grad_w_tflops": flop / gw_ms / 1e9})
@@ -170,13 +175,13 @@ def custom_kernels(dev, pk=None):
     pairs = float(N) * K * L * O
     for name, fn in (("custom_dx", lambda: ops.bgemm_custom_grad_uint8_dx(x, w, dy, tab)),
                      ("custom_dw", lambda: ops.bgemm_custom_grad_uint8_dw(x, w, dy, tab))):
-        ms = _time_ms(fn, iters=5, warmup=2)
+        ms = _time_ms(fn, iters=3, warmup=2, reps=4)
         out[name] = {"ms": ms, "lookups_per_s": pairs / (ms * 1e-3), "frac_of_lookup_peak": pairs / (ms * 1e-3) / pk["lookup_peak"]}
     B, C, H = 64, 128, 56
     lut = torch.round(torch.randn(65536, device=dev) * 100)
     x8 = torch.randint(-127, 128, (B, C, H, H), dtype=torch.int8, device=dev)
     wd = torch.randint(-127, 128, (C, 9), device=dev).float()
-    ms = _time_ms(lambda: ops.dwconv_fake_int8_claude(x8, wd, lut, 3, 1, 1, 1), iters=5, warmup=2)
+    ms = _time_ms(lambda: ops.dwconv_fake_int8_claude(x8, wd, lut, 3, 1, 1, 1), iters=3, warmup=2, reps=4)
     taps = float(B) * C * H * H * 9
     out["dwconv_3x3"] = {"ms": ms, "lookups_per_s": taps / (ms * 1e-3), "shape": [B, C, H, H],
                          "hbm_gbs": B * C * H * H * 5 / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": B * C * H * H * 5 / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
@@ -187,14 +192,8 @@ def custom_kernels(dev, pk=None):
 def _plan_name(R, K, O):
     plan = _C.GemmPlan()
     _C.check(_C.lib.atb_lut_gemm_plan(R, K, O, 0, -1, ctypes.byref(plan)), "plan")
-    if plan.stream_k_units:
-        kind = f"stream-K({plan.stream_k_units})"
-    elif plan.tail_row_tiles:
-        kind = f"waves+tail x{plan.splits}"
-    elif plan.splits > 1:
-        kind = f"split-K x{plan.splits}"
-    else:
-        kind = "whole tiles"
+    per_tile = plan.units_per_block / plan.chunks_per_tile
+    kind = f"{plan.blocks} blocks x {per_tile:.2f} tiles" + (" (cut)" if plan.cut_tiles else "")
     return f"{plan.block_rows} rows, {kind}"
 
 
@@ -204,7 +203,6 @@ def lut_conv_layers(dev, batch, pk=None, layers=None):
     layers = layers or RESNET50_LAYERS
     lut = (torch.arange(256, device=dev).view(-1, 1) * torch.arange(256, device=dev).view(1, -1) // 64 * 64).float().reshape(-1)
     img = ops.lut_image(lut)
-    flush = torch.empty(160 << 20, dtype=torch.uint8, device=dev)
     rows, tot_ms, tot_macs = [], 0.0, 0.0
     for (C, H, O, k, s, p, count) in layers:
         x = torch.randint(0, 256, (batch, C, H, H), dtype=torch.uint8, device=dev)
@@ -216,7 +214,7 @@ def lut_conv_layers(dev, batch, pk=None, layers=None):
         OH = (H + 2 * p - k) // s + 1
         R, K = batch * OH * OH, C * k * k
         ms = _time_ms(lambda: ops.lut_conv2d_launch(x, w, img, g4, -1, alpha=al, zero_x=zx, zero_w=zw, wsum=ws),
-                      iters=5, warmup=2, flush=flush)
+                      iters=3, warmup=2, reps=8)
         macs = float(R) * K * O
         rows.append({"C": C, "H": H, "O": O, "k": k, "stride": s, "count": count, "R": R, "K": K, "plan": _plan_name(R, K, O),
                      "ms": ms, "lookups_per_s": macs / (ms * 1e-3), "frac_of_lookup_peak": macs / (ms * 1e-3) / pk["lookup_peak"]})
@@ -224,7 +222,43 @@ def lut_conv_layers(dev, batch, pk=None, layers=None):
         tot_macs += macs * count
     return {"batch": batch, "layers": rows, "total_ms": tot_ms, "total_lut_macs": tot_macs,
             "lookups_per_s": tot_macs / (tot_ms * 1e-3), "frac_of_lookup_peak": tot_macs / (tot_ms * 1e-3) / pk["lookup_peak"],
-            "l2": "a 160 MiB buffer is rewritten before every timed call"}
+            "timing": "8 launches back to back per event pair (host launch latency hidden); operands L2-warm, as in "
+                      "the model, where the previous layer has just written them"}
+
+
+# ----------------------------------------------------------------------------------------------- whole model
+def unsigned_truncated_table(dev, low_bits=6):
+    """Exact unsigned product i*j with its low bits cleared (the ResNet-50 inference configuration's table)."""
+    i = torch.arange(256, device=dev, dtype=torch.int64)
+    prod = i.view(-1, 1) * i.view(1, -1)
+    return ((prod >> low_bits) << low_bits).float().reshape(-1)
+
+
+def build_resnet50_uint8(dev, calib_images=8):
+    """torchvision ResNet-50, random init, every conv but the first swapped for the unsigned approximate layer,
+    ranges frozen after one calibration pass (momentum 1: ranges := that batch's min / max)."""
+    import torchvision
+    from . import convert_model, nn as atnn
+    torch.manual_seed(0)
+    model = torchvision.models.resnet50()
+    convert_model(model, unsigned_truncated_table(dev), qtype="uint8", update_scale=True, scale_momentum=1.0)
+    model = model.to(dev).train()
+    with torch.no_grad():
+        model(torch.randn(calib_images, 3, 224, 224, device=dev))
+    model.eval()
+    for m in model.modules():
+        if isinstance(m, atnn.Conv2d_uint8):
+            m.freeze_scale()
+    return model
+
+
+def resnet50_forward(dev, batch, iters=3):
+    """Eager eval forwards of the converted ResNet-50 (the command whose kernel list the profiler summary shows)."""
+    model = build_resnet50_uint8(dev)
+    x = torch.randn(batch, 3, 224, 224, device=dev)
+    with torch.no_grad():
+        ms = _time_ms(lambda: model(x), iters=iters, warmup=2)
+    return {"batch": batch, "ms": ms, "img_s": batch / (ms * 1e-3), "launch": "eager (no CUDA graph)"}
 
 
 def run_all(dev, which=("lds", "stream", "backward", "custom", "layers"), batches=(128, 16)):
@@ -240,6 +274,9 @@ def run_all(dev, which=("lds", "stream", "backward", "custom", "layers"), batche
                 out["backward_ste_resnet18_cifar_b256"] = backward_kernels(dev)
             elif name == "custom":
                 out["custom"] = custom_kernels(dev, pk)
+            elif name == "model":
+                for b in batches:
+                    out[f"resnet50_forward_b{b}"] = resnet50_forward(dev, b)
             elif name == "layers":
                 for b in batches:
                     out[f"resnet50_lut_conv_layers_b{b}"] = lut_conv_layers(dev, b, pk)

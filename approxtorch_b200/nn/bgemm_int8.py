@@ -10,7 +10,7 @@ What differs from the reference is only what runs underneath:
   is written (the reference calls im2col_u8 first, approxtorch/nn/bgemm_int8.py:246-249);
 * the STE / LRE conv backward is one fused fp32 kernel pair of this package (table map, gather and
   fold inside the operand fetch) instead of lut_map + lut_map_pad + two cuDNN calls
-  (approxtorch/nn/bgemm_int8.py:165-212, 259-295);
+  (approxtorch/nn/bgemm_int8.py:165-212, 259-295); the depthwise case has per-channel kernels of its own;
 * every backward keeps 1-byte payloads (int8 image / uint8 indices).
 """
 
@@ -118,27 +118,6 @@ def _conv_forward(x, w, lut, g4, groups):
     return y.flatten(2), xq8, wq
 
 
-def _depthwise_backward(go, xf, wf, g4, groups, pad_value_image=None):
-    """Depthwise (groups == C) data / weight gradients through ATen's convolution_backward with TF32
-    off, the route the reference takes for every grouped case (approxtorch/nn/bgemm_int8.py:189-210)."""
-    (_kh, _kw), (sh, sw), (ph, pw), (dh, dw) = g4
-    prev = torch.backends.cudnn.allow_tf32
-    torch.backends.cudnn.allow_tf32 = False
-    try:
-        if pad_value_image is None:
-            gx, gw, _ = torch.ops.aten.convolution_backward(
-                go, xf, wf, None, [sh, sw], [ph, pw], [dh, dw], False, [0, 0], groups, [True, True, False])
-        else:
-            gx, _, _ = torch.ops.aten.convolution_backward(
-                go, xf, wf, None, [sh, sw], [ph, pw], [dh, dw], False, [0, 0], groups, [True, False, False])
-            _, gw, _ = torch.ops.aten.convolution_backward(
-                go, pad_value_image, wf, None, [sh, sw], [0, 0], [dh, dw], False, [0, 0], groups,
-                [False, True, False])
-    finally:
-        torch.backends.cudnn.allow_tf32 = prev
-    return gx, gw
-
-
 class _conv2d_int8_ste(Function):
 
     @staticmethod
@@ -162,10 +141,10 @@ class _conv2d_int8_ste(Function):
             gx, gw = _ops.lre_conv_backward(go, xq8, wq, dec, dec, g4, _PAD_INDEX,
                                             need_x=ctx.needs_input_grad[0], need_w=ctx.needs_input_grad[1])
             return gx, gw, None, None
-        (kh, kw) = g4[0]
-        wf = (wq.float() - 128.0).view(O, C // groups, kh, kw)
-        gx, gw = _depthwise_backward(go, xq8.float(), wf, g4, groups)
-        return gx, gw.reshape(O, -1), None, None
+        dec = _ops.decode_table(xq8.device, 128)         # depthwise: per-channel gather / reduction kernels
+        gx, gw = _ops.dwconv_backward(go, xq8, wq, dec, dec, g4, _PAD_INDEX,
+                                      need_x=ctx.needs_input_grad[0], need_w=ctx.needs_input_grad[1])
+        return gx, gw, None, None
 
 
 def conv2d_int8_ste(x, w, lut, geom):
@@ -195,12 +174,9 @@ class _conv2d_int8_lre(Function):
             gx, gw = _ops.lre_conv_backward(go, xq8, wq, dx.contiguous(), dw.contiguous(), g4, _PAD_INDEX,
                                             need_x=ctx.needs_input_grad[0], need_w=ctx.needs_input_grad[1])
             return gx, gw, None, None, None, None
-        (kh, kw), _, (ph, pw), _ = g4
-        wp = _ops.lut_map(wq, dx).view(O, C // groups, kh, kw)
-        xp = _ops.lut_map_pad(xq8, dw, (ph, pw))
-        dummy = go.new_empty(1).expand(B, C, H, W)
-        gx, gw = _depthwise_backward(go, dummy, wp, g4, groups, pad_value_image=xp)
-        return gx, gw.reshape(O, -1), None, None, None, None
+        gx, gw = _ops.dwconv_backward(go, xq8, wq, dx.contiguous(), dw.contiguous(), g4, _PAD_INDEX,
+                                      need_x=ctx.needs_input_grad[0], need_w=ctx.needs_input_grad[1])
+        return gx, gw, None, None, None, None
 
 
 def conv2d_int8_lre(x, w, lut, dx, dw, geom):
@@ -208,35 +184,30 @@ def conv2d_int8_lre(x, w, lut, dx, dw, geom):
 
 
 class _conv2d_int8_custom(Function):
-    """Conv wrapper of the pair-wise custom-gradient kernels (groups == 1 only): the backward works on
-    the unfolded index matrix, then folds the column gradient back to the image."""
+    """Conv wrapper of the pair-wise custom-gradient kernels (groups == 1 only).  The forward is the im2col-free LUT
+    conv; the backward gathers the taps from the saved int8 image and folds the column gradient back into the image
+    inside the kernels, so neither the [N,K,L] index matrix nor an [N,K,L] gradient is ever written (the reference
+    unfolds with im2col_u8 and folds with F.fold, approxtorch/nn/bgemm_int8.py:87-118)."""
 
     @staticmethod
     def forward(ctx, x, w, lut, dx_lut, dw_lut, geom):
         g4, groups = _geom4(geom)
         if groups != 1:
             raise NotImplementedError("custom gradient currently supports only groups=1")
-        (kh, kw), stride, padding, dilation = g4
-        xq8 = x.detach().to(torch.int8)
-        cols = _ops.im2col_u8(xq8, (kh, kw), stride, padding, dilation)
-        y, xq, wq = _ops.bgemm_fake_int8_claude_save(cols, w.detach(), lut)
-        ctx.save_for_backward(xq, wq, dx_lut, dw_lut)
-        ctx.input_shape = tuple(x.shape)
+        y, xq8, wq = _conv_forward(x, w, lut, g4, 1)
+        ctx.save_for_backward(xq8, wq, dx_lut, dw_lut)
         ctx.geom = g4
         return y
 
     @staticmethod
     def backward(ctx, grad_output):
-        xq, wq, dx_lut, dw_lut = ctx.saved_tensors
-        (kh, kw), (sh, sw), (ph, pw), (dh, dw) = ctx.geom
-        _, _, height, width = ctx.input_shape
-        gx = gw = None
-        if ctx.needs_input_grad[0]:
-            gcols = _ops.bgemm_custom_grad_uint8_dx(xq, wq, grad_output, dx_lut)
-            gx = torch.nn.functional.fold(gcols, (height, width), (kh, kw), dilation=(dh, dw),
-                                          padding=(ph, pw), stride=(sh, sw))
-        if ctx.needs_input_grad[1]:
-            gw = _ops.bgemm_custom_grad_uint8_dw(xq, wq, grad_output, dw_lut)
+        xq8, wq, dx_lut, dw_lut = ctx.saved_tensors
+        B = xq8.shape[0]
+        O = wq.shape[0]
+        OH, OW = _out_hw(xq8.shape, ctx.geom)
+        go = grad_output.reshape(B, O, OH, OW).contiguous()
+        gx, gw = _ops.custom_conv_backward(go, xq8, wq, dx_lut, dw_lut, ctx.geom, _PAD_INDEX,
+                                           need_x=ctx.needs_input_grad[0], need_w=ctx.needs_input_grad[1])
         return gx, gw, None, None, None, None
 
 

@@ -1,6 +1,6 @@
 """Benchmark of the approximate-multiplier hot path: raw LUT-BGEMM throughput (LUT-MAC/s).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload bgemm|resnet50]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload bgemm|resnet18_qat]
 
 Workload (the raw LUT-BGEMM configuration): batch 16, A [16,4096,576], B [16,576,256] uniform 8-bit
 operands given as uint8 LUT indices (value + 128), table = exact signed product + seeded integer noise
@@ -135,6 +135,34 @@ def gpu_reference_leg(a, b, lut):
             "protocol": "5 warm-up + 30 timed iterations between CUDA events, device-resident operands"}
 
 
+def gpu_reference_custom_leg():
+    """The reference's own custom-pair backward kernels on the single-layer configuration's GEMM shape
+    (N=8, K=576, L=1024, O=64), timed in the reference worker process; None when they were not built."""
+    import tempfile
+    from oracle import build_ref_gpu
+    if build_ref_gpu.built_library() is None:
+        return None
+    rng = np.random.default_rng(3)
+    N, Kc, L, O = 8, 576, 1024, 64
+    x = rng.integers(0, 256, (N, Kc, L), dtype=np.uint8)
+    w = rng.integers(0, 256, (O, Kc), dtype=np.uint8)
+    dy = rng.standard_normal((N, O, L)).astype(np.float32)
+    tab = rng.standard_normal(65536).astype(np.float32)
+    out = {}
+    for name in ("bgemm_custom_grad_uint8_dx", "bgemm_custom_grad_uint8_dw"):
+        with tempfile.TemporaryDirectory() as d:
+            req, rep = os.path.join(d, "req.npz"), os.path.join(d, "rep.npz")
+            np.savez(req, op=np.array("time:" + name), arg0=x, arg1=w, arg2=dy, arg3=tab)
+            proc = subprocess.run([sys.executable, os.path.join(REPO, "oracle", "ref_gpu_worker.py"), req, rep],
+                                  capture_output=True, text=True, timeout=600)
+            if proc.returncode != 0 or not os.path.exists(rep):
+                out[name] = {"error": proc.stderr[-200:]}
+                continue
+            ms = float(np.load(rep, allow_pickle=False)["ms_per_call"])
+            out[name] = {"ms": ms, "lookups_per_s": N * Kc * L * O / (ms * 1e-3)}
+    return out
+
+
 # ----------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -187,24 +215,8 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------------------------- ResNet legs
 def build_resnet50_uint8(dev, calib_images=8):
-    """torchvision ResNet-50, random init, every conv but the first swapped for the unsigned approximate layer
-    (table = exact unsigned product with the low 6 bits cleared), scales frozen after one calibration pass."""
-    import torch
-    import torchvision
-    import approxtorch_b200 as at
-    from oracle import lut_oracle as lo
-    torch.manual_seed(0)
-    model = torchvision.models.resnet50()
-    lut = torch.from_numpy(lo.lut_unsigned_truncated(6).reshape(-1)).to(dev)
-    at.convert_model(model, lut, qtype="uint8", update_scale=True, scale_momentum=1.0)
-    model = model.to(dev).train()
-    with torch.no_grad():
-        model(torch.randn(calib_images, 3, 224, 224, device=dev))        # momentum 1: ranges := this batch's min/max
-    model.eval()
-    for m in model.modules():
-        if isinstance(m, at.nn.Conv2d_uint8):
-            m.freeze_scale()
-    return model
+    from approxtorch_b200.kernel_bench import build_resnet50_uint8 as build
+    return build(dev, calib_images)
 
 
 def resnet50_inference_leg(dev, world, rank, steps, batch_per_gpu=128):
@@ -292,6 +304,126 @@ def _resnet50_timed(model, dev, world, rank, steps, per_rank, tag):
             f"{tag}_lut_mac_s_per_gpu": res["resident"] * 3.969e9 / world}
 
 
+# ----------------------------------------------------------------------------------------------- DDP QAT workload
+def run_resnet18_qat(args):
+    """ImageNet-shaped ResNet-18 quantisation-aware training step under DistributedDataParallel: signed layers,
+    grad='lre', 4-bit weights, table = exact signed product + seeded noise in [-128, 128], slopes by least squares;
+    N(0,1) images [B,3,224,224] per GPU, random labels; EMA scales on, the activation abs-max MAX-all-reduced per
+    layer per step, gradients averaged by DDP.  One JSON line: step time, img/s, the share of the step spent in the
+    19 scale all-reduces and in the exposed part of the gradient all-reduce, and whether every rank holds the same
+    scale_x bits after the steps."""
+    import torch
+    import torch.distributed as dist
+    import torchvision
+    import approxtorch_b200 as at
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    batch = int(os.environ.get("ATB_BENCH_QAT_BATCH", "256"))
+    rng = np.random.default_rng(0)
+    idx = np.arange(-128, 128, dtype=np.int64)
+    lut_np = np.clip(idx[:, None] * idx[None, :] + rng.integers(-128, 129, (256, 256)), -32767, 32767).astype(np.float32)
+    dx_np, dw_np = at.grad_lut.lre(lut_np, "int8", None)
+    torch.manual_seed(0)                                   # same initial weights on every rank
+    model = torchvision.models.resnet18()
+    at.convert_model(model, torch.from_numpy(lut_np.reshape(-1)), qtype="int8", grad="lre", dx=torch.from_numpy(dx_np),
+                     dw=torch.from_numpy(dw_np), weight_bits=4, scale_momentum=0.1)
+    model = model.to(dev).train()
+    layers = [m for m in model.modules() if isinstance(m, at.nn.Conv2d_int8)]
+    net = model
+    if world > 1:
+        net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local], broadcast_buffers=False)
+    opt = torch.optim.SGD(model.parameters(), lr=0.01, momentum=0.9)
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)          # every rank its own images
+    x = torch.randn(batch, 3, 224, 224, generator=g).to(dev)
+    y = torch.randint(0, 1000, (batch,), generator=g).to(dev)
+
+    # CUDA events around every scale all-reduce (the layers call torch.distributed.all_reduce)
+    spans = []
+    real_all_reduce = dist.all_reduce
+
+    def timed_all_reduce(*a, **k):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = real_all_reduce(*a, **k)
+        e1.record()
+        spans.append((e0, e1))
+        return out
+
+    def step(sync_grads=True):
+        opt.zero_grad(set_to_none=True)
+        ctx = net.no_sync() if (world > 1 and not sync_grads) else _null_context()
+        with ctx:
+            loss = torch.nn.functional.cross_entropy(net(x), y)
+            loss.backward()
+        opt.step()
+        return loss
+
+    def timed(n, sync_grads=True):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            loss = step(sync_grads)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / n], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item(), float(loss)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    ms_step, loss = timed(args.steps)
+    ms_nosync = timed(args.steps, sync_grads=False)[0] if world > 1 else ms_step
+    scale_ms = 0.0
+    if world > 1:
+        dist.all_reduce = timed_all_reduce
+        try:
+            spans.clear()
+            for _ in range(args.steps):
+                step()
+            torch.cuda.synchronize()
+            scale_ms = sum(a.elapsed_time(b) for a, b in spans) / args.steps
+        finally:
+            dist.all_reduce = real_all_reduce
+    same = True
+    if world > 1:
+        mine = torch.stack([m.scale_x.detach().reshape(()) for m in layers]).view(torch.int32)
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine)
+        same = all(torch.equal(gathered[0], t) for t in gathered)
+    if rank == 0:
+        macs_per_img = 1.696e9
+        print(json.dumps({
+            "workload": "ResNet-18 (ImageNet stem) QAT step, int8 signed layers, grad='lre', weight_bits=4, DDP, EMA scales",
+            "n_gpus": world, "batch_per_gpu": batch, "steps": args.steps, "ms_per_step": ms_step,
+            "img_s": world * batch / (ms_step * 1e-3), "loss": loss,
+            "forward_lut_mac_s_per_gpu_if_forward_were_the_whole_step": batch * macs_per_img / (ms_step * 1e-3),
+            "scale_allreduces_per_step": len(layers), "scale_allreduce_ms_per_step": scale_ms,
+            "scale_allreduce_share": scale_ms / ms_step,
+            "ms_per_step_without_gradient_allreduce": ms_nosync,
+            "gradient_allreduce_exposed_share": max(0.0, ms_step - ms_nosync) / ms_step,
+            "scale_x_bit_identical_on_all_ranks": bool(same), "ddp_broadcast_buffers": False, "data": "synthetic"}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+class _null_context:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
 # ----------------------------------------------------------------------------------------------- GPU arm
 def run_gpu_arm(args):
     import torch
@@ -325,9 +457,8 @@ def run_gpu_arm(args):
         ops.lut_gemm_launch(a_dev, bq, image, y, BATCH * M, K, 1, NCOL, wb_rows=M, w_batch_stride=NCOL * K, cfg=args.cfg)
     plan = _C.GemmPlan()
     _C.check(_C.lib.atb_lut_gemm_plan(BATCH * M, K, NCOL, M, args.cfg, ctypes.byref(plan)), "plan")
-    # 16 weight transposes + the LUT GEMM call: one launch, or two (whole waves unsplit, then the trailing row
-    # tiles split along K) plus the reduction of the split part
-    launches_per_step = BATCH + (2 if plan.tail_row_tiles else 1) + (1 if plan.splits > 1 else 0)
+    # 16 weight transposes + the LUT GEMM call: one persistent launch (tiles cut between blocks are finished inside it)
+    launches_per_step = BATCH + 1
 
     def barrier():
         if world > 1:
@@ -531,9 +662,8 @@ def run_gpu_arm(args):
                                       "1 lookup per LUT-MAC",
                          "frac_at_sampled_clock": (achieved / (sms * 32 * run_mhz * 1e6)) if run_mhz else None,
                          "kernel_ms": gemm_s * 1e3,
-                         "kernel_ms_covers": "one atb_lut_bgemm_fwd call = all lookups of the step: lut_gemm_kernel over "
-                                             "the whole waves, lut_gemm_kernel over the K-split trailing row tiles, "
-                                             "and the reduction of those partial sums",
+                         "kernel_ms_covers": "one atb_lut_bgemm_fwd call = all lookups of the step: one persistent "
+                                             "lut_gemm_kernel launch (plus the memset of its arrival counters)",
                          # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM call (its three launches) on
                          # this workload, from the ncu capture summarised under profiles/
                          "traffic": 79.3e6,
@@ -555,6 +685,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="bgemm", choices=["bgemm", "resnet18_qat"],
+                    help="bgemm: the headline line (default); resnet18_qat: the DDP training-step measurement (its own JSON line)")
     ap.add_argument("--no-models", action="store_true", help="skip the ResNet-50 inference leg reported under extra")
     ap.add_argument("--cfg", type=int, default=-1, help="tiling override passed to the LUT-GEMM launch (-1: automatic)")
     ap.add_argument("--kernel-only", action="store_true",
@@ -563,6 +695,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "resnet18_qat":
+        run_resnet18_qat(args)
     else:
         run_gpu_arm(args)
 

@@ -37,6 +37,9 @@ extern "C" {
 
 const char* atb_last_error(void);
 int atb_version(void);
+/* Device-side error word of the current device (host pointer out; synchronises).  0 = none; 1 = a LUT GEMM block
+ * gave up waiting for its table copy and left its tiles unwritten.  (No counterpart in the reference.) */
+int atb_device_status(int* status /*host*/);
 
 /* ---- LUT image --------------------------------------------------------------------------
  * Device-side image of a 256x256 fp32 table: 16-bit and fp32 copies, natural and transposed,
@@ -67,22 +70,26 @@ int atb_im2col_u8(const void* x, int dtype, int N, int C, int H, int W, int kh, 
  * alpha/beta are optional (NULL = 1 / 0).  The zero-point terms are formed only when zero_x != NULL:
  * zx = *zero_x and zw = zero_w[o] are integer-valued fp32, wsum[o] = sum_k w_idx[o,k] (int32),
  * xsum = sum_k x_idx of the row; they are combined in integer arithmetic before the single
- * conversion to fp32.  Integer tables accumulate in int32 (exact), other tables in fp32 in ascending k.
+ * conversion to fp32.  Integer tables accumulate in int32 (exact; K up to 65536), other tables in fp32 in
+ * ascending k (ascending k inside a k-segment, segments added in ascending order when a tile is cut).
  *
- * cfg: -1 automatic.  Otherwise bits 0-15 pixel rows per block (64, 128, 256 or 512; 0 = automatic),
- * bits 16-23 split-K factor for every tile (0 = automatic), bit 24 accumulate with shift + add instead of the
- * dot-product instruction, bit 25 never split only the trailing row tiles, bit 26 never stream-K, bit 27 always stream-K (when the launch can be one).
+ * Scheduling: the work is cut into units of (64-channel tile, 16-step k-chunk) and dealt out in equal contiguous
+ * runs, one per thread block (persistent stream-K).  A tile that lies inside one run is written straight to y; a
+ * tile cut between runs is finished by the last of its blocks to arrive, the others having parked their partial
+ * sums in `scratch` (no reduction kernel, nobody waits).  Integer tables give the same bits under every plan.
  *
- * The plan says how the launch will be tiled and how much scratch (bytes) a split-K launch needs. */
+ * cfg: -1 automatic.  Otherwise bits 0-15 pixel rows per tile (a multiple of 32 up to 512; 0 = automatic) and
+ * bits 16-23 the cutting rule: 0 automatic, 1 never cut a tile (runs of whole tiles), S > 1 cut every tile into
+ * (about) S k-segments, one block each.  Other bits are ignored.
+ *
+ * The plan says how a launch will be laid out and how much scratch (bytes) it needs. */
 typedef struct {
-    int block_rows;      /* pixel rows per thread block: 64, 128, 256 or 512 */
-    int splits;          /* split-K factor; > 1 needs scratch */
-    size_t scratch_bytes;
-    int tail_row_tiles;  /* 0: `splits` applies to every tile; n > 0: only the last n row tiles are split (they
-                            complete a ragged last wave), the rest run unsplit in a launch of their own */
-    int stream_k_units;  /* 0: tiles are whole blocks; n > 0: stream-K, every block works through n consecutive
-                            (tile, 16-step k-chunk) units and `splits` is the largest number of partial sums of
-                            any tile */
+    int block_rows;       /* pixel rows per tile: a multiple of 32 up to 512 */
+    int blocks;           /* thread blocks launched (at most one per SM under the automatic plan) */
+    int units_per_block;  /* (tile, k-chunk) units in a block's run */
+    int chunks_per_tile;  /* ceil(K / 16) */
+    int cut_tiles;        /* 1 when runs end inside tiles: needs scratch_bytes of scratch (16-byte aligned) */
+    size_t scratch_bytes; /* arrival counters + two parking slots per block; 0 when no tile is cut */
 } atb_gemm_plan;
 
 int atb_lut_gemm_plan(long long R, int K, int O, int wb_rows, int cfg, atb_gemm_plan* plan /*host*/);
@@ -102,11 +109,11 @@ int atb_lut_bgemm_fwd(const uint8_t* x, const uint8_t* w, const void* lut_image,
  * reference: its operators allocate their split-K workspace from torch's allocator on every call.)
  * A host that is capturing a CUDA graph, runs under a closed memory pool, or binds this library from a
  * runtime that cannot create device buffers inside an operator call has no scratch buffer to hand in, so
- * this variant keeps the split-K partial sums in a fixed area of ATB_STATIC_SCRATCH_BYTES bytes of device
+ * this variant keeps the parked partial sums of cut tiles in a fixed area of ATB_STATIC_SCRATCH_BYTES bytes of device
  * global memory that is part of the library image: every GPU that loads the library holds it until the
  * process exits.  Arguments and results are those of atb_lut_bgemm_fwd; shapes whose plan needs more
  * scratch than the area holds are refused with ATB_ERR_SCRATCH (atb_lut_gemm_plan reports the need, and
- * cfg can force fewer splits).  The area's device address is looked up once per device, by the first of
+ * cfg can choose a plan that cuts no tile, or shorter tiles).  The area's device address is looked up once per device, by the first of
  * atb_static_scratch_bytes() or atb_lut_bgemm_fwd_noalloc() called while that device is current: call
  * atb_static_scratch_bytes() on every device you will use before starting any stream capture.  The
  * address is remembered per device ordinal for the life of the process (a cudaDeviceReset invalidates it;
@@ -189,16 +196,44 @@ int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t*
 /* ---- backward: custom pair tables (256x256) --------------------------------------------------------
  * grad_x[n,k,l] = sum_o dY[n,o,l] * dx_lut[x][w[o,k]]   (approxtorch/backend/csrc/cuda/bgemm_custom_grad_optimize.cu:30-116, 212-257)
  * grad_w[o,k]   = sum_{n,l} dY[n,o,l] * dw_lut[x][w]    (same file :136-205, 259-301)
- * x, w are uint8 LUT indices. */
-int atb_custom_bwd_dx(const uint8_t* x, const uint8_t* w, const float* dy, const float* dx_lut,
-                      float* grad_x, int N, int K, int L, int O, void* stream);
-int atb_custom_bwd_dw(const uint8_t* x, const uint8_t* w, const float* dy, const float* dw_lut,
-                      float* grad_w, int N, int K, int L, int O, void* stream);
+ * x, w are uint8 LUT indices.  The kernels read a PREPARED copy of the table (transposed and lane-permuted for
+ * their staging loads): build it once per table with atb_pair_table_prepare (atb_pair_table_bytes() bytes,
+ * 16-byte aligned) and pass it as dx_prepared / dw_prepared.
+ * mode: 0 = the table is held in the shared memory of a two-block cluster, half each, and read across the
+ * cluster (the default); 1 = staging reads come from global memory.  Same results either way.
+ * grad_w is accumulated with fp32 atomics over the pixel-row tiles (zeroed by the call). */
+size_t atb_pair_table_bytes(void);
+int atb_pair_table_prepare(const float* table /*[256][256], row = x*/, float* prepared, void* stream);
+int atb_custom_bwd_dx(const uint8_t* x, const uint8_t* w, const float* dy, const float* dx_prepared,
+                      float* grad_x, int N, int K, int L, int O, int mode, void* stream);
+int atb_custom_bwd_dw(const uint8_t* x, const uint8_t* w, const float* dy, const float* dw_prepared,
+                      float* grad_w, int N, int K, int L, int O, int mode, void* stream);
+/* Image form of both (conv2d_int8_custom's backward, approxtorch/nn/bgemm_int8.py:105-118, without its im2col_u8
+ * columns and F.fold): x is the quantised image [N,C,H,W] (int8 values or uint8 indices), taps outside it look
+ * up pad_index; grad_x [N,C,H,W] is the gradient with respect to the image (fp32 atomics), grad_w is
+ * [O, C*kh*kw].  Either output may be NULL. */
+int atb_custom_conv_bwd(const void* x, int dtype, const uint8_t* w, const float* dy,
+                        const float* dx_prepared, const float* dw_prepared, float* grad_x, float* grad_w,
+                        int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
+                        int dh, int dw_, int pad_index, int mode, void* stream);
+/* Device-side error word of the custom-gradient kernels (host pointer out; synchronises): 1 = a block gave up
+ * waiting for its half of the table and skipped its work.  (No counterpart in the reference.) */
+int atb_pair_status(int* status /*host*/);
 
-/* ---- depthwise LUT conv forward (groups == C, channel multiplier 1) ------------------------------
- * (dwconv_fake_int8_claude, approxtorch/backend/csrc/claude/dwconv_claude.cu:78-266). */
+/* ---- depthwise LUT conv (groups == C, channel multiplier 1) ----------------------------------------
+ * Forward: dwconv_fake_int8_claude, approxtorch/backend/csrc/claude/dwconv_claude.cu:78-266 (taps in ascending
+ * (i, j) order: bit-identical to a per-channel LUT GEMM). */
 int atb_lut_dwconv_fwd(const void* x, int dtype, const uint8_t* widx /*[C, kh*kw]*/, const void* lut_image,
                        float* y, int N, int C, int H, int W, int kh, int kw, int sh, int sw, int ph, int pw,
+                       int dh, int dw, int pad_index, void* stream);
+/* STE / LRE backward of the same layer on the saved 8-bit tensors:
+ *   grad_x[n,c,h,w] = gs[c] * sum_taps go * dx[widx[c,t]],   grad_w[c,t] = gs[c] * sum_{n,oh,ow} go * dw[x or pad_index]
+ * (dx / dw the 256-entry slope or decode tables; pad_index 256 selects a 257th entry of dw; gs optional).  Replaces
+ * the lut_map + lut_map_pad + two grouped cuDNN calls of approxtorch/nn/bgemm_int8.py:189-210.  Either output may
+ * be NULL; grad_w is added with fp32 atomics when a channel's pixels are split over several blocks. */
+int atb_lut_dwconv_bwd(const float* go, const void* x, int dtype, const uint8_t* widx,
+                       const float* dx, const float* dw_tab, const float* go_scale, float* grad_x, float* grad_w,
+                       int N, int C, int H, int W, int kh, int kw, int sh, int sw, int ph, int pw,
                        int dh, int dw, int pad_index, void* stream);
 
 /* ---- measurement aid (no counterpart in the reference) ---------------------------------------------

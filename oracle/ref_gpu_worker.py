@@ -5,7 +5,7 @@ schemas as this repository's binding, so it cannot share a process with ``approx
 this file with ``python oracle/ref_gpu_worker.py <request.npz> <reply.npz>``.
 
 Request keys: ``op`` (operator name) plus its tensor arguments ``arg0..argN`` (numpy arrays; int scalars as
-0-d arrays).  Special op ``bench_bgemm16``: times the raw LUT-BGEMM workload the reference way — 16 per-item
+0-d arrays).  ``time:<operator>`` times that operator instead of returning its outputs.  Special op ``bench_bgemm16``: times the raw LUT-BGEMM workload the reference way — 16 per-item
 ``gemm_fake_int8_forward_cuda_claude`` calls, 5 warm-up + 30 timed iterations between CUDA events
 (approxtorch/backend/csrc/claude/bench.py:140-152).
 """
@@ -54,6 +54,20 @@ def main(req_path: str, reply_path: str) -> int:
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / 30
         np.savez(reply_path, ms_per_step=np.array(ms))
+        return 0
+    if op.startswith("time:"):
+        # any operator timed the reference's way: 5 warm-up + 30 iterations between CUDA events
+        fn = getattr(torch.ops.approxtorch, op[5:])
+        for _ in range(5):
+            fn(*args)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(30):
+            fn(*args)
+        e1.record()
+        torch.cuda.synchronize()
+        np.savez(reply_path, ms_per_call=np.array(e0.elapsed_time(e1) / 30))
         return 0
     out = getattr(torch.ops.approxtorch, op)(*args)
     if isinstance(out, torch.Tensor):

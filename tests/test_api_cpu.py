@@ -196,19 +196,19 @@ def test_library_exports_every_declared_symbol():
     assert _C.lib.atb_version() >= 100
     plan = _C.GemmPlan()
     assert _C.lib.atb_lut_gemm_plan(65536, 576, 256, 4096, -1, plan) == 0
-    assert plan.block_rows % 32 == 0 and plan.splits >= 1
-    # 128 row tiles x 4 column tiles on 148 SMs: three whole waves unsplit, the last 17 row tiles split in two
-    assert (plan.block_rows, plan.splits, plan.tail_row_tiles) == (512, 2, 17)
-    assert plan.scratch_bytes == 2 * 17 * 512 * 257 * 4
-    assert _C.lib.atb_lut_gemm_plan(65536, 576, 256, 4096, 1 << 25, plan) == 0
-    assert (plan.splits, plan.tail_row_tiles, plan.scratch_bytes) == (1, 0, 0)
-    # 112 tiles on 148 SMs (a ResNet-50 stage-3 1x1 layer at batch 16): stream-K deals the 112 x 16 k-chunks out in
-    # runs of 13, and a tile then has at most 3 partial sums
+    # 16 x 8 row tiles x 4 column tiles of 36 k-chunks on 148 SMs: equal runs of 125 units, which end inside tiles
+    assert (plan.block_rows, plan.chunks_per_tile, plan.blocks, plan.units_per_block, plan.cut_tiles) == (512, 36, 148, 125, 1)
+    assert plan.scratch_bytes == 2048 + 2 * 148 * 133120
+    assert _C.lib.atb_lut_gemm_plan(65536, 576, 256, 4096, 1 << 16, plan) == 0          # whole tiles only
+    assert (plan.units_per_block, plan.blocks, plan.cut_tiles, plan.scratch_bytes) == (4 * 36, 128, 0, 0)
+    # 3136 rows (a ResNet-50 stage-3 layer at batch 16): seven row tiles of equal height instead of six full + one sliver
     assert _C.lib.atb_lut_gemm_plan(3136, 256, 1024, 0, -1, plan) == 0
-    assert (plan.stream_k_units, plan.splits, plan.tail_row_tiles) == (13, 3, 0)
-    assert plan.scratch_bytes == 3 * 3136 * 1025 * 4
-    assert _C.lib.atb_lut_gemm_plan(3136, 256, 1024, 0, 1 << 26, plan) == 0 and plan.stream_k_units == 0
-    assert _C.lib.atb_lut_gemm_plan(-1, 1, 1, 0, -1, plan) != 0 and "negative" in _C.last_error()
+    assert (plan.block_rows, plan.chunks_per_tile) == (448, 16) and plan.blocks <= 148
+    assert plan.blocks * plan.units_per_block >= 7 * 16 * 16 > (plan.blocks - 1) * plan.units_per_block
+    # every tile cut in three: more blocks than SMs is fine (nobody waits for anybody)
+    assert _C.lib.atb_lut_gemm_plan(3136, 256, 1024, 0, (3 << 16) | 64, plan) == 0
+    assert (plan.block_rows, plan.units_per_block, plan.blocks, plan.cut_tiles) == (64, 6, 49 * 16 * 16 // 6 + 1, 1)
+    assert _C.lib.atb_lut_gemm_plan(100, 70000, 8, 0, -1, plan) != 0 and "65536" in _C.last_error()
 
 
 def test_operators_are_registered_and_refuse_cpu_tensors():

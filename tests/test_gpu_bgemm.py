@@ -58,8 +58,8 @@ def test_shape_sweep_against_oracle(dev, shape):
     np.testing.assert_array_equal(wq.cpu().numpy(), lo.to_lut_index(w, 128))
 
 
-@pytest.mark.parametrize("cfg", [-1, 0, 7, 100, 64, 128, 256, 512, (3 << 16) | 128, (2 << 16) | 512, (5 << 16),
-                                 (1 << 24) | 256, (1 << 24) | (2 << 16) | 64])
+@pytest.mark.parametrize("cfg", [-1, 0, 7, 100, 32, 64, 96, 128, 256, 320, 512, (3 << 16) | 128, (2 << 16) | 512, (5 << 16),
+                                 (1 << 16) | 448, (13 << 16) | 160, (1 << 24) | 256, (1 << 24) | (2 << 16) | 64])
 def test_forced_tilings_and_split_k_are_bit_identical(dev, cfg):
     ops = _ops()
     rng = np.random.default_rng(5)
@@ -216,19 +216,20 @@ def _plan(ops, R, K, O, wb_rows=0, cfg=-1):
     return plan
 
 
-NO_TAIL = 1 << 25            # cfg bit 25: never split only the trailing row tiles
+NO_TAIL = 1 << 16            # cfg bits 16-23 = 1: runs of whole tiles only (no tile is cut between blocks)
 
 
 def test_ragged_last_wave_is_split_along_k_column_operand(dev):
-    """More than one wave of tiles with a ragged last wave: the trailing row tiles run split-K in a launch of
-    their own.  Same integers as the oracle and as the unsplit plan, with and without the zero-point terms."""
+    """More tiles than one wave of blocks, not a multiple of the SM count: the equal runs end inside tiles, which are
+    finished by the last block to arrive.  Same integers as the oracle and as the whole-tile plan, with and without
+    the zero-point terms."""
     ops = _ops()
     rng = np.random.default_rng(77)
     N, K, L, O = 1, 80, 20000, 256
     plan = _plan(ops, N * L, K, O)
-    assert plan.tail_row_tiles > 0 and plan.splits > 1
-    assert plan.scratch_bytes < plan.splits * N * L * (O + 1) * 4         # scratch covers the tail rows only
-    assert _plan(ops, N * L, K, O, cfg=NO_TAIL).tail_row_tiles == 0
+    assert plan.cut_tiles and plan.scratch_bytes > 0
+    whole = _plan(ops, N * L, K, O, cfg=NO_TAIL)
+    assert not whole.cut_tiles and whole.scratch_bytes == 0 and whole.units_per_block % whole.chunks_per_tile == 0
     x = rng.integers(0, 256, (N, K, L), dtype=np.uint8)
     w = rng.integers(0, 256, (O, K), dtype=np.uint8)
     lut = lo.lut_signed_noisy(64, seed=4)
@@ -261,7 +262,7 @@ def test_ragged_last_wave_per_batch_weights_and_image_operand(dev):
     img = ops.lut_image(_t(lut.reshape(-1), dev))
     # one weight matrix per batch item, batch rows not a multiple of the block rows
     Bt, M, K, Nc = 5, 4600, 96, 256
-    assert _plan(ops, Bt * M, K, Nc, wb_rows=M).tail_row_tiles > 0
+    assert _plan(ops, Bt * M, K, Nc, wb_rows=M).cut_tiles
     A = rng.integers(0, 256, (Bt, M, K), dtype=np.uint8)
     Bm = rng.integers(0, 256, (Bt, Nc, K), dtype=np.uint8)
     y = torch.empty((Bt, M, Nc), dtype=torch.float32, device=dev)
@@ -270,7 +271,7 @@ def test_ragged_last_wave_per_batch_weights_and_image_operand(dev):
         np.testing.assert_array_equal(y[b].cpu().numpy().astype(np.int64), lo.gemm_exact(A[b], Bm[b].T, lut))
     # image operand (im2col in the tile loader)
     B, C, H, W, O = 8, 8, 80, 80, 128
-    assert _plan(ops, B * H * W, C * 9, O).tail_row_tiles > 0
+    assert _plan(ops, B * H * W, C * 9, O).cut_tiles
     x8 = rng.integers(-127, 128, (B, C, H, W)).astype(np.int8)
     widx = rng.integers(0, 256, (O, C * 9), dtype=np.uint8)
     cols = lo.im2col_index(lo.index_of(x8, True), 3, 3, 1, 1, 1, 1, 1, 1, 128)
@@ -281,7 +282,7 @@ def test_ragged_last_wave_per_batch_weights_and_image_operand(dev):
     assert torch.equal(yc, ops.lut_conv2d_launch(_t(x8, dev), _t(widx, dev), img, g4, 128, cfg=NO_TAIL))
 
 
-STREAM_K = 1 << 27           # cfg bit 27: stream-K whenever the launch can be one
+STREAM_K = 3 << 16           # cfg bits 16-23 = 3: every tile is cut into three k-segments, one block each
 
 
 @pytest.mark.parametrize("shape", [(1, 256, 3136, 200), (3, 100, 500, 70), (2, 37, 1300, 64), (1, 600, 70, 130),
@@ -296,7 +297,7 @@ def test_stream_k_is_bit_identical(dev, shape):
     w = rng.integers(0, 256, (O, K), dtype=np.uint8)
     lut = lo.lut_signed_noisy(64, seed=6)
     img = ops.lut_image(_t(lut.reshape(-1), dev))
-    assert _plan(ops, N * L, K, O, cfg=STREAM_K).stream_k_units > 0
+    assert _plan(ops, N * L, K, O, cfg=STREAM_K).cut_tiles == (1 if K > 16 else 0)
     ref = c_oracle.bgemm_u8(x, w, lut)
     y = torch.empty((N, O, L), dtype=torch.float32, device=dev)
     ops.lut_gemm_launch(_t(x, dev), _t(w, dev), img, y, N, K, L, O, cfg=STREAM_K)
@@ -309,7 +310,7 @@ def test_stream_k_is_bit_identical(dev, shape):
     wsum = _t(w.astype(np.int64).sum(axis=1).astype(np.int32), dev)
     ya = torch.empty((N * L, O), dtype=torch.float32, device=dev)
     yb = torch.empty_like(ya)
-    for out, cfg in ((ya, STREAM_K), (yb, 1 << 26)):
+    for out, cfg in ((ya, STREAM_K), (yb, NO_TAIL)):
         ops.lut_gemm_launch(_t(xr, dev), _t(w, dev), img, out, N * L, K, 1, O, alpha=alpha, zero_x=zx, zero_w=zw,
                             wsum=wsum, cfg=cfg)
     assert torch.equal(ya, yb)
@@ -325,7 +326,7 @@ def test_stream_k_image_operand_and_fp32_table(dev):
     for lut in (lo.lut_affine_asymmetric(), lo.lut_signed_noisy(64, seed=1) + 0.25):     # integer table, fp32-class table
         img = ops.lut_image(_t(np.asarray(lut, dtype=np.float32).reshape(-1), dev))
         ya = ops.lut_conv2d_launch(_t(x8, dev), _t(widx, dev), img, g4, 128, cfg=STREAM_K)
-        yb = ops.lut_conv2d_launch(_t(x8, dev), _t(widx, dev), img, g4, 128, cfg=(1 << 26) | (1 << 25))
+        yb = ops.lut_conv2d_launch(_t(x8, dev), _t(widx, dev), img, g4, 128, cfg=NO_TAIL)
         if float(np.asarray(lut).reshape(-1)[0]) == int(np.asarray(lut).reshape(-1)[0]):
             assert torch.equal(ya, yb)
         else:                                   # fp32 sums: the partial sums are added in another order

@@ -377,14 +377,46 @@ def test_depthwise_layer(dev):
     ref = np.stack([lo.bgemm_exact(cols[:, c * 9:(c + 1) * 9], lo.to_lut_index(w[c:c + 1], 128), lut)[:, 0]
                     for c in range(C)], axis=1)
     np.testing.assert_array_equal(y.flatten(2).cpu().numpy().astype(np.int64), ref)
+    # the layer: forward and STE / LRE gradients against the per-channel fp64 chain (stride 2, and a 5x5 window with
+    # dilation), including the padded taps' slope dw[128] and clipped activations
     for mode in ("ste", "lre"):
-        dx, dw = lo.lre_slopes(lut)
-        layer = at.nn.Conv2d_int8(C, C, 3, _t(lut.reshape(-1), dev), grad=mode, dx=_t(dx, dev), dw=_t(dw, dev),
-                                  padding=1, groups=C, update_scale=False).to(dev)
-        xt = torch.randn(B, C, H, W, device=dev, requires_grad=True)
-        out = layer(xt)
-        out.sum().backward()
-        assert out.shape == (B, C, H, W) and xt.grad is not None and layer.weight.grad.shape == layer.weight.shape
+        for (k, s, p, d) in ((3, 2, 1, 1), (3, 1, 1, 1), (5, 1, 4, 2)):
+            dx, dw = lo.lre_slopes(lut)
+            dw = dw.copy(); dw[128] = 2.5
+            torch.manual_seed(5)
+            layer = at.nn.Conv2d_int8(C, C, k, _t(lut.reshape(-1), dev), grad=mode, dx=_t(dx, dev), dw=_t(dw, dev), bias=True,
+                                      stride=s, padding=p, dilation=d, groups=C, update_scale=False).to(dev)
+            with torch.no_grad():
+                layer.scale_x.fill_(0.02)
+            xin = (rng.standard_normal((B, C, H, W)) * 1.5).astype(np.float32)
+            xt = _t(xin, dev).requires_grad_(True)
+            out = layer(xt)
+            go = rng.standard_normal(tuple(out.shape)).astype(np.float32)
+            out.backward(_t(go, dev))
+            sw = layer.scale_w.cpu().numpy()
+            wnp = layer.weight.detach().cpu().numpy()                       # [C, 1, k, k]
+            xq, xm = lo.fakequant_sym(xin, np.float32(0.02), -127, 127)
+            wq, wm = lo.fakequant_sym(wnp, sw.reshape(-1, 1, 1, 1), -127, 127)
+            sc = (np.float32(0.02) * sw).astype(np.float64)
+            OH, OW = out.shape[2], out.shape[3]
+            ry = np.zeros((B, C, OH * OW)); rgx = np.zeros((B, C, H, W)); rgw = np.zeros((C, k * k))
+            for c in range(C):
+                colsc = lo.im2col_index(lo.to_lut_index(xq[:, c:c + 1], 128), k, k, s, s, p, p, d, d, 128)
+                wc = lo.to_lut_index(wq[c].reshape(1, -1), 128)
+                ry[:, c] = lo.bgemm_exact(colsc, wc, lut)[:, 0] * sc[c] + layer.bias.detach().cpu().numpy()[c]
+                gch = go.reshape(B, C, -1)[:, c:c + 1].astype(np.float64) * sc[c]
+                if mode == "ste":
+                    gcols, gwc = lo.ste_backward(gch, colsc, wc)
+                else:
+                    gcols, gwc = lo.lre_backward(gch, colsc, wc, dx, dw)
+                rgx[:, c] = lo.fold(gcols, 1, H, W, k, k, s, s, p, p, d, d)[:, 0]
+                rgw[c] = gwc[0]
+            rgx = rgx * xm / 0.02
+            rgw = rgw.reshape(wnp.shape) * wm / np.maximum(sw.astype(np.float64), 1e-12).reshape(-1, 1, 1, 1)
+            _close(out.flatten(2), ry)
+            _close(xt.grad, rgx)
+            _close(layer.weight.grad, rgw)
+            _close(layer.bias.grad, go.astype(np.float64).sum(axis=(0, 2, 3)))
 
 
 def test_linear_layer_on_the_lut_gemm(dev):
