@@ -201,10 +201,12 @@ def test_library_exports_every_declared_symbol():
     assert plan.scratch_bytes == 2048 + 2 * 148 * 133120
     assert _C.lib.atb_lut_gemm_plan(65536, 576, 256, 4096, 1 << 16, plan) == 0          # whole tiles only
     assert (plan.units_per_block, plan.blocks, plan.cut_tiles, plan.scratch_bytes) == (4 * 36, 128, 0, 0)
-    # 3136 rows (a ResNet-50 stage-3 layer at batch 16): seven row tiles of equal height instead of six full + one sliver
+    # 3136 rows (a ResNet-50 stage-3 layer at batch 16): seven 512-row tiles x 16 column tiles x 16 chunks in equal runs
     assert _C.lib.atb_lut_gemm_plan(3136, 256, 1024, 0, -1, plan) == 0
-    assert (plan.block_rows, plan.chunks_per_tile) == (448, 16) and plan.blocks <= 148
+    assert (plan.block_rows, plan.chunks_per_tile) == (512, 16) and plan.blocks <= 148
     assert plan.blocks * plan.units_per_block >= 7 * 16 * 16 > (plan.blocks - 1) * plan.units_per_block
+    # fewer than 512 rows: one shorter tile (a multiple of the 32 rows a warp holds)
+    assert _C.lib.atb_lut_gemm_plan(200, 64, 64, 0, -1, plan) == 0 and plan.block_rows == 224
     # every tile cut in three: more blocks than SMs is fine (nobody waits for anybody)
     assert _C.lib.atb_lut_gemm_plan(3136, 256, 1024, 0, (3 << 16) | 64, plan) == 0
     assert (plan.block_rows, plan.units_per_block, plan.blocks, plan.cut_tiles) == (64, 6, 49 * 16 * 16 // 6 + 1, 1)
