@@ -46,6 +46,7 @@ _SIGNATURES = {
     "atb_device_status": (_i, [ctypes.POINTER(ctypes.c_int)]),
     "atb_lut_image_bytes": (_sz, []),
     "atb_lut_prepare": (_i, [_vp, _vp, _vp]),
+    "atb_lut_image_class": (_i, [_vp, ctypes.POINTER(ctypes.c_int), _vp]),
     "atb_quantize_u8": (_i, [_vp, _vp, _ll, _i, _vp]),
     "atb_quantize_transpose_u8": (_i, [_vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]),
     "atb_im2col_u8": (_i, [_vp, _i] + [_i] * 12 + [_i, _vp, _vp]),

@@ -94,7 +94,30 @@ def lut_image(lut: Tensor) -> Tensor:
     with _Guard(lut):
         _check(_lib.atb_lut_prepare(_ptr(src), _ptr(img), _stream(lut)), "atb_lut_prepare")
     _images[key] = (weakref.ref(lut, lambda _r, k=key: _images.pop(k, None)), (lut._version, lut.data_ptr()), img)
+    _image_class.pop(img.data_ptr(), None)
     return img
+
+
+_image_class: dict = {}   # image data_ptr -> table class (0 int16, 1 uint16, 2 fp32), asked for once per image build
+FP32_TABLE_ON_CHIP = True  # tables of the fp32 class run on the cluster kernel (False: gather from global memory)
+
+
+def _class_flag(image: Tensor) -> int:
+    """cfg bit 24 when the image holds a table of the fp32 class.  The class is read back from the device once per
+    image build (a 16-byte copy that synchronises the stream); during a stream capture the question cannot be asked
+    and an unknown class takes the generic kernel."""
+    if not FP32_TABLE_ON_CHIP:
+        return 0
+    key = image.data_ptr()
+    cls = _image_class.get(key)
+    if cls is None:
+        if torch.cuda.is_current_stream_capturing():
+            return 0
+        out = ctypes.c_int(-1)
+        with _Guard(image):
+            _check(_lib.atb_lut_image_class(_ptr(image), ctypes.byref(out), _stream(image)), "atb_lut_image_class")
+        cls = _image_class[key] = out.value
+    return (1 << 24) if cls == 2 else 0
 
 
 _PAIR_BYTES = int(_lib.atb_pair_table_bytes())
@@ -158,7 +181,7 @@ def _normalise_cfg(cfg: int) -> int:
     rows = cfg & 0xFFFF
     if rows % 32 != 0 or rows > 512:
         return -1
-    return cfg & 0xFFFFFF
+    return cfg & 0x3FFFFFF
 
 
 def lut_gemm_launch(x_idx: Tensor, w_idx: Tensor, image: Tensor, y: Tensor, N: int, K: int, L: int, O: int,
@@ -166,6 +189,9 @@ def lut_gemm_launch(x_idx: Tensor, w_idx: Tensor, image: Tensor, y: Tensor, N: i
                     beta: Tensor | None = None, zero_x: Tensor | None = None, zero_w: Tensor | None = None,
                     wsum: Tensor | None = None, cfg: int = -1) -> None:
     cfg = _normalise_cfg(int(cfg))
+    flag = _class_flag(image) if wb_rows == 0 else 0
+    if flag:
+        cfg = max(cfg, 0) | flag
     plan = _C.GemmPlan()
     with _Guard(y):
         _check(_lib.atb_lut_gemm_plan(N * L, K, O, wb_rows, cfg, ctypes.byref(plan)), "atb_lut_gemm_plan")
@@ -193,6 +219,9 @@ def lut_conv2d_launch(img8: Tensor, w_idx: Tensor, image: Tensor, geom, pad_inde
     _require(OH >= 1 and OW >= 1, "conv geometry yields empty output")
     y = torch.empty((B, O, OH, OW), dtype=torch.float32, device=img8.device)
     cfg = _normalise_cfg(int(cfg))
+    flag = _class_flag(image)
+    if flag:
+        cfg = max(cfg, 0) | flag
     plan = _C.GemmPlan()
     with _Guard(y):
         _check(_lib.atb_lut_gemm_plan(B * OH * OW, C * kh * kw, O, 0, cfg, ctypes.byref(plan)), "atb_lut_gemm_plan")

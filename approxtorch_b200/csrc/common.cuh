@@ -58,6 +58,10 @@ struct LutImage {
     int16_t tab16[65536];
     float tabT32[65536];
     float tab32[65536];
+    // tabTP32: transposed ([w][x]) and x-permuted within each half-row of 128 for the fp32 staging loads: position
+    // h*128 + 4*l + e of row w holds x = h*128 + l + 32*e, so that lane l of a staging warp gets the four entries
+    // x = l, l+32, l+64, l+96 of its half-row with one 16-byte load
+    float tabTP32[65536];
 };
 
 enum LutClass { LUT_I16 = 0, LUT_U16 = 1, LUT_F32 = 2 };
@@ -109,6 +113,24 @@ inline bool conv_out_shape(int H, int W, int kh, int kw, int sh, int sw, int ph,
     *OW = static_cast<int>(ow);
     return true;
 }
+
+// Forward LUT GEMM on a table of the fp32 class, run by the cluster kernel of pair_grad.cu (filled in by lut_gemm.cu)
+struct PairFwdParams {
+    const uint8_t* x;
+    const uint8_t* w;
+    const float* tab;          // LutImage::tabTP32
+    float* y;
+    long long R;
+    int K, L, O;
+    int image_mode, x_xor, pad_index;
+    ConvGeom g;
+    const float* alpha;
+    const float* beta;
+    const float* zero_x;
+    const float* zero_w;
+    const int* wsum;
+};
+int pair_forward_launch(const PairFwdParams& p, int mode, cudaStream_t stream);
 
 inline int grid_for(long long work, int threads, int cap)
 {

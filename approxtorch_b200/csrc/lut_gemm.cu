@@ -916,6 +916,16 @@ static int launch_gemm(GemmArgs a, int cfg, void* scratch, size_t scratch_bytes,
         lut_gemm_empty_k_kernel<<<grid_for(a.R * a.O, 256, 4096), 256, 0, stream>>>(a);
         return check_launch("lut_gemm_empty_k_kernel");
     }
+    if (cfg >= 0 && ((cfg >> 24) & 1) && a.wb_rows == 0) {
+        // The caller knows the table is of the fp32 class (atb_lut_image_class): whole-reduction tiles on the kernel
+        // that keeps the fp32 table on chip, half in each block of a two-block cluster.
+        PairFwdParams p{};
+        p.x = a.x; p.w = a.w; p.tab = a.img->tabTP32; p.y = a.y;
+        p.R = a.R; p.K = a.K; p.L = a.L; p.O = a.O;
+        p.image_mode = a.image_mode; p.x_xor = a.x_xor; p.pad_index = a.pad_index; p.g = a.g;
+        p.alpha = a.alpha; p.beta = a.beta; p.zero_x = a.zero_x; p.zero_w = a.zero_w; p.wsum = a.wsum;
+        return pair_forward_launch(p, (cfg >> 25) & 1, stream);
+    }
     FullPlan plan;
     int rc = make_plan(a.R, a.K, a.O, a.wb_rows, cfg, &plan);
     if (rc != ATB_OK) return rc;
@@ -950,12 +960,25 @@ extern "C" int atb_lut_gemm_plan(long long R, int K, int O, int wb_rows, int cfg
     FullPlan p;
     const int rc = make_plan(R, K, O, wb_rows, cfg, &p);
     if (rc != ATB_OK) return rc;
+    if (cfg >= 0 && ((cfg >> 24) & 1) && wb_rows == 0) { p.cut = 0; p.scratch_bytes = 0; }     // fp32-class kernel: whole reductions
     plan->block_rows = p.block_rows;
     plan->blocks = p.ctas;
     plan->units_per_block = p.units_per_cta;
     plan->chunks_per_tile = p.nchunks;
     plan->cut_tiles = p.cut;
     plan->scratch_bytes = p.scratch_bytes;
+    return ATB_OK;
+}
+
+extern "C" int atb_lut_image_class(const void* lut_image, int* cls /*host*/, void* stream)
+{
+    ATB_REQUIRE(lut_image != nullptr && cls != nullptr, "null pointer");
+    int flags[4] = {0, 0, 0, 0};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(flags, lut_image, sizeof(flags), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) { set_error("atb_lut_image_class: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
+    *cls = flags[0] == 0 ? LUT_I16 : (flags[1] == 0 ? LUT_U16 : LUT_F32);
     return ATB_OK;
 }
 

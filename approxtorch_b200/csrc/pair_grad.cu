@@ -108,6 +108,46 @@ __device__ __forceinline__ int ld_cluster_s32(uint32_t addr)
     return v;
 }
 
+// This block's half of the table (cluster rank r holds rows 128 r .. 128 r + 127): one bulk asynchronous copy with a
+// bounded wait; both blocks of the cluster then meet, so that each knows the other's half is in place and learns
+// whether it arrived.  Returns false (and raises the status word) when either half is missing.
+template <bool CLUSTER>
+__device__ __forceinline__ bool table_half_load(const float* tab, uint32_t s_tab_addr, uint64_t* s_bar, int* s_ok)
+{
+    if constexpr (!CLUSTER) {
+        return true;
+    } else {
+        const int tid = threadIdx.x;
+        const uint32_t rank = cluster_rank();
+        const uint32_t bar_a = static_cast<uint32_t>(__cvta_generic_to_shared(s_bar));
+        if (tid == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a) : "memory");
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(PTabHalf) : "memory");
+            const char* src = reinterpret_cast<const char*>(tab) + static_cast<size_t>(rank) * PTabHalf;
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(s_tab_addr + i * 32768), "l"(src + i * 32768), "r"(32768), "r"(bar_a) : "memory");
+        }
+        __syncthreads();
+        bool mine = false;
+        for (int i = 0; i < (1 << 20) && !mine; ++i) {
+            uint32_t done;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(done) : "r"(bar_a) : "memory");
+            mine = done != 0;
+        }
+        mine = __syncthreads_and(mine);
+        if (tid == 0) *s_ok = mine ? 1 : 0;
+        cluster_sync_all();
+        const int peer_ok = ld_cluster_s32(map_to_rank(static_cast<uint32_t>(__cvta_generic_to_shared(s_ok)), rank ^ 1u));
+        const bool ok = mine && peer_ok != 0;
+        if (!ok && tid == 0) atomicExch(&g_pair_status, 1);
+        return ok;
+    }
+}
+
 // ---- staging ------------------------------------------------------------------------------------------------------
 struct QuadPart {
     float4 c[4];            // c[t]: entries x = l, l+32, l+64, l+96 (+ 128 h) of the column of channel q + 8 t
@@ -116,7 +156,7 @@ struct QuadPart {
 // Warp p builds half h = p >> 3 of quad row q = p & 7.  `wstep` holds the k-step's 32 weight indices, quad row by
 // quad row (the four of a quad row in one word).
 template <bool CLUSTER>
-__device__ __forceinline__ void fetch_part(const PairArgs& a, uint32_t s_tab_addr, const uint8_t* wstep, int warp, int lane, QuadPart& v)
+__device__ __forceinline__ void fetch_part(const float* tab, uint32_t s_tab_addr, const uint8_t* wstep, int warp, int lane, QuadPart& v)
 {
     const int q = warp & 7, h = warp >> 3;
     const uint32_t w4 = reinterpret_cast<const uint32_t*>(wstep)[q];
@@ -127,7 +167,7 @@ __device__ __forceinline__ void fetch_part(const PairArgs& a, uint32_t s_tab_add
             const uint32_t local = s_tab_addr + (wi & 127u) * 1024u + h * 512u + lane * 16u;
             v.c[t] = ld_cluster_f4(map_to_rank(local, wi >> 7));
         } else {
-            v.c[t] = __ldg(reinterpret_cast<const float4*>(a.tab + (wi << 8) + (h << 7)) + lane);
+            v.c[t] = __ldg(reinterpret_cast<const float4*>(tab + (wi << 8) + (h << 7)) + lane);
         }
     }
 }
@@ -269,37 +309,7 @@ __global__ void __launch_bounds__(PThreads, 1) pair_grad_kernel(const PairArgs a
     const int g = lane >> 3, q = lane & 7;
     const uint32_t s_tab_addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
 
-    bool ok = true;
-    if constexpr (CLUSTER) {
-        // this block's half of the table: one bulk copy, bounded wait; both blocks of the cluster then meet so that
-        // each knows the other's half is in place (and learns whether it arrived)
-        const uint32_t rank = cluster_rank();
-        const uint32_t bar_a = static_cast<uint32_t>(__cvta_generic_to_shared(&s_bar));
-        if (tid == 0) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_a) : "memory");
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(PTabHalf) : "memory");
-            const char* src = reinterpret_cast<const char*>(a.tab) + static_cast<size_t>(rank) * PTabHalf;
-#pragma unroll
-            for (int i = 0; i < 4; ++i)
-                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                             ::"r"(s_tab_addr + i * 32768), "l"(src + i * 32768), "r"(32768), "r"(bar_a) : "memory");
-        }
-        __syncthreads();
-        bool mine = false;
-        for (int i = 0; i < (1 << 20) && !mine; ++i) {
-            uint32_t done;
-            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                         : "=r"(done) : "r"(bar_a) : "memory");
-            mine = done != 0;
-        }
-        mine = __syncthreads_and(mine);
-        if (tid == 0) s_ok = mine ? 1 : 0;
-        cluster_sync_all();
-        const int peer_ok = ld_cluster_s32(map_to_rank(static_cast<uint32_t>(__cvta_generic_to_shared(&s_ok)), rank ^ 1u));
-        ok = mine && peer_ok != 0;
-        if (!ok && tid == 0) atomicExch(&g_pair_status, 1);
-    }
+    const bool ok = table_half_load<CLUSTER>(a.tab, s_tab_addr, &s_bar, &s_ok);
 
     long long u = static_cast<long long>(blockIdx.x) * a.units_per_cta;
     const long long u_end = min(a.total_units, u + a.units_per_cta);
@@ -333,7 +343,7 @@ __global__ void __launch_bounds__(PThreads, 1) pair_grad_kernel(const PairArgs a
             __syncthreads();
             {
                 QuadPart v;
-                fetch_part<CLUSTER>(a, s_tab_addr, s_w, warp, lane, v);
+                fetch_part<CLUSTER>(a.tab, s_tab_addr, s_w, warp, lane, v);
                 store_part(s_stage, warp, lane, v);
             }
             __syncthreads();
@@ -354,7 +364,7 @@ __global__ void __launch_bounds__(PThreads, 1) pair_grad_kernel(const PairArgs a
                     else if (has_next) wnext = s_w + ((cur ^ 1) * PChunk) * PS;
                     const uint8_t* stage_cur = s_stage + (step & 1) * PStageBytes;
                     QuadPart v;
-                    if (wnext != nullptr) fetch_part<CLUSTER>(a, s_tab_addr, wnext, warp, lane, v);
+                    if (wnext != nullptr) fetch_part<CLUSTER>(a.tab, s_tab_addr, wnext, warp, lane, v);
 
                     const uint2 xb = *reinterpret_cast<const uint2*>(xrow);          // the 8 rows' activation indices
                     const float4* col = reinterpret_cast<const float4*>(stage_cur + q * PPitch);
@@ -436,6 +446,142 @@ __global__ void __launch_bounds__(PThreads, 1) pair_grad_kernel(const PairArgs a
     if constexpr (CLUSTER) cluster_sync_all();       // the peer may still be reading this block's half of the table
 }
 
+// ---- forward on a table of the fp32 class ----------------------------------------------------------------------------
+// y[r, o] = sum_k T[w(o,k)][x(r,k)] accumulated in fp32 in ascending k (the reference's order,
+// approxtorch/backend/csrc/claude/bgemm_lut_kernels.cuh:278-281, 344-359; it gathers from the 256 KB table in global
+// memory).  Tiles of 512 pixel rows x 32 channels, the whole reduction inside one block (no cut along k, so the sum
+// order is exactly ascending k), tiles dealt round-robin to a persistent grid, column tile fastest.
+struct FwdEpilogue {
+    float* y;
+    const float* alpha;
+    const float* beta;
+    const float* zero_x;
+    const float* zero_w;
+    const int* wsum;
+};
+
+__device__ __forceinline__ float fwd_finalize(float total, int xsum, int o, int K, const FwdEpilogue& ep)
+{
+    float v = total;
+    if (ep.zero_x != nullptr) {
+        // integer zero-point terms added in double, one rounding back to fp32
+        const long long zx = llrintf(__ldg(ep.zero_x));
+        const long long zw = llrintf(__ldg(ep.zero_w + o));
+        const long long ws = __ldg(ep.wsum + o);
+        v = static_cast<float>(static_cast<double>(total) +
+                               static_cast<double>(-zw * xsum - zx * ws + static_cast<long long>(K) * zx * zw));
+    }
+    if (ep.alpha != nullptr) v = v * __ldg(ep.alpha + o);
+    if (ep.beta != nullptr) v = v + __ldg(ep.beta + o);
+    return v;
+}
+
+template <bool CLUSTER>
+__global__ void __launch_bounds__(PThreads, 1) pair_fwd_kernel(PairArgs a, const FwdEpilogue ep)
+{
+    extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ __align__(8) uint64_t s_bar;
+    __shared__ int s_ok;
+    uint8_t* s_stage = smem + PSmemStage;
+    uint8_t* s_x = smem + PSmemX;
+    uint8_t* s_w = smem + PSmemW;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 3, q = lane & 7;
+    const uint32_t s_tab_addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const bool ok = table_half_load<CLUSTER>(a.tab, s_tab_addr, &s_bar, &s_ok);
+    if (a.pad_index < 0) a.pad_index = min(255, max(0, static_cast<int>(llrintf(__ldg(ep.zero_x)))));
+    const bool want_xsum = ep.zero_x != nullptr;
+    const long long tiles = static_cast<long long>(a.row_tiles) * a.ch_tiles;
+    for (long long tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+        const int rt = static_cast<int>(tile / a.ch_tiles);
+        const int c0 = static_cast<int>(tile - static_cast<long long>(rt) * a.ch_tiles) * PS;
+        const long long r0 = static_cast<long long>(rt) * PQ;
+        const PRow rc = make_row(a, min(r0 + tid, a.R - 1));
+        const uint8_t* wcol = a.w + static_cast<long long>(min(c0 + tid, a.O - 1)) * a.K;
+        float acc[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { acc[j][0] = 0.0f; acc[j][1] = 0.0f; acc[j][2] = 0.0f; acc[j][3] = 0.0f; }
+        int xsum = 0;
+        uint32_t xr[4], wr[4];
+        __syncthreads();                                  // the previous tile is done with the tiles and the turning space
+        p_load_chunk(a, rc, wcol, 0, tid, xr, wr);
+        p_store_chunk(s_x, s_w, 0, tid, xr, wr);
+        __syncthreads();
+        {
+            QuadPart v;
+            fetch_part<CLUSTER>(a.tab, s_tab_addr, s_w, warp, lane, v);
+            store_part(s_stage, warp, lane, v);
+        }
+        __syncthreads();
+        int step = 0;
+        for (int ci = 0; ci < a.nchunks; ++ci) {
+            const int k0 = ci * PChunk;
+            const int kc = min(PChunk, a.K - k0);
+            const int cur = ci & 1;
+            const bool has_next = ci + 1 < a.nchunks;
+            if (has_next) p_load_chunk(a, rc, wcol, k0 + PChunk, tid, xr, wr);
+            for (int kk = 0; kk < kc; ++kk, ++step) {
+                if (has_next && kk == 4) p_store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr);
+                const uint8_t* xrow_w = s_x + (cur * PChunk + kk) * PQ + warp * 32;
+                const uint8_t* wstep = s_w + (cur * PChunk + kk) * PS;
+                const uint8_t* wnext = nullptr;
+                if (kk + 1 < kc) wnext = wstep + PS;
+                else if (has_next) wnext = s_w + ((cur ^ 1) * PChunk) * PS;
+                QuadPart v;
+                if (wnext != nullptr) fetch_part<CLUSTER>(a.tab, s_tab_addr, wnext, warp, lane, v);
+                if (want_xsum) xsum += static_cast<int>(xrow_w[lane]);
+                const uint2 xb = *reinterpret_cast<const uint2*>(xrow_w + g * 8);
+                const float4* col = reinterpret_cast<const float4*>(s_stage + (step & 1) * PStageBytes + q * PPitch);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const uint32_t xi = ((j < 4 ? xb.x : xb.y) >> (8 * (j & 3))) & 0xffu;
+                    const float4 e = col[xi];
+                    acc[j][0] += e.x; acc[j][1] += e.y; acc[j][2] += e.z; acc[j][3] += e.w;
+                }
+                if (wnext != nullptr) store_part(s_stage + ((step + 1) & 1) * PStageBytes, warp, lane, v);
+                __syncthreads();
+            }
+        }
+        // ---- epilogue: thread (g, q) holds rows warp*32 + g*8 + j, channels c0 + q + 8 t
+        if (a.L == 1) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const long long r = r0 + warp * 32 + g * 8 + j;
+                const int xs = __shfl_sync(0xffffffffu, xsum, g * 8 + j);
+                if (r >= a.R) continue;
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const int o = c0 + q + 8 * t;
+                    if (o < a.O) ep.y[r * a.O + o] = fwd_finalize(acc[j][t], xs, o, a.K, ep);
+                }
+            }
+        } else {
+            // the fast axis of y[n, o, l] is the pixel: turn the warp's 32 x 32 tile around in the (now free) stage area
+            constexpr int kPitch = 33;
+            float* turn = reinterpret_cast<float*>(s_stage) + warp * (32 * kPitch);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int xs = __shfl_sync(0xffffffffu, xsum, g * 8 + j);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    const int oc = q + 8 * t;
+                    turn[oc * kPitch + g * 8 + j] = (c0 + oc < a.O) ? fwd_finalize(acc[j][t], xs, c0 + oc, a.K, ep) : 0.0f;
+                }
+            }
+            __syncwarp();
+            const long long r = r0 + warp * 32 + lane;
+            if (r < a.R) {
+                const long long n = r / a.L;
+                const long long l = r - n * a.L;
+                float* dst = ep.y + (n * a.O + c0) * a.L + l;
+                const int ncols = min(PS, a.O - c0);
+                for (int c = 0; c < ncols; ++c) dst[static_cast<long long>(c) * a.L] = turn[c * kPitch + lane];
+            }
+        }
+    }
+    if constexpr (CLUSTER) cluster_sync_all();       // the peer may still be reading this block's half of the table
+}
+
 template <bool GRAD_W, bool CLUSTER>
 static int launch_pair(const PairArgs& a, int ctas, cudaStream_t stream)
 {
@@ -466,6 +612,58 @@ static int launch_pair(const PairArgs& a, int ctas, cudaStream_t stream)
     e = cudaLaunchKernelEx(&cfg, pair_grad_kernel<GRAD_W, CLUSTER>, a);
     if (e != cudaSuccess) { set_error("pair_grad_kernel launch: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
     return check_launch("pair_grad_kernel");
+}
+
+template <bool CLUSTER>
+static int launch_pair_fwd(const PairArgs& a, const FwdEpilogue& ep, int ctas, cudaStream_t stream)
+{
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        set_error("cudaGetDevice: %s", e != cudaSuccess ? cudaGetErrorString(e) : "device index out of range");
+        return ATB_ERR_CUDA;
+    }
+    if (!attr_set[dev]) {
+        e = cudaFuncSetAttribute(pair_fwd_kernel<CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize, PSmemTotal);
+        if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+    cfg.blockDim = dim3(PThreads);
+    cfg.dynamicSmemBytes = PSmemTotal;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CLUSTER ? 2 : 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, pair_fwd_kernel<CLUSTER>, a, ep);
+    if (e != cudaSuccess) { set_error("pair_fwd_kernel launch: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
+    return check_launch("pair_fwd_kernel");
+}
+
+int pair_forward_launch(const PairFwdParams& p, int mode, cudaStream_t stream)
+{
+    PairArgs a{};
+    a.x = p.x; a.w = p.w; a.tab = p.tab;
+    a.R = p.R; a.K = p.K; a.L = p.L; a.O = p.O;
+    a.image_mode = p.image_mode; a.x_xor = p.x_xor; a.pad_index = p.pad_index; a.g = p.g;
+    a.row_tiles = ceil_div(a.R, PQ);
+    a.ch_tiles = ceil_div(a.O, PS);
+    a.nchunks = ceil_div(a.K, PChunk);
+    const FwdEpilogue ep{p.y, p.alpha, p.beta, p.zero_x, p.zero_w, p.wsum};
+    const bool cluster = (mode & 1) == 0;
+    const long long tiles = static_cast<long long>(a.row_tiles) * a.ch_tiles;
+    int sms = sm_count();
+    if (cluster) sms &= ~1;
+    long long ctas = tiles < sms ? tiles : sms;
+    if (cluster && (ctas & 1)) ++ctas;
+    return cluster ? launch_pair_fwd<true>(a, ep, static_cast<int>(ctas), stream)
+                   : launch_pair_fwd<false>(a, ep, static_cast<int>(ctas), stream);
 }
 
 __global__ void pair_zero_kernel(float* p, long long n)

@@ -48,6 +48,10 @@ __global__ void lut_prepare_kernel(const float* __restrict__ lut, LutImage* __re
     img->tab32[i] = v;
     img->tabT16[t] = v16;
     img->tabT32[t] = v;
+    {
+        const int xh = (i >> 8) >> 7, xl = (i >> 8) & 127;
+        img->tabTP32[((i & 255) << 8) + (xh << 7) + ((xl & 31) << 2) + (xl >> 5)] = v;
+    }
     const int xi = i >> 8, wi = i & 255;
     // pair i = xi & 127 = {x = i, x = i + 128} sits at word 4 * (i & 31) + (i >> 5) of row wi: a 16-byte load by
     // lane l then yields the pairs l, l + 32, l + 64, l + 96

@@ -13,6 +13,7 @@ What is measured, and against what:
                  operator-form fake-quant forward and backward) on a 256 MiB fp32 tensor: algorithmic bytes / time
                  against the measured copy bandwidth;
 * ``backward`` - STE / LRE image-space backward (grad_x, grad_w) on the ResNet-18 layer set: 2*B*L*K*O flop / time;
+* ``fp32``     - a table of the fp32 class on the headline GEMM shape: table on chip (cluster) vs global memory;
 * ``custom``   - custom-pair backward and the depthwise forward on the single-layer configuration's shape: lookups/s;
 * ``layers``   - the LUT conv forward per distinct ResNet-50 layer shape (with the unsigned zero-point epilogue):
                  plan chosen, time, lookups/s, fraction of the lookup roofline, and the multiplicity-weighted total.
@@ -226,6 +227,33 @@ def lut_conv_layers(dev, batch, pk=None, layers=None):
                       "the model, where the previous layer has just written them"}
 
 
+# ----------------------------------------------------------------------------------------------- fp32-class tables
+def fp32_table(dev, pk=None):
+    """A table that is not 16-bit exact (0.5 grid) on the headline GEMM shape (65536 x 576 x 256): the kernel that holds
+    the fp32 table in a two-block cluster's shared memory, the same kernel staging from global memory, and the
+    generic kernel's gather from global memory."""
+    pk = pk or peaks(dev)
+    R, K, O = 65536, 576, 256
+    lut = (torch.randint(-4000, 4000, (65536,), device=dev).float() * 0.5)
+    img = ops.lut_image(lut)
+    x = torch.randint(0, 256, (R, K), dtype=torch.uint8, device=dev)
+    w = torch.randint(0, 256, (O, K), dtype=torch.uint8, device=dev)
+    y = torch.empty((R, O), dtype=torch.float32, device=dev)
+    macs = float(R) * K * O
+    out = {}
+    saved = ops.FP32_TABLE_ON_CHIP
+    try:
+        for name, on_chip, cfg in (("cluster_shared_memory", True, -1), ("staged_from_global_memory", True, 1 << 25),
+                                   ("gather_from_global_memory", False, -1)):
+            ops.FP32_TABLE_ON_CHIP = on_chip
+            ms = _time_ms(lambda: ops.lut_gemm_launch(x, w, img, y, R, K, 1, O, cfg=cfg), iters=3, warmup=2, reps=3)
+            out[name] = {"ms": ms, "lookups_per_s": macs / (ms * 1e-3), "frac_of_lookup_peak": macs / (ms * 1e-3) / pk["lookup_peak"]}
+    finally:
+        ops.FP32_TABLE_ON_CHIP = saved
+    out["shape"] = [R, K, O]
+    return out
+
+
 # ----------------------------------------------------------------------------------------------- whole model
 def unsigned_truncated_table(dev, low_bits=6):
     """Exact unsigned product i*j with its low bits cleared (the ResNet-50 inference configuration's table)."""
@@ -261,7 +289,7 @@ def resnet50_forward(dev, batch, iters=3):
     return {"batch": batch, "ms": ms, "img_s": batch / (ms * 1e-3), "launch": "eager (no CUDA graph)"}
 
 
-def run_all(dev, which=("lds", "stream", "backward", "custom", "layers"), batches=(128, 16)):
+def run_all(dev, which=("lds", "stream", "backward", "custom", "fp32", "layers"), batches=(128, 16)):
     pk = peaks(dev)
     out = {"peaks": pk}
     for name in which:
@@ -274,6 +302,8 @@ def run_all(dev, which=("lds", "stream", "backward", "custom", "layers"), batche
                 out["backward_ste_resnet18_cifar_b256"] = backward_kernels(dev)
             elif name == "custom":
                 out["custom"] = custom_kernels(dev, pk)
+            elif name == "fp32":
+                out["fp32_class_table"] = fp32_table(dev, pk)
             elif name == "model":
                 for b in batches:
                     out[f"resnet50_forward_b{b}"] = resnet50_forward(dev, b)
@@ -299,7 +329,7 @@ def _print_table(res):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="lds,stream,backward,custom,layers")
+    ap.add_argument("--only", default="lds,stream,backward,custom,fp32,layers")
     ap.add_argument("--batch", default="128,16")
     ap.add_argument("--json", action="store_true")
     a = ap.parse_args()

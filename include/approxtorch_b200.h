@@ -49,6 +49,11 @@ int atb_device_status(int* status /*host*/);
  *  approxtorch/backend/csrc/claude/bgemm_float_claude.cu:163-192); built once per table, not per call. */
 size_t atb_lut_image_bytes(void);
 int atb_lut_prepare(const float* lut /*[65536]*/, void* image /*atb_lut_image_bytes()*/, void* stream);
+/* Class of a prepared table, read back to the host (synchronises `stream`): 0 = int16-exact, 1 = uint16-exact,
+ * 2 = neither (fp32).  The eligibility rules are the reference's
+ * (approxtorch/backend/csrc/claude/bgemm_lut_kernels.cuh:126-134).  A host that knows the class is 2 can ask for
+ * the kernel that keeps the fp32 table on chip (cfg bit 24 of the GEMM / conv entries). */
+int atb_lut_image_class(const void* lut_image, int* cls /*host*/, void* stream);
 
 /* ---- operand prepasses ------------------------------------------------------------------ */
 /* fp32 integer-valued operand -> uint8 LUT index, clamp(rn(v)+offset, 0, 255)
@@ -80,7 +85,11 @@ int atb_im2col_u8(const void* x, int dtype, int N, int C, int H, int W, int kh, 
  *
  * cfg: -1 automatic.  Otherwise bits 0-15 pixel rows per tile (a multiple of 32 up to 512; 0 = automatic) and
  * bits 16-23 the cutting rule: 0 automatic, 1 never cut a tile (runs of whole tiles), S > 1 cut every tile into
- * (about) S k-segments, one block each.  Other bits are ignored.
+ * (about) S k-segments, one block each.  Bit 24: the table is known to be of the fp32 class (atb_lut_image_class):
+ * run it on the kernel that holds the 256 KB fp32 table in the shared memory of a two-block cluster, half each,
+ * read across the cluster (tiles of 512 rows x 32 channels, whole reductions in ascending k, no scratch); without
+ * the bit such tables are gathered from global memory.  Bit 25 (with bit 24): stage from global memory instead of
+ * the cluster's shared memory.  Other bits are ignored.
  *
  * The plan says how a launch will be laid out and how much scratch (bytes) it needs. */
 typedef struct {

@@ -123,6 +123,73 @@ def test_lut_classes(dev):
     np.testing.assert_array_equal(y.cpu().numpy().astype(np.int64), ref)
 
 
+def test_fp32_class_table_on_chip_equals_the_global_gather(dev):
+    """Tables that are not 16-bit exact: the kernel that keeps the fp32 table in a two-block cluster's shared memory,
+    the same kernel staging from global memory, and the generic kernel's gather from global memory all sum in fp32
+    in ascending k, so they agree bit for bit with each other and with the ascending-k oracle - column operand,
+    row-major operand, image operand, with the zero-point epilogue, odd sizes."""
+    ops = _ops()
+    rng = np.random.default_rng(61)
+    tab = (rng.integers(-3000, 3000, (256, 256)) * 0.25).astype(np.float32)          # sums round in fp32
+    assert lo.lut_class(tab) == "f32"
+    lt = _t(tab.reshape(-1), dev)
+    img = ops.lut_image(lt)
+    assert ops._class_flag(img) == 1 << 24
+    N, K, L, O = 3, 150, 700, 70
+    x = rng.integers(0, 256, (N, K, L), dtype=np.uint8)
+    w = rng.integers(0, 256, (O, K), dtype=np.uint8)
+    ref = lo.bgemm_f32_ascending(x, w, tab)
+    outs = []
+    for cfg in (-1, 1 << 25):                                 # cluster shared memory / staging from global memory
+        y = torch.empty((N, O, L), dtype=torch.float32, device=dev)
+        ops.lut_gemm_launch(_t(x, dev), _t(w, dev), img, y, N, K, L, O, cfg=cfg)
+        outs.append(y)
+    ops.FP32_TABLE_ON_CHIP = False
+    try:
+        y = torch.empty((N, O, L), dtype=torch.float32, device=dev)
+        ops.lut_gemm_launch(_t(x, dev), _t(w, dev), img, y, N, K, L, O, cfg=1 << 16)          # generic kernel, whole tiles
+        outs.append(y)
+    finally:
+        ops.FP32_TABLE_ON_CHIP = True
+    for y in outs:
+        np.testing.assert_array_equal(y.cpu().numpy(), ref)
+    # row-major operand (L == 1) with scale, shift and zero points
+    xr = np.ascontiguousarray(x.transpose(0, 2, 1).reshape(N * L, K))
+    alpha = _t(rng.uniform(0.5, 2.0, O).astype(np.float32), dev)
+    beta = _t(rng.uniform(-1, 1, O).astype(np.float32), dev)
+    zx = _t(np.array([91.0], dtype=np.float32), dev)
+    zw = _t(rng.integers(0, 256, O).astype(np.float32), dev)
+    wsum = _t(w.astype(np.int64).sum(axis=1).astype(np.int32), dev)
+    ya = torch.empty((N * L, O), dtype=torch.float32, device=dev)
+    yb = torch.empty_like(ya)
+    kw = dict(alpha=alpha, beta=beta, zero_x=zx, zero_w=zw, wsum=wsum)
+    ops.lut_gemm_launch(_t(xr, dev), _t(w, dev), img, ya, N * L, K, 1, O, **kw)
+    ops.FP32_TABLE_ON_CHIP = False
+    try:
+        ops.lut_gemm_launch(_t(xr, dev), _t(w, dev), img, yb, N * L, K, 1, O, cfg=1 << 16, **kw)
+    finally:
+        ops.FP32_TABLE_ON_CHIP = True
+    assert torch.equal(ya, yb)
+    # image operand: strided, padded conv with the pad value taken from the zero point
+    B, C, H, W, Oc = 3, 10, 13, 11, 40
+    x8 = rng.integers(0, 256, (B, C, H, W), dtype=np.uint8)
+    wi = rng.integers(0, 256, (Oc, C * 9), dtype=np.uint8)
+    g4 = ((3, 3), (2, 1), (1, 2), (1, 1))
+    ws2 = _t(wi.astype(np.int64).sum(axis=1).astype(np.int32), dev)
+    zw2 = _t(rng.integers(0, 256, Oc).astype(np.float32), dev)
+    ya = ops.lut_conv2d_launch(_t(x8, dev), _t(wi, dev), img, g4, -1, zero_x=zx, zero_w=zw2, wsum=ws2)
+    ops.FP32_TABLE_ON_CHIP = False
+    try:
+        yb = ops.lut_conv2d_launch(_t(x8, dev), _t(wi, dev), img, g4, -1, zero_x=zx, zero_w=zw2, wsum=ws2, cfg=1 << 16)
+    finally:
+        ops.FP32_TABLE_ON_CHIP = True
+    assert torch.equal(ya, yb)
+    cols = lo.im2col_index(x8, 3, 3, 2, 1, 1, 2, 1, 1, 91)
+    raw = lo.bgemm_f32_ascending(cols, wi, tab).astype(np.float64)
+    t = lo.uint8_zero_point_correction(raw, cols, wi, 91.0, zw2.cpu().numpy())
+    np.testing.assert_allclose(ya.flatten(2).cpu().numpy(), t, rtol=1e-6, atol=1e-6 * np.abs(t).max())
+
+
 def test_lut_image_cache_follows_in_place_updates(dev):
     ops = _ops()
     rng = np.random.default_rng(2)
