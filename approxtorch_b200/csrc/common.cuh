@@ -132,6 +132,13 @@ struct PairFwdParams {
 };
 int pair_forward_launch(const PairFwdParams& p, int mode, cudaStream_t stream);
 
+// STE / LRE image-space backward on the tensor cores (tc_grad.cu); used by atb_lre_conv_bwd
+int tc_conv_grad_w(const float* go, const void* x, int x_dtype, const float* dw, const float* go_scale, float* grad_w,
+                   int N, int O, const ConvGeom& g, int pad_index, bool exact_tables, cudaStream_t s);
+int tc_conv_grad_x(const float* go, const uint8_t* widx, const float* dx, const float* go_scale, const float* w_zero,
+                   float* grad_x, int N, int O, const ConvGeom& g, bool exact_tables, cudaStream_t s);
+int tc_status_read(int* status);
+
 inline int grid_for(long long work, int threads, int cap)
 {
     long long b = (work + threads - 1) / threads;

@@ -637,6 +637,12 @@ static int split_factor(long long tiles, long long P)
 
 using namespace atb;
 
+extern "C" int atb_tensor_core_status(int* status /*host*/)
+{
+    ATB_REQUIRE(status != nullptr, "status is null");
+    return tc_status_read(status);
+}
+
 extern "C" int atb_lre_bwd(const float* go, const void* x, int x_dtype, const void* w, int w_dtype, int w_ok_layout,
                            const float* dx, const float* dw, float* grad_x, float* grad_w,
                            int N, int K, int L, int O, void* stream)
@@ -679,11 +685,13 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
                                 const float* dx, const float* dw, const float* go_scale, const float* w_zero,
                                 float* grad_x, float* grad_w,
                                 int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
-                                int dh, int dw_, int pad_index, void* stream)
+                                int dh, int dw_, int pad_index, int flags, void* stream)
 {
     ATB_REQUIRE(N >= 0 && C >= 0 && H >= 0 && W >= 0 && O >= 0, "negative dimension");
     ATB_REQUIRE(x_dtype >= 0 && x_dtype <= 2, "bad dtype");
     ATB_REQUIRE(pad_index >= 0 && pad_index <= 256, "pad_index out of range");
+    const bool exact_tables = (flags & 1) != 0;      // dx / dw (and w_zero) hold integers of magnitude <= 256
+    const bool simt_only = (flags & 2) != 0;         // keep to the fp32 SIMT kernels
     int OH = 0, OW = 0;
     ATB_REQUIRE(conv_out_shape(H, W, kh, kw, sh, sw, ph, pw, dh, dw_, &OH, &OW), "conv geometry yields empty output");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -706,7 +714,10 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
             zero_kernel<<<grid_for(Mx * C, 256, 4096), 256, 0, s>>>(grad_x, Mx * C);
         } else {
             ATB_REQUIRE(go && widx && dx, "null pointer");
-            if (lean && sh * sw <= 64) {
+            if (lean && !simt_only && sh * sw <= 64 && kh * kw <= 128) {
+                rc = tc_conv_grad_x(go, widx, dx, go_scale, w_zero, grad_x, N, O, g, exact_tables, s);
+                if (rc != ATB_OK) return rc;
+            } else if (lean && sh * sw <= 64) {
                 ConvGradXTaps p{go, widx, dx, go_scale, w_zero, grad_x, N, O, static_cast<int>(K), (O + TK - 1) / TK * TK, g,
                                 make_fastdiv(sh), make_fastdiv(sw)};
                 const long long max_class = static_cast<long long>(N) * ((H + sh - 1) / sh) * ((W + sw - 1) / sw);
@@ -731,7 +742,10 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
             ATB_REQUIRE(go && x && dw, "null pointer");
             ATB_REQUIRE(ceil_div(K, 64) <= 65535, "K too large");
             const unsigned gz = split_factor(sgemm_tiles(O, K), P);
-            if (lean) {
+            if (lean && !simt_only) {
+                rc = tc_conv_grad_w(go, x, x_dtype, dw, go_scale, grad_w, N, O, g, pad_index, exact_tables, s);
+                if (rc != ATB_OK) return rc;
+            } else if (lean) {
                 const FastDiv dL = make_fastdiv(OH * OW), dOW = make_fastdiv(OW), dKK = make_fastdiv(kh * kw), dKW = make_fastdiv(kw);
                 if (x_dtype == ATB_U8) {
                     ConvGradWLean<ATB_U8> p{go, x, dw, go_scale, grad_w, O, static_cast<int>(K), pad_index, P, g, dL, dOW, dKK, dKW};

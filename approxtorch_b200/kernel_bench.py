@@ -134,30 +134,37 @@ def stream_kernels(dev, pk=None, mib=256):
 
 
 # ----------------------------------------------------------------------------------------------- dense backward
-def backward_kernels(dev, batch=256, layers=None, mode="ste"):
-    """grad_x and grad_w of the image-space STE / LRE backward per layer shape; flop = 2 * B*OH*OW * C*k*k * O."""
+def backward_kernels(dev, batch=256, layers=None, mode="ste", tensor_cores=True):
+    """grad_x and grad_w of the image-space STE / LRE backward per layer shape; flop = 2 * B*OH*OW * C*k*k * O (the
+    useful fp32-equivalent work, whatever number of bf16 products the tensor-core path spends on it)."""
     layers = layers or RESNET18_CIFAR_LAYERS
     rows, tot = [], {"gx_ms": 0.0, "gw_ms": 0.0, "flop": 0.0}
     table = ops.decode_table(dev, 128) if mode == "ste" else torch.randn(256, device=dev)
-    for (C, H, O, k, s, p, count) in layers:
-        x8 = torch.randint(-127, 128, (batch, C, H, H), dtype=torch.int8, device=dev)
-        widx = torch.randint(0, 256, (O, C * k * k), dtype=torch.uint8, device=dev)
-        g4 = ((k, k), (s, s), (p, p), (1, 1))
-        OH = (H + 2 * p - k) // s + 1
-        go = torch.randn(batch, O, OH, OH, device=dev)
-        gs = torch.rand(O, device=dev)
-        gx_ms = _time_ms(lambda: ops.lre_conv_backward(go, x8, widx, table, table, g4, 128, go_scale=gs, need_w=False),
-                         iters=3, warmup=2, reps=4)
-        gw_ms = _time_ms(lambda: ops.lre_conv_backward(go, x8, widx, table, table, g4, 128, go_scale=gs, need_x=False),
-                         iters=3, warmup=2, reps=4)
-        flop = 2.0 * batch * OH * OH * C * k * k * O
-        rows.append({"C": C, "H": H, "O": O, "k": k, "stride": s, "count": count, "grad_x_ms": gx_ms, "grad_w_ms": gw_ms,
-                     "grad_x_tflops": flop / gx_ms / 1e9, "grad_w_tflops": flop / gw_ms / 1e9})
-        tot["gx_ms"] += gx_ms * count
-        tot["gw_ms"] += gw_ms * count
-        tot["flop"] += flop * count
-    return {"batch": batch, "mode": mode, "layers": rows,
-            "total_grad_x_ms": tot["gx_ms"], "total_grad_w_ms": tot["gw_ms"],
+    exact = mode == "ste"
+    saved = ops.TENSOR_CORE_BACKWARD
+    ops.TENSOR_CORE_BACKWARD = tensor_cores
+    try:
+        for (C, H, O, k, s, p, count) in layers:
+            x8 = torch.randint(-127, 128, (batch, C, H, H), dtype=torch.int8, device=dev)
+            widx = torch.randint(0, 256, (O, C * k * k), dtype=torch.uint8, device=dev)
+            g4 = ((k, k), (s, s), (p, p), (1, 1))
+            OH = (H + 2 * p - k) // s + 1
+            go = torch.randn(batch, O, OH, OH, device=dev)
+            gs = torch.rand(O, device=dev)
+            gx_ms = _time_ms(lambda: ops.lre_conv_backward(go, x8, widx, table, table, g4, 128, go_scale=gs, need_w=False,
+                                                           exact_tables=exact), iters=3, warmup=2, reps=4)
+            gw_ms = _time_ms(lambda: ops.lre_conv_backward(go, x8, widx, table, table, g4, 128, go_scale=gs, need_x=False,
+                                                           exact_tables=exact), iters=3, warmup=2, reps=4)
+            flop = 2.0 * batch * OH * OH * C * k * k * O
+            rows.append({"C": C, "H": H, "O": O, "k": k, "stride": s, "count": count, "grad_x_ms": gx_ms, "grad_w_ms": gw_ms,
+                         "grad_x_tflops": flop / gx_ms / 1e9, "grad_w_tflops": flop / gw_ms / 1e9})
+            tot["gx_ms"] += gx_ms * count
+            tot["gw_ms"] += gw_ms * count
+            tot["flop"] += flop * count
+    finally:
+        ops.TENSOR_CORE_BACKWARD = saved
+    return {"batch": batch, "mode": mode, "path": "tcgen05 (bf16 x3 split, fp32 TMEM accumulator)" if tensor_cores else "fp32 SIMT",
+            "layers": rows, "total_grad_x_ms": tot["gx_ms"], "total_grad_w_ms": tot["gw_ms"],
             "total_grad_x_tflops": tot["flop"] / tot["gx_ms"] / 1e9, "total_grad_w_tflops": tot["flop"] / tot["gw_ms"] / 1e9,
             "fp32_fma_peak_tflops": 74.4}
 
@@ -289,6 +296,47 @@ def resnet50_forward(dev, batch, iters=3):
     return {"batch": batch, "ms": ms, "img_s": batch / (ms * 1e-3), "launch": "eager (no CUDA graph)"}
 
 
+# ----------------------------------------------------------------------------------------------- one launch of each kernel
+def profile_once(dev):
+    """Every hot kernel launched exactly once on a case sized for a profiler capture (operands of the streaming
+    kernels larger than L2, a few hundred MB on the device in all): the command behind the summaries in profiles/."""
+    pk = peaks(dev)
+    n = 64 * (1 << 20)                                     # 256 MiB of fp32
+    x = torch.randn(n, device=dev)
+    scale, zero = torch.tensor(0.03, device=dev), torch.tensor(117.0, device=dev)
+    ops.absmax(x, want_minmax=True)
+    q8, mask = ops.quantize_image(x, scale, None, -127, 127)
+    ops._fakequant_backward(x, mask, scale)
+    del x, q8, mask
+    # LUT conv forward: a ResNet-50 stage-3 1x1 layer at batch 128, and the headline GEMM shape's kernel on one batch item
+    lut = unsigned_truncated_table(dev)
+    img = ops.lut_image(lut)
+    xi = torch.randint(0, 256, (128, 256, 14, 14), dtype=torch.uint8, device=dev)
+    w = torch.randint(0, 256, (1024, 256), dtype=torch.uint8, device=dev)
+    zw = torch.full((1024,), 120.0, device=dev)
+    ops.lut_conv2d_launch(xi, w, img, ((1, 1), (1, 1), (0, 0), (1, 1)), -1, alpha=torch.rand(1024, device=dev), zero_x=zero,
+                          zero_w=zw, wsum=w.sum(dim=1, dtype=torch.int32))
+    # tensor-core backward: a ResNet-18 stage-2 3x3 layer at batch 256
+    x8 = torch.randint(-127, 128, (256, 128, 16, 16), dtype=torch.int8, device=dev)
+    wi = torch.randint(0, 256, (128, 128 * 9), dtype=torch.uint8, device=dev)
+    go = torch.randn(256, 128, 16, 16, device=dev)
+    dec = ops.decode_table(dev, 128)
+    ops.lre_conv_backward(go, x8, wi, dec, dec, ((3, 3), (1, 1), (1, 1), (1, 1)), 128, exact_tables=True)
+    # custom-pair backward and a table of the fp32 class on the single-layer configuration's GEMM shape
+    N, K, L, O = 8, 576, 1024, 64
+    xc = torch.randint(0, 256, (N, K, L), dtype=torch.uint8, device=dev)
+    wc = torch.randint(0, 256, (O, K), dtype=torch.uint8, device=dev)
+    dy = torch.randn(N, O, L, device=dev)
+    tab = torch.randn(65536, device=dev)
+    ops.bgemm_custom_grad_uint8_dx(xc, wc, dy, tab)
+    ops.bgemm_custom_grad_uint8_dw(xc, wc, dy, tab)
+    half = torch.randint(-4000, 4000, (65536,), device=dev).float() * 0.5
+    y = torch.empty((N, O, L), dtype=torch.float32, device=dev)
+    ops.lut_gemm_launch(xc, wc, ops.lut_image(half), y, N, K, L, O)
+    torch.cuda.synchronize()
+    return {"launched": "stats, quantize_image, fakequant_bwd, lut_gemm (1x1 conv), tc_gemm (grad_x, grad_w), pair_grad (dx, dw), pair_fwd"}
+
+
 def run_all(dev, which=("lds", "stream", "backward", "custom", "fp32", "layers"), batches=(128, 16)):
     pk = peaks(dev)
     out = {"peaks": pk}
@@ -300,8 +348,12 @@ def run_all(dev, which=("lds", "stream", "backward", "custom", "fp32", "layers")
                 out["stream"] = stream_kernels(dev, pk)
             elif name == "backward":
                 out["backward_ste_resnet18_cifar_b256"] = backward_kernels(dev)
+                out["backward_lre_resnet18_cifar_b256"] = backward_kernels(dev, mode="lre")
+                out["backward_ste_resnet18_cifar_b256_simt"] = backward_kernels(dev, tensor_cores=False)
             elif name == "custom":
                 out["custom"] = custom_kernels(dev, pk)
+            elif name == "profile":
+                out["profile"] = profile_once(dev)
             elif name == "fp32":
                 out["fp32_class_table"] = fp32_table(dev, pk)
             elif name == "model":

@@ -138,7 +138,7 @@ class _conv2d_int8_ste(Function):
         go = grad_outputs.reshape(B, O, OH, OW).contiguous()
         if groups == 1:
             dec = _ops.decode_table(xq8.device, 128)     # dec[128] == 0: padded taps add nothing
-            gx, gw = _ops.lre_conv_backward(go, xq8, wq, dec, dec, g4, _PAD_INDEX,
+            gx, gw = _ops.lre_conv_backward(go, xq8, wq, dec, dec, g4, _PAD_INDEX, exact_tables=True,
                                             need_x=ctx.needs_input_grad[0], need_w=ctx.needs_input_grad[1])
             return gx, gw, None, None
         dec = _ops.decode_table(xq8.device, 128)         # depthwise: per-channel gather / reduction kernels
@@ -260,7 +260,7 @@ class _approx_conv2d_int8(Function):
         gx = gw = gb = None
         if need_gx or need_gw:
             gimg, gwq = _ops.lre_conv_backward(go, xq8, widx, dxt, dwt, ctx.g4, _PAD_INDEX, go_scale=alpha,
-                                               need_x=need_gx, need_w=need_gw)
+                                               need_x=need_gx, need_w=need_gw, exact_tables=ctx.mode != 'lre')
             if need_gx:
                 gx = torch.ops.approxtorch.fakequant_per_tensor_backward_claude.default(gimg, xmask, scale_x)
             if need_gw:

@@ -163,7 +163,7 @@ class _approx_conv2d_uint8(Function):
         gx = gw = gb = None
         if need_gx or need_gw:
             gimg, gwq = _ops.lre_conv_backward(go, xq8, widx, t_x, t_w_ext, ctx.g4, 256, go_scale=alpha,
-                                               need_x=need_gx, need_w=need_gw, w_zero=zw)
+                                               need_x=need_gx, need_w=need_gw, w_zero=zw, exact_tables=ctx.mode != 'lre')
             if need_gx:
                 gx = torch.ops.approxtorch.fakequant_per_tensor_asymmetric_backward_claude.default(gimg, xmask, scale_x)
             if need_gw:

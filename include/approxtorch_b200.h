@@ -195,12 +195,19 @@ int atb_lre_bwd(const float* go, const void* x, int x_dtype, const void* w, int 
  * channel.  `w_zero` (optional, [O]) is subtracted from the mapped weight, grad_x uses dx[widx[o,k]] - w_zero[o]:
  * the weight zero point of the asymmetric layer, whose correction term -z_w[o] * sum_k q_x has that derivative
  * (approxtorch/nn/Conv2d_uint8.py:308-315).
+ * Runs on the tensor cores (tcgen05, fp32 operands split into three bf16 terms, fp32 accumulation in TMEM) whenever
+ * every tensor is addressable with 32-bit offsets; otherwise on the fp32 SIMT kernels.
+ * flags: bit 0 = dx, dw and w_zero hold integers of magnitude <= 256 (the STE decode tables): half the tensor-core
+ * work; bit 1 = use the SIMT kernels.
  * Replaces the cuDNN convolution_backward calls of approxtorch/nn/bgemm_int8.py:165-212, 259-295. */
 int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t* widx /*[O,K]*/,
                      const float* dx, const float* dw, const float* go_scale, const float* w_zero,
                      float* grad_x /*[N,C,H,W]*/, float* grad_w /*[O,K]*/,
                      int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
-                     int dh, int dw_, int pad_index, void* stream);
+                     int dh, int dw_, int pad_index, int flags, void* stream);
+/* Device-side error word of the tensor-core backward (host pointer out; synchronises): 1 = a block gave up waiting
+ * for its MMAs and left its tile unwritten.  (No counterpart in the reference.) */
+int atb_tensor_core_status(int* status /*host*/);
 
 /* ---- backward: custom pair tables (256x256) --------------------------------------------------------
  * grad_x[n,k,l] = sum_o dY[n,o,l] * dx_lut[x][w[o,k]]   (approxtorch/backend/csrc/cuda/bgemm_custom_grad_optimize.cu:30-116, 212-257)

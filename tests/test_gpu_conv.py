@@ -249,6 +249,50 @@ def test_lre_backward_im2col_operator(dev):
     _close(gw, rgw.T)
 
 
+@pytest.mark.parametrize("geom", [(4, 70, 20, 20, 150, 3, 1, 1, 1), (3, 40, 17, 19, 130, 3, 2, 1, 1), (2, 200, 9, 9, 260, 1, 1, 0, 1),
+                                  (2, 33, 14, 14, 40, (3, 2), (2, 1), (1, 2), (1, 2))])
+def test_tensor_core_backward_against_fp64_and_the_simt_kernels(dev, geom):
+    """Image-space STE / LRE backward on the tensor cores (three-term bf16 split, fp32 accumulation): several output
+    tiles, a reduction split over the grid, stride classes, ragged edges - against the fp64 oracle at rel 1e-5 and
+    against the fp32 SIMT kernels of the same entry point."""
+    from approxtorch_b200.backend import ops, _C
+    import ctypes
+    B, C, H, W, O, k, s, p, d = geom
+    g4 = (_pair(k), _pair(s), _pair(p), _pair(d))
+    (kh, kw), (sh, sw), (ph, pw), (dh, dw_) = g4
+    rng = np.random.default_rng(97)
+    x8 = rng.integers(-127, 128, (B, C, H, W)).astype(np.int8)
+    widx = rng.integers(0, 256, (O, C * kh * kw), dtype=np.uint8)
+    cols = lo.im2col_index(lo.index_of(x8, True), kh, kw, sh, sw, ph, pw, dh, dw_, 128)
+    go = rng.standard_normal((B, O, cols.shape[2])).astype(np.float32)
+    gs = rng.uniform(0.5, 2.0, O).astype(np.float32)
+    OH, OW = lo.conv_out_hw(H, W, kh, kw, sh, sw, ph, pw, dh, dw_)
+    slopes_x = (rng.standard_normal(256) * 3).astype(np.float32)
+    slopes_w = (rng.standard_normal(256) * 3).astype(np.float32)
+    slopes_w[128] = 777.0                                     # the padded taps' value
+    dec = np.arange(256, dtype=np.float32) - 128
+    for name, tx, tw, exact in (("ste", dec, dec, True), ("lre", slopes_x, slopes_w, False)):
+        g64 = go.astype(np.float64) * gs.astype(np.float64)[None, :, None]
+        rgcols, rgw = lo.lre_backward(g64, cols, widx, tx, tw)
+        rgx = lo.fold(rgcols, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw_)
+        outs = {}
+        for tc in (True, False):
+            ops.TENSOR_CORE_BACKWARD = tc
+            try:
+                gx, gw = ops.lre_conv_backward(_t(go, dev).view(B, O, OH, OW), _t(x8, dev), _t(widx, dev), _t(tx, dev), _t(tw, dev),
+                                               g4, 128, go_scale=_t(gs, dev), exact_tables=exact)
+            finally:
+                ops.TENSOR_CORE_BACKWARD = True
+            _close(gx, rgx)
+            _close(gw, rgw)
+            outs[tc] = (gx, gw)
+        _close(outs[True][0], outs[False][0].double().cpu().numpy())
+        _close(outs[True][1], outs[False][1].double().cpu().numpy())
+    status = ctypes.c_int(-1)
+    torch.cuda.synchronize()
+    assert _C.lib.atb_tensor_core_status(ctypes.byref(status)) == 0 and status.value == 0
+
+
 def _uint8_layer_truth(x, w, bias, lut, sx, zx, sw, zw, geom):
     (kh, kw), (sh, sw_), (ph, pw), (dh, dw_) = geom
     O = w.shape[0]
