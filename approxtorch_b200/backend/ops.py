@@ -281,11 +281,13 @@ TENSOR_CORE_BACKWARD = True   # False: keep the STE / LRE image-space backward o
 
 def lre_conv_backward(go: Tensor, x8: Tensor, w_idx: Tensor | None, dx: Tensor | None, dw: Tensor | None,
                       geom, pad_index: int, go_scale: Tensor | None = None, need_x: bool = True, need_w: bool = True,
-                      w_zero: Tensor | None = None, exact_tables: bool = False):
+                      w_zero: Tensor | None = None, exact_tables: bool = False, x_mask: Tensor | None = None,
+                      x_scale: Tensor | None = None):
     """Image-space STE/LRE backward: (grad wrt the quantised image [B,C,H,W], grad_w [O,K]).
     pad_index 256 selects a 257th entry of ``dw``; ``w_zero[o]`` is subtracted from the mapped weight.
     ``exact_tables``: dx, dw and w_zero hold integers of magnitude <= 256 (the STE decode tables), which the
-    tensor-core path multiplies as single bf16 terms."""
+    tensor-core path multiplies as single bf16 terms.  ``x_mask`` / ``x_scale``: apply the activation's fake-quant
+    backward, (mask ? g : 0) / max(scale, 1e-12), in the store of the image gradient."""
     (kh, kw), (sh, sw), (ph, pw), (dh, dw_) = geom
     B, C, H, W = x8.shape
     go = go.contiguous()
@@ -294,7 +296,8 @@ def lre_conv_backward(go: Tensor, x8: Tensor, w_idx: Tensor | None, dx: Tensor |
     gw = torch.empty((O, C * kh * kw), dtype=torch.float32, device=go.device) if need_w else None
     with _Guard(go):
         _check(_lib.atb_lre_conv_bwd(_ptr(go), _ptr(x8), _DTYPE_CODE[x8.dtype], _ptr(w_idx), _ptr(dx), _ptr(dw),
-                                     _ptr(go_scale), _ptr(w_zero), _ptr(gx), _ptr(gw), B, C, H, W, O, kh, kw, sh, sw, ph, pw,
+                                     _ptr(go_scale), _ptr(w_zero), _ptr(x_mask), _ptr(x_scale), _ptr(gx), _ptr(gw),
+                                     B, C, H, W, O, kh, kw, sh, sw, ph, pw,
                                      dh, dw_, pad_index, (1 if exact_tables else 0) | (0 if TENSOR_CORE_BACKWARD else 2),
                                      _stream(go)), "atb_lre_conv_bwd")
     return gx, gw

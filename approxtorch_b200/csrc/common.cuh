@@ -136,7 +136,8 @@ int pair_forward_launch(const PairFwdParams& p, int mode, cudaStream_t stream);
 int tc_conv_grad_w(const float* go, const void* x, int x_dtype, const float* dw, const float* go_scale, float* grad_w,
                    int N, int O, const ConvGeom& g, int pad_index, bool exact_tables, cudaStream_t s);
 int tc_conv_grad_x(const float* go, const uint8_t* widx, const float* dx, const float* go_scale, const float* w_zero,
-                   float* grad_x, int N, int O, const ConvGeom& g, bool exact_tables, cudaStream_t s);
+                   const uint8_t* x_mask, const float* x_scale, float* grad_x, int N, int O, const ConvGeom& g,
+                   bool exact_tables, cudaStream_t s);
 int tc_status_read(int* status);
 
 inline int grid_for(long long work, int threads, int cap)

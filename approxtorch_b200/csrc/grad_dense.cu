@@ -137,6 +137,7 @@ struct ConvGradX {
     const float* go; const uint8_t* widx; const float* dx; const float* gs; const float* wz; float* gx;
     int Nb, O, K; ConvGeom g;
     FastDiv divHW, divW, divKK, divKW, divSH, divSW;
+    const uint8_t* xmask; const float* xscale;      // optional: fake-quant backward (mask ? v : 0) / max(scale, 1e-12) in the store
     static constexpr bool kAtomic = false, kARFast = false, kBRFast = false;
     __device__ int M() const { return Nb * g.H * g.W; }
     __device__ int N() const { return g.C; }
@@ -172,7 +173,9 @@ struct ConvGradX {
     {
         const unsigned n = fdiv(m, divHW);
         const unsigned hw = m - n * (g.H * g.W);
-        gx[(static_cast<long long>(n) * g.C + c) * (g.H * g.W) + hw] = v;
+        const long long at = (static_cast<long long>(n) * g.C + c) * (g.H * g.W) + hw;
+        if (xmask != nullptr) v = (xmask[at] ? v : 0.0f) / fmaxf(__ldg(xscale), 1e-12f);
+        gx[at] = v;
     }
     // Every thread fetches for ONE image pixel m and ONE input channel c (element e = tid + 256 q has
     // m = m0 + (tid & 127), r = r0 + (tid >> 7) + 2 q), so the pixel's decomposition is done once per block tile
@@ -347,6 +350,7 @@ struct ConvGradXTaps {
     const float* go; const uint8_t* widx; const float* dx; const float* gs; const float* wz; float* gx;
     int Nb, O, K, O8; ConvGeom g;
     FastDiv divSH, divSW;
+    const uint8_t* xmask; const float* xscale;      // optional fake-quant backward in the store
     static constexpr bool kAtomic = false, kARFast = false, kBRFast = false;
     // block state
     int Mc, Hc, Wc, h0, w0, ntaps;
@@ -434,7 +438,9 @@ struct ConvGradXTaps {
     {
         int n, h, w;
         pixel_of(m, n, h, w);
-        gx[((n * g.C + c) * g.H + h) * g.W + w] = v;
+        const int at = ((n * g.C + c) * g.H + h) * g.W + w;
+        if (xmask != nullptr) v = (xmask[at] ? v : 0.0f) / fmaxf(__ldg(xscale), 1e-12f);
+        gx[at] = v;
     }
 };
 
@@ -683,6 +689,7 @@ extern "C" int atb_lre_bwd(const float* go, const void* x, int x_dtype, const vo
 
 extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t* widx,
                                 const float* dx, const float* dw, const float* go_scale, const float* w_zero,
+                                const uint8_t* x_mask, const float* x_scale,
                                 float* grad_x, float* grad_w,
                                 int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
                                 int dh, int dw_, int pad_index, int flags, void* stream)
@@ -690,6 +697,7 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
     ATB_REQUIRE(N >= 0 && C >= 0 && H >= 0 && W >= 0 && O >= 0, "negative dimension");
     ATB_REQUIRE(x_dtype >= 0 && x_dtype <= 2, "bad dtype");
     ATB_REQUIRE(pad_index >= 0 && pad_index <= 256, "pad_index out of range");
+    ATB_REQUIRE((x_mask == nullptr) == (x_scale == nullptr), "x_mask and x_scale go together");
     const bool exact_tables = (flags & 1) != 0;      // dx / dw (and w_zero) hold integers of magnitude <= 256
     const bool simt_only = (flags & 2) != 0;         // keep to the fp32 SIMT kernels
     int OH = 0, OW = 0;
@@ -715,18 +723,18 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
         } else {
             ATB_REQUIRE(go && widx && dx, "null pointer");
             if (lean && !simt_only && sh * sw <= 64 && kh * kw <= 128) {
-                rc = tc_conv_grad_x(go, widx, dx, go_scale, w_zero, grad_x, N, O, g, exact_tables, s);
+                rc = tc_conv_grad_x(go, widx, dx, go_scale, w_zero, x_mask, x_scale, grad_x, N, O, g, exact_tables, s);
                 if (rc != ATB_OK) return rc;
             } else if (lean && sh * sw <= 64) {
                 ConvGradXTaps p{go, widx, dx, go_scale, w_zero, grad_x, N, O, static_cast<int>(K), (O + TK - 1) / TK * TK, g,
-                                make_fastdiv(sh), make_fastdiv(sw)};
+                                make_fastdiv(sh), make_fastdiv(sw), x_mask, x_scale};
                 const long long max_class = static_cast<long long>(N) * ((H + sh - 1) / sh) * ((W + sw - 1) / sw);
                 ATB_REQUIRE(ceil_div(C, 64) <= 65535, "C too large");
                 launch_sgemm(p, max_class, C, sh * sw, s);
             } else {
                 ConvGradX p{go, widx, dx, go_scale, w_zero, grad_x, N, O, static_cast<int>(K), g,
                             make_fastdiv(H * W), make_fastdiv(W), make_fastdiv(kh * kw), make_fastdiv(kw),
-                            make_fastdiv(sh), make_fastdiv(sw)};
+                            make_fastdiv(sh), make_fastdiv(sw), x_mask, x_scale};
                 ATB_REQUIRE(ceil_div(C, 64) <= 65535, "C too large");
                 launch_sgemm(p, Mx, C, 1, s);
             }

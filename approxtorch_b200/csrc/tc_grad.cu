@@ -11,10 +11,13 @@
 // six products hi*hi, hi*mid, mid*hi, mid*mid, hi*lo, lo*hi into one fp32 accumulator; when one operand is exactly
 // representable in bf16 (the STE tables are the integers -128..127, minus an integer zero point) three suffice.
 //
-// Block = 128 x 128 output tile, 512 threads.  Per stage a 32-wide slice of the reduction: thread t produces the 8
-// consecutive reduction elements kg = t / 128 of row t % 128 of A and of B, writes each bf16 split as one 16-byte
-// row of an 8 x 16-byte core matrix (K-major canonical layout without swizzle: k-groups 128 bytes apart, 8-row
-// groups 512 bytes apart), fences the writes for the asynchronous proxy, and after the block barrier thread 0 issues
+// Block = 128 x 128 output tile, 512 threads.  Per stage a 32-wide slice of the reduction: every thread produces
+// eight elements of A and eight of B - the warp's lanes run along whichever axis is contiguous in memory, so each
+// global load is one coalesced segment - and writes their bf16 terms into the K-major canonical layout without
+// swizzle (8-row x 16-byte core matrices, k-groups 144 bytes apart so that a warp's stores fall into different
+// banks, 8-row groups 576 bytes apart).  The raw values of the next slice are loaded right after this slice's have
+// been stored, so their latency runs under the barrier and the MMA issue.  The writes are fenced for the
+// asynchronous proxy, and after the block barrier thread 0 issues
 // the stage's MMAs (two k=16 steps x 3 or 6 products) followed by a commit that arrives on the stage's mbarrier.
 // Two stages: the tensor core works on one while the threads produce the other; a stage is rewritten only after its
 // mbarrier reports the MMAs that read it complete (bounded wait: a block that gives up raises the status word and
@@ -30,11 +33,14 @@ namespace atb {
 
 constexpr int TcM = 128, TcN = 128, TcK = 32;
 constexpr int TcThreads = 512;
-constexpr int TcSplitBytes = 128 * TcK * 2;          // one bf16 split of one operand tile: 8192
-constexpr int TcStageBytes = 6 * TcSplitBytes;       // A hi/mid/lo, B hi/mid/lo: 49152
-constexpr int TcSmemBytes = 2 * TcStageBytes;        // 98304
-constexpr uint32_t TcLBO = 128;                      // bytes between the two 8-element k-groups of a k=16 step
-constexpr uint32_t TcSBO = 128 * (TcK / 8);          // bytes between 8-row groups: 512
+// K-major canonical layout without swizzle: a core matrix is 8 rows x 16 bytes (8 bf16 of the reduction) stored
+// contiguously; the k-groups of a row group lie TcLBO bytes apart and the 8-row groups TcSBO bytes apart.  144 =
+// 128 + 16: the four k-groups a warp writes at once start 36 words apart, i.e. in different banks.
+constexpr uint32_t TcLBO = 144;
+constexpr uint32_t TcSBO = TcLBO * (TcK / 8);        // 576
+constexpr int TcSplitBytes = 16 * TcSBO;             // one bf16 split of one 128-row operand tile: 9216
+constexpr int TcStageBytes = 6 * TcSplitBytes;       // A hi/mid/lo, B hi/mid/lo: 55296
+constexpr int TcSmemBytes = 2 * TcStageBytes;        // 110592
 constexpr int TcMaxTaps = 128;
 
 __device__ int g_tc_status = 0;                      // 1: a block gave up waiting for its MMAs
@@ -84,6 +90,28 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity)
     return false;
 }
 
+// one fp32 value -> three bf16 terms, v = hi + mid + lo exactly
+__device__ __forceinline__ void tc_split1(float v, uint16_t& hi, uint16_t& mid, uint16_t& lo)
+{
+    const __nv_bfloat16 h = __float2bfloat16_rn(v);
+    const float r = v - __bfloat162float(h);
+    const __nv_bfloat16 m = __float2bfloat16_rn(r);
+    const __nv_bfloat16 l = __float2bfloat16_rn(r - __bfloat162float(m));
+    hi = __bfloat16_as_ushort(h); mid = __bfloat16_as_ushort(m); lo = __bfloat16_as_ushort(l);
+}
+// two fp32 values (consecutive reduction elements) -> three words of two bf16
+__device__ __forceinline__ void tc_split2(float a, float b, uint32_t& hi, uint32_t& mid, uint32_t& lo)
+{
+    const __nv_bfloat162 ph = __floats2bfloat162_rn(a, b);
+    hi = *reinterpret_cast<const uint32_t*>(&ph);
+    const float ra = a - __uint_as_float(hi << 16), rb = b - __uint_as_float(hi & 0xffff0000u);
+    const __nv_bfloat162 pm = __floats2bfloat162_rn(ra, rb);
+    mid = *reinterpret_cast<const uint32_t*>(&pm);
+    const float sa = ra - __uint_as_float(mid << 16), sb = rb - __uint_as_float(mid & 0xffff0000u);
+    const __nv_bfloat162 pl = __floats2bfloat162_rn(sa, sb);
+    lo = *reinterpret_cast<const uint32_t*>(&pl);
+}
+
 // eight fp32 values -> three rows of eight bf16 (hi, mid, lo), v = hi + mid + lo exactly
 __device__ __forceinline__ void tc_split8(const float (&v)[8], uint4& hi, uint4& mid, uint4& lo)
 {
@@ -106,67 +134,105 @@ __device__ __forceinline__ void tc_split8(const float (&v)[8], uint4& hi, uint4&
 }
 
 // ---- problem: grad_w ----------------------------------------------------------------------------------------------------
-// C[o, k] = gs[o] * sum_p go[n,o,l] * dw[idx(x[n,c,ih,iw]) or pad];  rows of A: o, rows of B: k = (c,i,j); reduction: p
+// C[o, k] = gs[o] * sum_p go[n,o,l] * dw[idx(x[n,c,ih,iw]) or pad];  rows of A: o, rows of B: k = (c,i,j); reduction: p.
+// Producer mapping: the 32 lanes of a warp are the 32 consecutive pixels of the slice (contiguous in go and, for a
+// stride-1 window, in x), warp w produces rows w, w + 16, ... of both tiles: every global load is one coalesced
+// segment per row, every element is stored as three 2-byte terms.
 template <int XDT>
 struct TcGradW {
     const float* go; const void* x; const float* dw; const float* gs; float* gw;
     int O, K, pad_index, Nb; long long P; ConvGeom g;
     TcFastDiv divL, divOW, divKK, divKW;
     static constexpr bool kAtomic = true;
-    // thread state
-    int o_off, x_koff, k_dh, k_dw;      // o * L (or -1); tap offset from the window origin; tap displacement (k_dh = INT_MIN: no tap)
+    const float* tab;                   // dw (257 entries) in shared memory
+    // thread state: the 8 rows this thread produces (row = warp + 16 i)
+    int o_off[8];                       // o * L, or -1
+    int x_koff[8];                      // tap offset from the window origin
+    int k_dhw[8];                       // (i*DH - PH) << 16 | (j*DW - PW) & 0xffff; INT_MIN: no such tap
+    uint32_t soff[8];                   // byte offset of (row, lane) inside a split tile
     __device__ int M() const { return O; }
     __device__ int N() const { return K; }
     __device__ void setup(int z, int nz, int& rbeg, int& rend)
     {
+        __shared__ float s_tab[257];
+        for (int i = threadIdx.x; i < 257; i += blockDim.x) s_tab[i] = __ldg(dw + (i < 256 || pad_index == 256 ? i : 255));
+        __syncthreads();
+        tab = s_tab;
         const long long per = ((P + nz - 1) / nz + TcK - 1) / TcK * TcK;
         const long long b0 = per * z;
         rbeg = static_cast<int>(b0 < P ? b0 : P);
         rend = static_cast<int>(b0 + per < P ? b0 + per : P);
     }
-    __device__ void prep(int row, int m0, int n0)
+    __device__ void prep(int warp, int lane, int m0, int n0)
     {
         const int L = g.OH * g.OW;
-        const int o = m0 + row;
-        o_off = o < O ? o * L : -1;
-        const int k = n0 + row;
-        k_dh = INT_MIN; k_dw = 0; x_koff = 0;
-        if (k < K) {
-            const unsigned c = tc_div(k, divKK);
-            const unsigned ij = k - c * (g.KH * g.KW);
-            const unsigned i = tc_div(ij, divKW);
-            const unsigned j = ij - i * g.KW;
-            k_dh = static_cast<int>(i) * g.DH - g.PH;
-            k_dw = static_cast<int>(j) * g.DW - g.PW;
-            x_koff = (static_cast<int>(c) * g.H + k_dh) * g.W + k_dw;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int row = warp + 16 * i;
+            const int o = m0 + row;
+            o_off[i] = o < O ? o * L : -1;
+            const int k = n0 + row;
+            k_dhw[i] = INT_MIN; x_koff[i] = 0;
+            if (k < K) {
+                const unsigned c = tc_div(k, divKK);
+                const unsigned ij = k - c * (g.KH * g.KW);
+                const unsigned ti = tc_div(ij, divKW);
+                const unsigned tj = ij - ti * g.KW;
+                const int dh = static_cast<int>(ti) * g.DH - g.PH, dw_ = static_cast<int>(tj) * g.DW - g.PW;
+                k_dhw[i] = (dh << 16) | (dw_ & 0xffff);
+                x_koff[i] = (static_cast<int>(c) * g.H + dh) * g.W + dw_;
+            }
+            soff[i] = static_cast<uint32_t>(row >> 3) * TcSBO + static_cast<uint32_t>(lane >> 3) * TcLBO +
+                      static_cast<uint32_t>(row & 7) * 16u + static_cast<uint32_t>(lane & 7) * 2u;
         }
     }
-    __device__ void fetch(int p0, int rend, float (&va)[8], float (&vb)[8]) const
+    // raw values of the slice starting at reduction index r0: this lane's pixel is r0 + lane
+    __device__ void load(int r0, int rend, int warp, int lane, float (&va)[8], float (&vb)[8]) const
     {
         const int L = g.OH * g.OW;
-        unsigned n = tc_div(p0 < rend ? p0 : 0, divL);
-        int l = (p0 < rend ? p0 : 0) - static_cast<int>(n) * L;
-        int oh = static_cast<int>(tc_div(l, divOW));
-        int ow = l - oh * g.OW;
+        const int p = r0 + lane;
+        const bool live = p < rend;
+        const unsigned n = tc_div(live ? p : 0, divL);
+        const int l = (live ? p : 0) - static_cast<int>(n) * L;
+        const int oh = static_cast<int>(tc_div(l, divOW));
+        const int ow = l - oh * g.OW;
+        const float* go_p = go + static_cast<int>(n) * O * L + l;
+        const int x_p = (static_cast<int>(n) * g.C * g.H + oh * g.SH) * g.W + ow * g.SW;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const bool live = p0 + e < rend;
-            va[e] = (live && o_off >= 0) ? __ldg(go + static_cast<int>(n) * O * L + o_off + l) : 0.0f;
+        for (int i = 0; i < 8; ++i) {
+            va[i] = (live && o_off[i] >= 0) ? __ldg(go_p + o_off[i]) : 0.0f;
             float b = 0.0f;
-            if (live && k_dh != INT_MIN) {
-                const int ih = oh * g.SH + k_dh, iw = ow * g.SW + k_dw;
+            if (live && k_dhw[i] != INT_MIN) {
+                const int ih = oh * g.SH + (k_dhw[i] >> 16), iw = ow * g.SW + static_cast<short>(k_dhw[i] & 0xffff);
                 int idx = pad_index;
                 if (static_cast<unsigned>(ih) < static_cast<unsigned>(g.H) && static_cast<unsigned>(iw) < static_cast<unsigned>(g.W))
-                    idx = index_of<XDT>(x, (static_cast<int>(n) * g.C * g.H + oh * g.SH) * g.W + ow * g.SW + x_koff);
-                b = __ldg(dw + idx);
+                    idx = index_of<XDT>(x, x_p + x_koff[i]);
+                b = tab[idx];
             }
-            vb[e] = b;
-            ++l;
-            if (++ow == g.OW) { ow = 0; ++oh; }
-            if (l == L) { l = 0; oh = 0; ow = 0; ++n; }
+            vb[i] = b;
         }
     }
-    __device__ void store(int o, int k, float v) const
+    template <bool EXACT_B>
+    __device__ void store(uint8_t* stage, const float (&va)[8], const float (&vb)[8]) const
+    {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint16_t hi, mid, lo;
+            tc_split1(va[i], hi, mid, lo);
+            *reinterpret_cast<uint16_t*>(stage + soff[i]) = hi;
+            *reinterpret_cast<uint16_t*>(stage + TcSplitBytes + soff[i]) = mid;
+            *reinterpret_cast<uint16_t*>(stage + 2 * TcSplitBytes + soff[i]) = lo;
+            if (EXACT_B) {
+                *reinterpret_cast<uint16_t*>(stage + 3 * TcSplitBytes + soff[i]) = __bfloat16_as_ushort(__float2bfloat16_rn(vb[i]));
+            } else {
+                tc_split1(vb[i], hi, mid, lo);
+                *reinterpret_cast<uint16_t*>(stage + 3 * TcSplitBytes + soff[i]) = hi;
+                *reinterpret_cast<uint16_t*>(stage + 4 * TcSplitBytes + soff[i]) = mid;
+                *reinterpret_cast<uint16_t*>(stage + 5 * TcSplitBytes + soff[i]) = lo;
+            }
+        }
+    }
+    __device__ void finish(int o, int k, float v) const
     {
         if (gs != nullptr) v *= __ldg(gs + o);
         atomicAdd(gw + o * K + k, v);
@@ -176,22 +242,31 @@ struct TcGradW {
 // ---- problem: grad_x, per stride class, tap-major ---------------------------------------------------------------------------
 // Pixels are grouped by class (a, b) = ((h + PH) % SH, (w + PW) % SW) = blockIdx.z; a class only receives from the
 // taps with (a - i*DH) % SH == 0 and (b - j*DW) % SW == 0.  C[m, c] with m the class's pixels; reduction index
-// r = tap * O8 + o (O8 = O rounded up to 8), so the eight elements a thread produces share one tap.
+// r = tap * O8 + o (O8 = O rounded up to 8).
+// Producer mapping: the 32 lanes of a warp are 32 consecutive rows (pixels of A, contiguous in go; channels of B),
+// warp w produces the two adjacent reduction elements 2w, 2w + 1 of the slice for the four 32-row groups: every go
+// load is one coalesced segment, every store is one 32-bit word holding both elements.
 struct TcGradX {
     const float* go; const uint8_t* widx; const float* dx; const float* gs; const float* wz; float* gx;
     int Nb, O, K, O8; ConvGeom g;
     TcFastDiv divSH, divSW;
+    const uint8_t* xmask; const float* xscale;      // optional: fake-quant backward (mask ? v : 0) / max(scale, 1e-12) in the store
     static constexpr bool kAtomic = false;
     // block state
     int Mc, Hc, Wc, h0, w0, ntaps;
     const int* tap_dh; const int* tap_dw; const int* tap_ij;
-    // thread state
-    int hp, wp, go_n, ckk;
+    const float* tab;                   // dx in shared memory
+    // thread state: four rows (32 rg + lane)
+    int hp[4], wp[4], go_n[4], ckk[4];
+    uint32_t soff[4];
     __device__ int M() const { return Mc; }
     __device__ int N() const { return g.C; }
     __device__ void setup(int z, int, int& rbeg, int& rend)
     {
         __shared__ int s_dh[TcMaxTaps], s_dw[TcMaxTaps], s_ij[TcMaxTaps], s_n;
+        __shared__ float s_tab[256];
+        for (int i = threadIdx.x; i < 256; i += blockDim.x) s_tab[i] = __ldg(dx + i);
+        tab = s_tab;
         const int a = z / g.SW, b = z - a * g.SW;
         h0 = ((a - g.PH) % g.SH + g.SH) % g.SH;
         w0 = ((b - g.PW) % g.SW + g.SW) % g.SW;
@@ -223,62 +298,93 @@ struct TcGradX {
         h = h0 + g.SH * t;
         w = w0 + g.SW * (rem - t * Wc);
     }
-    __device__ void prep(int row, int m0, int n0)
+    __device__ void prep(int warp, int lane, int m0, int n0)
     {
-        const int m = m0 + row;
-        hp = wp = -(1 << 28);
-        go_n = 0;
-        if (m < Mc) {
-            int n, h, w;
-            pixel_of(m, n, h, w);
-            hp = h + g.PH; wp = w + g.PW;
-            go_n = n * O * g.OH * g.OW;
-        }
-        const int c = n0 + row;
-        ckk = c < g.C ? c * (g.KH * g.KW) : -1;
-    }
-    __device__ void fetch(int r0, int rend, float (&va)[8], float (&vb)[8]) const
-    {
-        const bool live = r0 < rend;
-        const int tap = live ? r0 / O8 : 0;
-        const int o0 = r0 - tap * O8;
-        const int th = hp - tap_dh[tap], tw = wp - tap_dw[tap], ij = tap_ij[tap];
-        unsigned oh = th, ow = tw;
-        if (g.SH != 1) oh = tc_div(th < 0 ? 0 : th, divSH);
-        if (g.SW != 1) ow = tc_div(tw < 0 ? 0 : tw, divSW);
-        const bool hit = live && th >= 0 && tw >= 0 && oh < static_cast<unsigned>(g.OH) && ow < static_cast<unsigned>(g.OW);
-        const int a_off = hit ? go_n + static_cast<int>(oh) * g.OW + static_cast<int>(ow) : 0;
-        const int ohw = g.OH * g.OW;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const int o = o0 + e;
-            const bool o_ok = live && o < O;
-            float a = 0.0f;
-            if (hit && o_ok) {
-                a = __ldg(go + a_off + o * ohw);
-                if (gs != nullptr) a *= __ldg(gs + o);
+        for (int rg = 0; rg < 4; ++rg) {
+            const int row = 32 * rg + lane;
+            const int m = m0 + row;
+            hp[rg] = wp[rg] = -(1 << 28);
+            go_n[rg] = 0;
+            if (m < Mc) {
+                int n, h, w;
+                pixel_of(m, n, h, w);
+                hp[rg] = h + g.PH; wp[rg] = w + g.PW;
+                go_n[rg] = n * O * g.OH * g.OW;
             }
-            va[e] = a;
-            float b = 0.0f;
-            if (o_ok && ckk >= 0) {
-                b = __ldg(dx + __ldg(widx + o * K + ckk + ij));
-                if (wz != nullptr) b -= __ldg(wz + o);
-            }
-            vb[e] = b;
+            const int c = n0 + row;
+            ckk[rg] = c < g.C ? c * (g.KH * g.KW) : -1;
+            soff[rg] = static_cast<uint32_t>(row >> 3) * TcSBO + static_cast<uint32_t>((2 * warp) >> 3) * TcLBO +
+                       static_cast<uint32_t>(row & 7) * 16u + static_cast<uint32_t>((2 * warp) & 7) * 2u;
         }
     }
-    __device__ void store(int m, int c, float v) const
+    // slot 2 rg + e: row group rg, reduction element r0 + 2 warp + e
+    __device__ void load(int r0, int rend, int warp, int lane, float (&va)[8], float (&vb)[8]) const
+    {
+        const int r = r0 + 2 * warp;
+        const bool live = r < rend;
+        const int tap = live ? r / O8 : 0;
+        const int o0 = r - tap * O8;
+        const int dh = tap_dh[tap], dw_ = tap_dw[tap], ij = tap_ij[tap];
+        const int ohw = g.OH * g.OW;
+        float sc[2], zz[2];
+        bool o_ok[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            o_ok[e] = live && o0 + e < O;
+            sc[e] = (o_ok[e] && gs != nullptr) ? __ldg(gs + o0 + e) : 1.0f;
+            zz[e] = (o_ok[e] && wz != nullptr) ? __ldg(wz + o0 + e) : 0.0f;
+        }
+#pragma unroll
+        for (int rg = 0; rg < 4; ++rg) {
+            const int th = hp[rg] - dh, tw = wp[rg] - dw_;
+            unsigned oh = th, ow = tw;
+            if (g.SH != 1) oh = tc_div(th < 0 ? 0 : th, divSH);
+            if (g.SW != 1) ow = tc_div(tw < 0 ? 0 : tw, divSW);
+            const bool hit = th >= 0 && tw >= 0 && oh < static_cast<unsigned>(g.OH) && ow < static_cast<unsigned>(g.OW);
+            const int a_off = go_n[rg] + static_cast<int>(oh) * g.OW + static_cast<int>(ow);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                va[2 * rg + e] = (hit && o_ok[e]) ? __ldg(go + a_off + (o0 + e) * ohw) * sc[e] : 0.0f;
+                vb[2 * rg + e] = (o_ok[e] && ckk[rg] >= 0) ? tab[__ldg(widx + (o0 + e) * K + ckk[rg] + ij)] - zz[e] : 0.0f;
+            }
+        }
+    }
+    template <bool EXACT_B>
+    __device__ void store(uint8_t* stage, const float (&va)[8], const float (&vb)[8]) const
+    {
+#pragma unroll
+        for (int rg = 0; rg < 4; ++rg) {
+            uint32_t hi, mid, lo;
+            tc_split2(va[2 * rg], va[2 * rg + 1], hi, mid, lo);
+            *reinterpret_cast<uint32_t*>(stage + soff[rg]) = hi;
+            *reinterpret_cast<uint32_t*>(stage + TcSplitBytes + soff[rg]) = mid;
+            *reinterpret_cast<uint32_t*>(stage + 2 * TcSplitBytes + soff[rg]) = lo;
+            if (EXACT_B) {
+                const __nv_bfloat162 pb = __floats2bfloat162_rn(vb[2 * rg], vb[2 * rg + 1]);
+                *reinterpret_cast<uint32_t*>(stage + 3 * TcSplitBytes + soff[rg]) = *reinterpret_cast<const uint32_t*>(&pb);
+            } else {
+                tc_split2(vb[2 * rg], vb[2 * rg + 1], hi, mid, lo);
+                *reinterpret_cast<uint32_t*>(stage + 3 * TcSplitBytes + soff[rg]) = hi;
+                *reinterpret_cast<uint32_t*>(stage + 4 * TcSplitBytes + soff[rg]) = mid;
+                *reinterpret_cast<uint32_t*>(stage + 5 * TcSplitBytes + soff[rg]) = lo;
+            }
+        }
+    }
+    __device__ void finish(int m, int c, float v) const
     {
         int n, h, w;
         pixel_of(m, n, h, w);
-        gx[((n * g.C + c) * g.H + h) * g.W + w] = v;
+        const int at = ((n * g.C + c) * g.H + h) * g.W + w;
+        if (xmask != nullptr) v = (xmask[at] ? v : 0.0f) / fmaxf(__ldg(xscale), 1e-12f);
+        gx[at] = v;
     }
 };
 
 // ---- the kernel -------------------------------------------------------------------------------------------------------------
 // EXACT_B: operand B is exactly representable in bf16 (only its hi term is produced and multiplied).
 template <class Prob, bool EXACT_B>
-__global__ void __launch_bounds__(TcThreads, 1) tc_gemm_kernel(const Prob prob_in)
+__global__ void __launch_bounds__(TcThreads, 2) tc_gemm_kernel(const Prob prob_in)
 {
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ uint32_t s_tmem;
@@ -291,7 +397,6 @@ __global__ void __launch_bounds__(TcThreads, 1) tc_gemm_kernel(const Prob prob_i
     if (m0 >= M) return;                                  // stride classes differ in size: surplus blocks leave
     if (Prob::kAtomic && rbeg >= rend) return;            // nothing to add
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row = tid & 127, kg = tid >> 7;
     const uint32_t bar0 = static_cast<uint32_t>(__cvta_generic_to_shared(&s_bar[0]));
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0) : "memory");
@@ -309,27 +414,18 @@ __global__ void __launch_bounds__(TcThreads, 1) tc_gemm_kernel(const Prob prob_i
     const uint32_t tmem = s_tmem;
     const uint32_t smem_a = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
 
-    p.prep(row, m0, n0);
-    const uint32_t off = static_cast<uint32_t>(row >> 3) * TcSBO + static_cast<uint32_t>(kg) * TcLBO + static_cast<uint32_t>(row & 7) * 16u;
+    p.prep(warp, lane, m0, n0);
     const int ntiles = (rend - rbeg + TcK - 1) / TcK;
     bool healthy = true;
+    // The raw operand values of the NEXT slice are fetched right after this slice's have been stored, so that their
+    // global-memory latency runs under the barrier, the MMA issue and the wait for the stage to become free.
+    float va[8], vb[8];
+    if (ntiles > 0) p.load(rbeg, rend, warp, lane, va, vb);
     for (int t = 0; t < ntiles; ++t) {
         const int s = t & 1;
         if (t >= 2 && !tc_wait(bar0 + 8 * s, ((t >> 1) - 1) & 1)) healthy = false;     // the MMAs that read this stage are done
-        float va[8], vb[8];
-        p.fetch(rbeg + t * TcK + kg * 8, rend, va, vb);
-        uint8_t* stage = smem + s * TcStageBytes;
-        uint4 hi, mid, lo;
-        tc_split8(va, hi, mid, lo);
-        *reinterpret_cast<uint4*>(stage + off) = hi;
-        *reinterpret_cast<uint4*>(stage + TcSplitBytes + off) = mid;
-        *reinterpret_cast<uint4*>(stage + 2 * TcSplitBytes + off) = lo;
-        tc_split8(vb, hi, mid, lo);
-        *reinterpret_cast<uint4*>(stage + 3 * TcSplitBytes + off) = hi;
-        if (!EXACT_B) {
-            *reinterpret_cast<uint4*>(stage + 4 * TcSplitBytes + off) = mid;
-            *reinterpret_cast<uint4*>(stage + 5 * TcSplitBytes + off) = lo;
-        }
+        p.template store<EXACT_B>(smem + s * TcStageBytes, va, vb);
+        if (t + 1 < ntiles) p.load(rbeg + (t + 1) * TcK, rend, warp, lane, va, vb);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // generic-proxy writes -> visible to the tensor core
         __syncthreads();
         if (tid == 0) {
@@ -377,7 +473,7 @@ __global__ void __launch_bounds__(TcThreads, 1) tc_gemm_kernel(const Prob prob_i
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
                 const int n = n0 + chunk * 32 + j;
-                if (n < N) p.store(m, n, __uint_as_float(r[j]));
+                if (n < N) p.finish(m, n, __uint_as_float(r[j]));
             }
         }
     } else if (ntiles == 0 && !Prob::kAtomic) {
@@ -387,7 +483,7 @@ __global__ void __launch_bounds__(TcThreads, 1) tc_gemm_kernel(const Prob prob_i
         if (m < M)
             for (int j = 0; j < 32; ++j) {
                 const int n = n0 + chunk * 32 + j;
-                if (n < N) p.store(m, n, 0.0f);
+                if (n < N) p.finish(m, n, 0.0f);
             }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -416,10 +512,12 @@ static int tc_launch(const Prob& p, long long M, long long N, unsigned gz, cudaS
     return check_launch("tc_gemm_kernel");
 }
 
+// Slices of the pixel axis per output tile: as many as keep every block resident at once (two blocks per SM), so
+// that no block runs in a second, nearly empty wave.
 static int tc_split_factor(long long tiles, long long P)
 {
-    const int target = 2 * sm_count();
-    long long s = tiles >= target ? 1 : (target + tiles - 1) / tiles;
+    const long long slots = 2LL * sm_count();
+    long long s = tiles >= slots ? 1 : slots / tiles;
     const long long maxs = (P + 8 * TcK - 1) / (8 * TcK);
     if (s > maxs) s = maxs;
     if (s > 1024) s = 1024;
@@ -447,10 +545,12 @@ int tc_conv_grad_w(const float* go, const void* x, int x_dtype, const float* dw,
 }
 
 int tc_conv_grad_x(const float* go, const uint8_t* widx, const float* dx, const float* go_scale, const float* w_zero,
-                   float* grad_x, int N, int O, const ConvGeom& g, bool exact_tables, cudaStream_t s)
+                   const uint8_t* x_mask, const float* x_scale, float* grad_x, int N, int O, const ConvGeom& g,
+                   bool exact_tables, cudaStream_t s)
 {
     const int K = g.C * g.KH * g.KW;
-    TcGradX p{go, widx, dx, go_scale, w_zero, grad_x, N, O, K, (O + 7) / 8 * 8, g, tc_fastdiv(g.SH), tc_fastdiv(g.SW)};
+    TcGradX p{go, widx, dx, go_scale, w_zero, grad_x, N, O, K, (O + 7) / 8 * 8, g, tc_fastdiv(g.SH), tc_fastdiv(g.SW),
+              x_mask, x_scale};
     const long long max_class = static_cast<long long>(N) * ((g.H + g.SH - 1) / g.SH) * ((g.W + g.SW - 1) / g.SW);
     return exact_tables ? tc_launch<TcGradX, true>(p, max_class, g.C, g.SH * g.SW, s)
                         : tc_launch<TcGradX, false>(p, max_class, g.C, g.SH * g.SW, s);

@@ -259,10 +259,10 @@ class _approx_conv2d_int8(Function):
         need_gx, need_gw, need_gb = ctx.needs_input_grad[:3]
         gx = gw = gb = None
         if need_gx or need_gw:
-            gimg, gwq = _ops.lre_conv_backward(go, xq8, widx, dxt, dwt, ctx.g4, _PAD_INDEX, go_scale=alpha,
-                                               need_x=need_gx, need_w=need_gw, exact_tables=ctx.mode != 'lre')
-            if need_gx:
-                gx = torch.ops.approxtorch.fakequant_per_tensor_backward_claude.default(gimg, xmask, scale_x)
+            # the activation's fake-quant backward (mask / scale) is applied in the store of the image gradient
+            gx, gwq = _ops.lre_conv_backward(go, xq8, widx, dxt, dwt, ctx.g4, _PAD_INDEX, go_scale=alpha,
+                                             need_x=need_gx, need_w=need_gw, exact_tables=ctx.mode != 'lre',
+                                             x_mask=xmask if need_gx else None, x_scale=scale_x if need_gx else None)
             if need_gw:
                 s = torch.clamp(scale_w, min=1e-12).view(-1, 1, 1, 1)
                 gw = gwq.view(ctx.wshape) * wmask.to(gwq.dtype) / s

@@ -197,11 +197,15 @@ int atb_lre_bwd(const float* go, const void* x, int x_dtype, const void* w, int 
  * (approxtorch/nn/Conv2d_uint8.py:308-315).
  * Runs on the tensor cores (tcgen05, fp32 operands split into three bf16 terms, fp32 accumulation in TMEM) whenever
  * every tensor is addressable with 32-bit offsets; otherwise on the fp32 SIMT kernels.
+ * x_mask / x_scale (optional, together): the fake-quant backward of the activation is applied in grad_x's store,
+ * grad_x = (x_mask ? g : 0) / max(*x_scale, 1e-12) (fakequant_per_tensor_backward_claude,
+ * approxtorch/backend/csrc/claude/quantization.cu:113-143, without its separate 9-byte-per-element pass).
  * flags: bit 0 = dx, dw and w_zero hold integers of magnitude <= 256 (the STE decode tables): half the tensor-core
  * work; bit 1 = use the SIMT kernels.
  * Replaces the cuDNN convolution_backward calls of approxtorch/nn/bgemm_int8.py:165-212, 259-295. */
 int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t* widx /*[O,K]*/,
                      const float* dx, const float* dw, const float* go_scale, const float* w_zero,
+                     const uint8_t* x_mask /*[N,C,H,W] or NULL*/, const float* x_scale /*scalar or NULL*/,
                      float* grad_x /*[N,C,H,W]*/, float* grad_w /*[O,K]*/,
                      int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
                      int dh, int dw_, int pad_index, int flags, void* stream);
