@@ -163,7 +163,8 @@ def backward_kernels(dev, batch=256, layers=None, mode="ste", tensor_cores=True)
             tot["flop"] += flop * count
     finally:
         ops.TENSOR_CORE_BACKWARD = saved
-    return {"batch": batch, "mode": mode, "path": "tcgen05 (bf16 x3 split, fp32 TMEM accumulator)" if tensor_cores else "fp32 SIMT",
+    return {"batch": batch, "mode": mode,
+            "path": "tcgen05 (bf16 x3 split, fp32 TMEM accumulator)" if tensor_cores else "fp32 SIMT",
             "layers": rows, "total_grad_x_ms": tot["gx_ms"], "total_grad_w_ms": tot["gw_ms"],
             "total_grad_x_tflops": tot["flop"] / tot["gx_ms"] / 1e9, "total_grad_w_tflops": tot["flop"] / tot["gw_ms"] / 1e9,
             "fp32_fma_peak_tflops": 74.4}

@@ -276,7 +276,7 @@ def test_tensor_core_backward_against_fp64_and_the_simt_kernels(dev, geom):
         rgcols, rgw = lo.lre_backward(g64, cols, widx, tx, tw)
         rgx = lo.fold(rgcols, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw_)
         outs = {}
-        for tc in (True, False):
+        for tc in (True, False):                                       # tensor cores, SIMT
             ops.TENSOR_CORE_BACKWARD = tc
             try:
                 gx, gw = ops.lre_conv_backward(_t(go, dev).view(B, O, OH, OW), _t(x8, dev), _t(widx, dev), _t(tx, dev), _t(tw, dev),
