@@ -66,7 +66,8 @@ _SIGNATURES = {
     "atb_lut_map": (_i, [_vp, _i, _vp, _vp, _ll, _vp]),
     "atb_lut_map_pad": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "atb_lre_bwd": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
-    "atb_lre_conv_bwd": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 13 + [_i, _i, _vp]),
+    "atb_lre_conv_bwd": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_i] * 13 + [_i, _i, _vp, _sz, _vp]),
+    "atb_lre_conv_bwd_scratch_bytes": (_sz, [_i] * 16),
     "atb_tensor_core_status": (_i, [ctypes.POINTER(ctypes.c_int)]),
     "atb_pair_table_bytes": (_sz, []),
     "atb_pair_table_prepare": (_i, [_vp, _vp, _vp]),

@@ -277,6 +277,7 @@ def quantize_weight(w: Tensor, scale: Tensor, zero_point: Tensor | None, qmin: i
 
 
 TENSOR_CORE_BACKWARD = True   # False: keep the STE / LRE image-space backward on the fp32 SIMT kernels
+PACKED_BACKWARD = True        # False: the tensor-core backward builds its operands inside the contraction kernels
 
 
 def lre_conv_backward(go: Tensor, x8: Tensor, w_idx: Tensor | None, dx: Tensor | None, dw: Tensor | None,
@@ -294,12 +295,16 @@ def lre_conv_backward(go: Tensor, x8: Tensor, w_idx: Tensor | None, dx: Tensor |
     O = go.shape[1]
     gx = torch.empty((B, C, H, W), dtype=torch.float32, device=go.device) if need_x else None
     gw = torch.empty((O, C * kh * kw), dtype=torch.float32, device=go.device) if need_w else None
+    flags = (1 if exact_tables else 0) | (0 if TENSOR_CORE_BACKWARD else 2) | (0 if PACKED_BACKWARD else 4)
     with _Guard(go):
+        # scratch for the packed bf16 planes of the gradient (0: the problem does not qualify or packing is off)
+        nbytes = int(_lib.atb_lre_conv_bwd_scratch_bytes(B, C, H, W, O, kh, kw, sh, sw, ph, pw, dh, dw_, flags,
+                                                         1 if need_x else 0, 1 if need_w else 0))
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device=go.device) if nbytes else None
         _check(_lib.atb_lre_conv_bwd(_ptr(go), _ptr(x8), _DTYPE_CODE[x8.dtype], _ptr(w_idx), _ptr(dx), _ptr(dw),
                                      _ptr(go_scale), _ptr(w_zero), _ptr(x_mask), _ptr(x_scale), _ptr(gx), _ptr(gw),
                                      B, C, H, W, O, kh, kw, sh, sw, ph, pw,
-                                     dh, dw_, pad_index, (1 if exact_tables else 0) | (0 if TENSOR_CORE_BACKWARD else 2),
-                                     _stream(go)), "atb_lre_conv_bwd")
+                                     dh, dw_, pad_index, flags, _ptr(scratch), nbytes, _stream(go)), "atb_lre_conv_bwd")
     return gx, gw
 
 

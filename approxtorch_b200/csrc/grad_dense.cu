@@ -643,6 +643,17 @@ static int split_factor(long long tiles, long long P)
 
 using namespace atb;
 
+extern "C" size_t atb_lre_conv_bwd_scratch_bytes(int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
+                                                 int dh, int dw_, int flags, int need_x, int need_w)
+{
+    int OH = 0, OW = 0;
+    if (N <= 0 || C <= 0 || O <= 0 || N > 65535 || (flags & 6) != 0 || (!need_x && !need_w)) return 0;
+    if (!conv_out_shape(H, W, kh, kw, sh, sw, ph, pw, dh, dw_, &OH, &OW)) return 0;
+    if (static_cast<long long>(sh) * sw > 64 || static_cast<long long>(kh) * kw > 128) return 0;
+    const ConvGeom g{C, H, W, kh, kw, sh, sw, ph, pw, dh, dw_, OH, OW};
+    return tc_packed_scratch_bytes(N, O, g, need_x != 0, need_w != 0, (flags & 1) != 0);
+}
+
 extern "C" int atb_tensor_core_status(int* status /*host*/)
 {
     ATB_REQUIRE(status != nullptr, "status is null");
@@ -692,7 +703,7 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
                                 const uint8_t* x_mask, const float* x_scale,
                                 float* grad_x, float* grad_w,
                                 int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
-                                int dh, int dw_, int pad_index, int flags, void* stream)
+                                int dh, int dw_, int pad_index, int flags, void* scratch, size_t scratch_bytes, void* stream)
 {
     ATB_REQUIRE(N >= 0 && C >= 0 && H >= 0 && W >= 0 && O >= 0, "negative dimension");
     ATB_REQUIRE(x_dtype >= 0 && x_dtype <= 2, "bad dtype");
@@ -717,6 +728,23 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
     const bool lean = static_cast<long long>(N) * O * OH * OW < 2147483647LL && Mx * C < 2147483647LL &&
                       static_cast<long long>(O) * K < 2147483647LL && kh * kw <= kMaxTaps;
     int rc = ATB_OK;
+    // Operands packed ahead of the contraction when the caller brought enough scratch for it.
+    const bool want_x = grad_x != nullptr && Mx * C > 0, want_w = grad_w != nullptr && O * K > 0;
+    if (lean && !simt_only && (flags & 4) == 0 && scratch != nullptr && O > 0 && P > 0 && N <= 65535 && (want_x || want_w) &&
+        sh * sw <= 64 && kh * kw <= 128) {
+        const size_t need = tc_packed_scratch_bytes(N, O, g, want_x, want_w, exact_tables);
+        if (need > 0 && scratch_bytes >= need) {
+            ATB_REQUIRE(aligned_to(scratch, 16), "scratch must be 16-byte aligned");
+            ATB_REQUIRE(go && (!want_x || (widx && dx)) && (!want_w || (x && dw)), "null pointer");
+            if (want_w) {
+                zero_kernel<<<grid_for(O * K, 256, 4096), 256, 0, s>>>(grad_w, O * K);
+                rc = check_launch("zero_kernel");
+                if (rc != ATB_OK) return rc;
+            }
+            return tc_packed_conv_bwd(go, x, x_dtype, widx, dx, dw, go_scale, w_zero, x_mask, x_scale, want_x ? grad_x : nullptr,
+                                      want_w ? grad_w : nullptr, N, O, g, pad_index, exact_tables, scratch, s);
+        }
+    }
     if (grad_x != nullptr && Mx * C > 0) {
         if (O == 0) {
             zero_kernel<<<grid_for(Mx * C, 256, 4096), 256, 0, s>>>(grad_x, Mx * C);

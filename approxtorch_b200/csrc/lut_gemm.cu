@@ -292,13 +292,15 @@ __device__ __forceinline__ void load_chunk(const GemmArgs& a, const RowCursor& r
             xr[q] = v[4 * q] | (v[4 * q + 1] << 8) | (v[4 * q + 2] << 16) | (v[4 * q + 3] << 24);
     } else if (vec_x) {
         const uint4 v = __ldg(reinterpret_cast<const uint4*>(rc.base + k0));
-        xr[0] = v.x; xr[1] = v.y; xr[2] = v.z; xr[3] = v.w;
+        const uint32_t flip = static_cast<uint32_t>(a.x_xor) * 0x01010101u;      // int8 values -> indices, 4 at a time
+        xr[0] = v.x ^ flip; xr[1] = v.y ^ flip; xr[2] = v.z ^ flip; xr[3] = v.w ^ flip;
     } else {
         xr[0] = xr[1] = xr[2] = xr[3] = 0u;
 #pragma unroll
         for (int kk = 0; kk < kChunk; ++kk) {
             if (k0 + kk < kend) {
-                const uint32_t v = __ldg(rc.base + static_cast<long long>(k0 + kk) * a.L);
+                const uint32_t v = static_cast<uint32_t>(__ldg(rc.base + static_cast<long long>(k0 + kk) * a.L)) ^
+                                   static_cast<uint32_t>(a.x_xor);
                 xr[kk >> 2] |= v << (8 * (kk & 3));
             }
         }
@@ -1106,6 +1108,11 @@ extern "C" int atb_lut_conv2d_fwd(const void* x, int dtype, const uint8_t* w, co
     a.wb_rows = 0; a.w_batch_stride = 0;
     a.image_mode = 1; a.x_xor = (dtype == ATB_I8) ? 0x80 : 0; a.pad_index = pad_index;
     a.g = ConvGeom{C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, OH, OW};
+    if (H == 1 && W == 1 && kh == 1 && kw == 1 && ph == 0 && pw == 0) {
+        // A 1x1 image under a 1x1 kernel is a plain matrix product (a fully connected layer): [N, C] rows that are
+        // contiguous along the reduction, read 16 bytes at a time by the column-mode loader instead of tap by tap.
+        a.image_mode = 0; a.L = 1; a.R = N;
+    }
     a.alpha = alpha; a.beta = beta; a.zero_x = zero_x; a.zero_w = zero_w; a.wsum = wsum;
     return launch_gemm(a, cfg, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
 }

@@ -244,7 +244,8 @@ __device__ __forceinline__ void p_load_chunk(const PairArgs& a, const PRow& rc, 
 #pragma unroll
         for (int kk = 0; kk < PChunk; ++kk) {
             if (k0 + kk < a.K) {
-                const uint32_t v = __ldg(rc.base + static_cast<long long>(k0 + kk) * a.L);
+                const uint32_t v = static_cast<uint32_t>(__ldg(rc.base + static_cast<long long>(k0 + kk) * a.L)) ^
+                                   static_cast<uint32_t>(a.x_xor);
                 xr[kk >> 2] |= v << (8 * (kk & 3));
             }
         }

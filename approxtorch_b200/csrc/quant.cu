@@ -16,6 +16,37 @@ static int stream_grid(long long work_items)
     return grid_for(work_items, kThreads, 16 * sm_count());
 }
 
+// Grid-stride loop over n 16-byte (or 4-byte) vectors with FOUR loads per thread in flight before the first is
+// consumed: a pass that moves one vector per iteration is bound by the load latency at about half of the HBM
+// bandwidth.  The operands are read once, so they are loaded with the streaming (evict-first) hint.
+template <class V, class F>
+__device__ __forceinline__ void stream4(const V* __restrict__ src, long long n, F&& f)
+{
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < n; i += 4 * stride) {
+        const V v0 = __ldcs(src + i), v1 = __ldcs(src + i + stride), v2 = __ldcs(src + i + 2 * stride),
+                v3 = __ldcs(src + i + 3 * stride);
+        f(i, v0); f(i + stride, v1); f(i + 2 * stride, v2); f(i + 3 * stride, v3);
+    }
+    for (; i < n; i += stride) f(i, __ldcs(src + i));
+}
+// the same with a second operand stream read at the same index
+template <class V, class W, class F>
+__device__ __forceinline__ void stream4(const V* __restrict__ src, const W* __restrict__ src2, long long n, F&& f)
+{
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < n; i += 4 * stride) {
+        const V v0 = __ldcs(src + i), v1 = __ldcs(src + i + stride), v2 = __ldcs(src + i + 2 * stride),
+                v3 = __ldcs(src + i + 3 * stride);
+        const W w0 = __ldcs(src2 + i), w1 = __ldcs(src2 + i + stride), w2 = __ldcs(src2 + i + 2 * stride),
+                w3 = __ldcs(src2 + i + 3 * stride);
+        f(i, v0, w0); f(i + stride, v1, w1); f(i + 2 * stride, v2, w2); f(i + 3 * stride, v3, w3);
+    }
+    for (; i < n; i += stride) f(i, __ldcs(src + i), __ldcs(src2 + i));
+}
+
 __device__ __forceinline__ float fq_value(float x, float s, float z, float qmin, float qmax, bool& inside)
 {
     const float v = x / s + z;     // z == 0 for the symmetric form; x/s + 0.0f == x/s bit for bit except -0 -> +0
@@ -38,7 +69,7 @@ __device__ __forceinline__ float fq_value_sym(float x, float s, float qmin, floa
 
 // ---- fp32 q + bool mask (the reference operator's outputs) ----------------------------------
 template <bool VEC, bool ASYM>
-__global__ void fakequant_fwd_kernel(const float* __restrict__ x, const float* __restrict__ scale,
+__global__ void __launch_bounds__(kThreads, 4) fakequant_fwd_kernel(const float* __restrict__ x, const float* __restrict__ scale,
                                      const float* __restrict__ zero, float* __restrict__ q,
                                      uint8_t* __restrict__ mask, long long numel, float qmin, float qmax)
 {
@@ -51,8 +82,7 @@ __global__ void fakequant_fwd_kernel(const float* __restrict__ x, const float* _
         const float4* x4 = reinterpret_cast<const float4*>(x);
         float4* q4 = reinterpret_cast<float4*>(q);
         uchar4* m4 = reinterpret_cast<uchar4*>(mask);
-        for (long long i = t0; i < n4; i += stride) {
-            const float4 v = x4[i];
+        stream4(x4, n4, [&](long long i, const float4 v) {
             bool a, b, c, d;
             float4 r;
             if (ASYM) {
@@ -64,7 +94,7 @@ __global__ void fakequant_fwd_kernel(const float* __restrict__ x, const float* _
             }
             q4[i] = r;
             m4[i] = make_uchar4(a, b, c, d);
-        }
+        });
     }
     for (long long i = (n4 << 2) + t0; i < numel; i += stride) {
         bool a;
@@ -74,7 +104,7 @@ __global__ void fakequant_fwd_kernel(const float* __restrict__ x, const float* _
 }
 
 template <bool VEC>
-__global__ void fakequant_bwd_kernel(const float* __restrict__ go, const uint8_t* __restrict__ mask,
+__global__ void __launch_bounds__(kThreads, 4) fakequant_bwd_kernel(const float* __restrict__ go, const uint8_t* __restrict__ mask,
                                      const float* __restrict__ scale, float* __restrict__ gx, long long numel)
 {
     const float s = fmaxf(__ldg(scale), 1e-12f);
@@ -85,14 +115,12 @@ __global__ void fakequant_bwd_kernel(const float* __restrict__ go, const uint8_t
         const float4* g4 = reinterpret_cast<const float4*>(go);
         const uchar4* m4 = reinterpret_cast<const uchar4*>(mask);
         float4* o4 = reinterpret_cast<float4*>(gx);
-        for (long long i = t0; i < n4; i += stride) {
-            const float4 g = g4[i];
-            const uchar4 m = m4[i];
+        stream4(g4, m4, n4, [&](long long i, const float4 g, const uchar4 m) {
             float4 r;
             r.x = (m.x ? g.x : 0.0f) / s; r.y = (m.y ? g.y : 0.0f) / s;
             r.z = (m.z ? g.z : 0.0f) / s; r.w = (m.w ? g.w : 0.0f) / s;
             o4[i] = r;
-        }
+        });
     }
     for (long long i = (n4 << 2) + t0; i < numel; i += stride) gx[i] = (mask[i] ? go[i] : 0.0f) / s;
 }
@@ -100,7 +128,7 @@ __global__ void fakequant_bwd_kernel(const float* __restrict__ go, const uint8_t
 // ---- fused form: 1-byte quantised image + mask -------------------------------------------------
 // symmetric: int8 value q; asymmetric: uint8 index q (q is already in [0,255])
 template <bool VEC, bool ASYM, bool MASK>
-__global__ void quantize_image_kernel(const float* __restrict__ x, const float* __restrict__ scale,
+__global__ void __launch_bounds__(kThreads, 4) quantize_image_kernel(const float* __restrict__ x, const float* __restrict__ scale,
                                       const float* __restrict__ zero, uint8_t* __restrict__ q8,
                                       uint8_t* __restrict__ mask, long long numel, float qmin, float qmax)
 {
@@ -119,14 +147,13 @@ __global__ void quantize_image_kernel(const float* __restrict__ x, const float* 
         const float4* x4 = reinterpret_cast<const float4*>(x);
         uchar4* o4 = reinterpret_cast<uchar4*>(q8);
         uchar4* m4 = reinterpret_cast<uchar4*>(mask);
-        for (long long i = t0; i < n4; i += stride) {
-            const float4 v = x4[i];
+        stream4(x4, n4, [&](long long i, const float4 v) {
             bool a, b, c, d;
             uchar4 r;
             r.x = one(v.x, a); r.y = one(v.y, b); r.z = one(v.z, c); r.w = one(v.w, d);
             o4[i] = r;
             if (MASK) m4[i] = make_uchar4(a, b, c, d);
-        }
+        });
     }
     for (long long i = (n4 << 2) + t0; i < numel; i += stride) {
         bool a;
@@ -214,10 +241,7 @@ __global__ void stats_kernel(const float* __restrict__ x, long long numel, float
     const long long n4 = VEC ? (numel >> 2) : 0;
     if (VEC) {
         const float4* x4 = reinterpret_cast<const float4*>(x);
-        for (long long i = t0; i < n4; i += stride) {
-            const float4 v = x4[i];
-            take(v.x); take(v.y); take(v.z); take(v.w);
-        }
+        stream4(x4, n4, [&](long long, const float4 v) { take(v.x); take(v.y); take(v.z); take(v.w); });
     }
     for (long long i = (n4 << 2) + t0; i < numel; i += stride) take(x[i]);
     for (int off = 16; off > 0; off >>= 1) {
@@ -248,11 +272,10 @@ __global__ void quantize_u8_kernel(const float* __restrict__ in, uint8_t* __rest
     if (VEC) {
         const float4* in4 = reinterpret_cast<const float4*>(in);
         uchar4* out4 = reinterpret_cast<uchar4*>(out);
-        for (long long i = t0; i < n4; i += stride) {
-            const float4 v = in4[i];
+        stream4(in4, n4, [&](long long i, const float4 v) {
             out4[i] = make_uchar4(index_from_float(v.x, offset), index_from_float(v.y, offset),
                                   index_from_float(v.z, offset), index_from_float(v.w, offset));
-        }
+        });
     }
     for (long long i = (n4 << 2) + t0; i < numel; i += stride) out[i] = index_from_float(in[i], offset);
 }

@@ -163,6 +163,17 @@ def gpu_reference_custom_leg():
     return out
 
 
+def ncu_traffic(kernel):
+    """DRAM bytes (read + write) of one launch of `kernel` on this workload, from the profiler capture whose figures
+    are kept in profiles/ncu_traffic.json (a number measured under the profiler, never during this run); None when
+    the file holds no entry for the kernel."""
+    try:
+        rec = json.load(open(os.path.join(REPO, "profiles", "ncu_traffic.json")))[kernel]
+        return float(rec["dram_bytes_read"]) + float(rec["dram_bytes_write"])
+    except Exception:
+        return None
+
+
 # ----------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -627,6 +638,14 @@ def run_gpu_arm(args):
             extra = resnet50_inference_leg(dev, world, rank, steps=3)
         except Exception as exc:                 # the model leg must never hide the headline number
             extra = {"resnet50_error": f"{type(exc).__name__}: {exc}"[:200]}
+        if world == 1:
+            # every other kernel of the path against its own roofline (streaming passes, tensor-core and custom-pair
+            # backward, fp32-class tables, depthwise, the ResNet-50 conv layers one by one)
+            try:
+                from approxtorch_b200 import kernel_bench
+                extra["kernels"] = kernel_bench.run_all(dev)
+            except Exception as exc:
+                extra["kernels_error"] = f"{type(exc).__name__}: {exc}"[:200]
 
     if rank == 0:
         peaks = {}
@@ -664,14 +683,15 @@ def run_gpu_arm(args):
                          "kernel_ms": gemm_s * 1e3,
                          "kernel_ms_covers": "one atb_lut_bgemm_fwd call = all lookups of the step: one persistent "
                                              "lut_gemm_kernel launch (plus the memset of its arrival counters)",
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM call (its three launches) on
-                         # this workload, from the ncu capture summarised under profiles/
-                         "traffic": 79.3e6,
+                         "traffic": ncu_traffic("lut_gemm_kernel"),
+                         "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of the launch, from the ncu "
+                                         "capture summarised under profiles/ (profiles/ncu_traffic.json)",
                          "hbm": {"algorithmic_bytes": int(alg_bytes), "achieved_gbs": alg_bytes / gemm_s / 1e9,
                                  "peak_gbs": hbm_peak, "frac": alg_bytes / gemm_s / 1e9 / hbm_peak,
                                  "peak_source": "MEASURED_PEAKS.json" if peaks else "fallback"}},
             "cpu_baseline": cpu,
             "gpu_reference": gpu_reference_leg(a_np, b_np, lut_np) if world == 1 and not args.no_models else None,
+            "gpu_reference_custom_backward": gpu_reference_custom_leg() if world == 1 and not args.no_models else None,
             "extra": extra,
         }
         print(json.dumps(line), flush=True)

@@ -201,14 +201,22 @@ int atb_lre_bwd(const float* go, const void* x, int x_dtype, const void* w, int 
  * grad_x = (x_mask ? g : 0) / max(*x_scale, 1e-12) (fakequant_per_tensor_backward_claude,
  * approxtorch/backend/csrc/claude/quantization.cu:113-143, without its separate 9-byte-per-element pass).
  * flags: bit 0 = dx, dw and w_zero hold integers of magnitude <= 256 (the STE decode tables): half the tensor-core
- * work; bit 1 = use the SIMT kernels.
+ * work; bit 1 = use the SIMT kernels; bit 2 = never pack the operands into scratch.
+ * scratch / scratch_bytes: optional device memory of atb_lre_conv_bwd_scratch_bytes() bytes (16-byte aligned).
  * Replaces the cuDNN convolution_backward calls of approxtorch/nn/bgemm_int8.py:165-212, 259-295. */
 int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t* widx /*[O,K]*/,
                      const float* dx, const float* dw, const float* go_scale, const float* w_zero,
                      const uint8_t* x_mask /*[N,C,H,W] or NULL*/, const float* x_scale /*scalar or NULL*/,
                      float* grad_x /*[N,C,H,W]*/, float* grad_w /*[O,K]*/,
                      int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
-                     int dh, int dw_, int pad_index, int flags, void* stream);
+                     int dh, int dw_, int pad_index, int flags, void* scratch, size_t scratch_bytes, void* stream);
+/* Bytes of device scratch with which atb_lre_conv_bwd packs its operands ahead of the contraction (the gradient is
+ * split once into bf16 planes laid out the way grad_x and grad_w read them, so that the operand tiles are filled by
+ * 16-byte asynchronous copies); 0 when the problem does not qualify.  With less scratch than this (or none) the same
+ * call builds the operands inside the contraction kernels: same results to fp32 rounding, slower.
+ * need_x / need_w: which gradients the call will ask for.  (No counterpart in the reference.) */
+size_t atb_lre_conv_bwd_scratch_bytes(int N, int C, int H, int W, int O, int kh, int kw, int sh, int sw, int ph, int pw,
+                                      int dh, int dw_, int flags, int need_x, int need_w);
 /* Device-side error word of the tensor-core backward (host pointer out; synchronises): 1 = a block gave up waiting
  * for its MMAs and left its tile unwritten.  (No counterpart in the reference.) */
 int atb_tensor_core_status(int* status /*host*/);

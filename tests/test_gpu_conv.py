@@ -463,15 +463,16 @@ def test_depthwise_layer(dev):
             _close(layer.bias.grad, go.astype(np.float64).sum(axis=(0, 2, 3)))
 
 
-def test_linear_layer_on_the_lut_gemm(dev):
+@pytest.mark.parametrize("in_f", [70, 64])        # byte-wise rows; rows read 16 bytes at a time (in_f % 16 == 0)
+def test_linear_layer_on_the_lut_gemm(dev, in_f):
     """Fully connected layer: forward equals the exact integer product of the quantised operands under an exact
     table (bit for bit before the fp32 scale), STE gradients equal autograd through the exact surrogate."""
     import approxtorch_b200 as at
     rng = np.random.default_rng(31)
     torch.manual_seed(3)
     lut = lo.lut_exact_signed()
-    layer = at.nn.Linear_int8(70, 33, _t(lut.reshape(-1), dev), bias=True, update_scale=False).to(dev)
-    x = (rng.standard_normal((4, 6, 70)) * 1.5).astype(np.float32)          # leading dims are flattened
+    layer = at.nn.Linear_int8(in_f, 33, _t(lut.reshape(-1), dev), bias=True, update_scale=False).to(dev)
+    x = (rng.standard_normal((4, 6, in_f)) * 1.5).astype(np.float32)          # leading dims are flattened
     with torch.no_grad():
         layer.conv.scale_x.fill_(float(np.abs(x).max() / 127))
     xt = _t(x, dev).requires_grad_(True)
@@ -482,13 +483,13 @@ def test_linear_layer_on_the_lut_gemm(dev):
     ws = layer.weight.detach().clone().requires_grad_(True)
     xq = q.static_quantize_int8(xs, layer.conv.scale_x, -127, 127)
     wq = q.static_quantize_int8(ws, layer.conv.scale_w, -127, 127, ch_axis=0)
-    ysur = (xq.double().reshape(-1, 70) @ wq.double().t()) * (layer.conv.scale_x * layer.conv.scale_w).double() \
+    ysur = (xq.double().reshape(-1, in_f) @ wq.double().t()) * (layer.conv.scale_x * layer.conv.scale_w).double() \
         + layer.bias.double()
     _close(y.reshape(-1, 33), ysur.detach().cpu().numpy())
     go = torch.randn_like(y)
     y.backward(go)
     gxs, gws = torch.autograd.grad(ysur, [xs, ws], go.double().reshape(-1, 33))
     _close(xt.grad, gxs.cpu().numpy().astype(np.float64))
-    _close(layer.conv.weight.grad.view(33, 70), gws.cpu().numpy().astype(np.float64))
+    _close(layer.conv.weight.grad.view(33, in_f), gws.cpu().numpy().astype(np.float64))
     with torch.no_grad():
         assert torch.equal(layer.eval()(_t(x, dev)), y.detach())
