@@ -253,11 +253,33 @@ __global__ void stats_kernel(const float* __restrict__ x, long long numel, float
             mx = (ox > mx || ox != ox) ? ox : mx;
         }
     }
-    if ((threadIdx.x & 31) == 0) {
-        atomicMax(reinterpret_cast<int*>(result), __float_as_int(am));   // |x| >= 0: int order == float order, NaN highest
+    // one atomic per block and statistic: the warps' results meet in shared memory first (thousands of atomics on
+    // the same three words would queue up behind one another at the end of the pass)
+    __shared__ float s_am[32], s_mn[32], s_mx[32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
+    if (lane == 0) { s_am[warp] = am; if (MINMAX) { s_mn[warp] = mn; s_mx[warp] = mx; } }
+    __syncthreads();
+    if (warp == 0) {
+        am = lane < nwarps ? s_am[lane] : 0.0f;
         if (MINMAX) {
-            if (mn != mn) atomic_min_nan(result + 1); else atomic_min_float(result + 1, mn);
-            if (mx != mx) atomic_max_nan(result + 2); else atomic_max_float(result + 2, mx);
+            mn = lane < nwarps ? s_mn[lane] : __int_as_float(0x7f800000);
+            mx = lane < nwarps ? s_mx[lane] : __int_as_float(0xff800000);
+        }
+        for (int off = 16; off > 0; off >>= 1) {
+            const float o = __shfl_down_sync(0xffffffffu, am, off);
+            am = (o > am || o != o) ? o : am;
+            if (MINMAX) {
+                const float on = __shfl_down_sync(0xffffffffu, mn, off), ox = __shfl_down_sync(0xffffffffu, mx, off);
+                mn = (on < mn || on != on) ? on : mn;
+                mx = (ox > mx || ox != ox) ? ox : mx;
+            }
+        }
+        if (lane == 0) {
+            atomicMax(reinterpret_cast<int*>(result), __float_as_int(am));   // |x| >= 0: int order == float order, NaN highest
+            if (MINMAX) {
+                if (mn != mn) atomic_min_nan(result + 1); else atomic_min_float(result + 1, mn);
+                if (mx != mx) atomic_max_nan(result + 2); else atomic_max_float(result + 2, mx);
+            }
         }
     }
 }

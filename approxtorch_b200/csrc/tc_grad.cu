@@ -592,39 +592,69 @@ __device__ __forceinline__ void tc_copy16(uint32_t dst, const void* src, int byt
 }
 
 // ---- the packing pass over the gradient ------------------------------------------------------------------------------------
-// block (32, 8): a tile of 32 pixels x 32 channels of one sample; v = go * gs[o] is split once and written to both planes
-__global__ void tc_pack_go_kernel(const float* __restrict__ go, const float* __restrict__ gs, uint16_t* __restrict__ gx_planes,
-                                  uint16_t* __restrict__ gw_planes, int O, int L, int O32, long long P, long long Ppad)
+// One block = 32 channels x 32 pixels of one sample, 256 threads; v = go * gs[o] is split once and written to both
+// plane sets.  VEC: L % 4 == 0 and 16-byte aligned go, so that a thread reads four consecutive pixels of a channel at
+// once and writes them as one 8-byte piece per term of GW, and - after the turn through shared memory - four
+// consecutive channels of a pixel as one 8-byte piece per term of GX.
+template <bool VEC>
+__global__ void __launch_bounds__(256) tc_pack_go_kernel(const float* __restrict__ go, const float* __restrict__ gs,
+                                                         uint16_t* __restrict__ gx_planes, uint16_t* __restrict__ gw_planes,
+                                                         int O, int L, int O32, long long P, long long Ppad)
 {
-    __shared__ uint16_t tile[3][32][34];
+    __shared__ __align__(8) uint16_t tile[3][32][36];               // [term][pixel][channel], 8-byte aligned rows
     const int l0 = blockIdx.x * 32, o0 = blockIdx.y * 32, n = blockIdx.z;
-    const int tx = threadIdx.x, ty = threadIdx.y;
+    const int t = threadIdx.x;
     const long long gx_plane = P * O32, gw_plane = static_cast<long long>(O) * Ppad;
+    {
+        const int o = o0 + (t >> 3), l = l0 + 4 * (t & 7);
+        float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (o < O) {
+            const float* src = go + (static_cast<long long>(n) * O + o) * L + l;
+            if (VEC) {
+                if (l < L) { const float4 f = __ldcs(reinterpret_cast<const float4*>(src)); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
+            } else {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int o = o0 + ty + 8 * i, l = l0 + tx;
-        uint16_t hi = 0, mid = 0, lo = 0;
-        if (o < O && l < L) {
-            float v = __ldcs(go + (static_cast<long long>(n) * O + o) * L + l);
-            if (gs != nullptr) v *= __ldg(gs + o);
-            tc_split1(v, hi, mid, lo);
-            if (gw_planes != nullptr) {
-                const long long at = o * Ppad + static_cast<long long>(n) * L + l;
-                gw_planes[at] = hi; gw_planes[gw_plane + at] = mid; gw_planes[2 * gw_plane + at] = lo;
+                for (int e = 0; e < 4; ++e) if (l + e < L) v[e] = __ldcs(src + e);
+            }
+            if (gs != nullptr) { const float sc = __ldg(gs + o); v[0] *= sc; v[1] *= sc; v[2] *= sc; v[3] *= sc; }
+        }
+        uint32_t h01, m01, l01, h23, m23, l23;
+        tc_split2(v[0], v[1], h01, m01, l01);
+        tc_split2(v[2], v[3], h23, m23, l23);
+        if (gw_planes != nullptr && o < O && l < L) {
+            const long long at = o * Ppad + static_cast<long long>(n) * L + l;
+            if (VEC) {
+                *reinterpret_cast<uint2*>(gw_planes + at) = make_uint2(h01, h23);
+                *reinterpret_cast<uint2*>(gw_planes + gw_plane + at) = make_uint2(m01, m23);
+                *reinterpret_cast<uint2*>(gw_planes + 2 * gw_plane + at) = make_uint2(l01, l23);
+            } else {
+                const uint32_t hh[2] = {h01, h23}, mm[2] = {m01, m23}, ll[2] = {l01, l23};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (l + e < L) {
+                        gw_planes[at + e] = static_cast<uint16_t>(hh[e >> 1] >> (16 * (e & 1)));
+                        gw_planes[gw_plane + at + e] = static_cast<uint16_t>(mm[e >> 1] >> (16 * (e & 1)));
+                        gw_planes[2 * gw_plane + at + e] = static_cast<uint16_t>(ll[e >> 1] >> (16 * (e & 1)));
+                    }
             }
         }
-        tile[0][ty + 8 * i][tx] = hi; tile[1][ty + 8 * i][tx] = mid; tile[2][ty + 8 * i][tx] = lo;
+        const int oc = t >> 3, lp = 4 * (t & 7);
+        tile[0][lp][oc] = static_cast<uint16_t>(h01); tile[0][lp + 1][oc] = static_cast<uint16_t>(h01 >> 16);
+        tile[0][lp + 2][oc] = static_cast<uint16_t>(h23); tile[0][lp + 3][oc] = static_cast<uint16_t>(h23 >> 16);
+        tile[1][lp][oc] = static_cast<uint16_t>(m01); tile[1][lp + 1][oc] = static_cast<uint16_t>(m01 >> 16);
+        tile[1][lp + 2][oc] = static_cast<uint16_t>(m23); tile[1][lp + 3][oc] = static_cast<uint16_t>(m23 >> 16);
+        tile[2][lp][oc] = static_cast<uint16_t>(l01); tile[2][lp + 1][oc] = static_cast<uint16_t>(l01 >> 16);
+        tile[2][lp + 2][oc] = static_cast<uint16_t>(l23); tile[2][lp + 3][oc] = static_cast<uint16_t>(l23 >> 16);
     }
     if (gx_planes == nullptr) return;
     __syncthreads();
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int l = l0 + ty + 8 * i, o = o0 + tx;             // o < O32 always: O32 is a multiple of 32
+    {
+        const int l = l0 + (t >> 3), oq = 4 * (t & 7);              // four consecutive channels of one pixel: 8 bytes per term
         if (l < L) {
-            const long long at = (static_cast<long long>(n) * L + l) * O32 + o;
-            gx_planes[at] = tile[0][tx][ty + 8 * i];
-            gx_planes[gx_plane + at] = tile[1][tx][ty + 8 * i];
-            gx_planes[2 * gx_plane + at] = tile[2][tx][ty + 8 * i];
+            const long long at = (static_cast<long long>(n) * L + l) * O32 + o0 + oq;
+#pragma unroll
+            for (int term = 0; term < 3; ++term)
+                *reinterpret_cast<uint2*>(gx_planes + term * gx_plane + at) = *reinterpret_cast<const uint2*>(&tile[term][t >> 3][oq]);
         }
     }
 }
@@ -1007,9 +1037,10 @@ int tc_packed_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_
     uint16_t* gwp = need_w ? reinterpret_cast<uint16_t*>(static_cast<char*>(scratch) + z.gx_bytes) : nullptr;
     uint16_t* wt = need_x ? reinterpret_cast<uint16_t*>(static_cast<char*>(scratch) + z.gx_bytes + z.gw_bytes) : nullptr;
     {
-        const dim3 grid(ceil_div(L, 32), z.O32 / 32, N), block(32, 8);
+        const dim3 grid(ceil_div(L, 32), z.O32 / 32, N);
         if (grid.y > 65535 || grid.z > 65535) return fail_invalid("problem too large for the tensor-core backward");
-        tc_pack_go_kernel<<<grid, block, 0, s>>>(go, go_scale, gxp, gwp, O, L, z.O32, z.P, z.Ppad);
+        if (L % 4 == 0 && aligned_to(go, 16)) tc_pack_go_kernel<true><<<grid, 256, 0, s>>>(go, go_scale, gxp, gwp, O, L, z.O32, z.P, z.Ppad);
+        else tc_pack_go_kernel<false><<<grid, 256, 0, s>>>(go, go_scale, gxp, gwp, O, L, z.O32, z.P, z.Ppad);
         int rc = check_launch("tc_pack_go_kernel");
         if (rc != ATB_OK) return rc;
     }

@@ -134,15 +134,15 @@ def stream_kernels(dev, pk=None, mib=256):
 
 
 # ----------------------------------------------------------------------------------------------- dense backward
-def backward_kernels(dev, batch=256, layers=None, mode="ste", tensor_cores=True):
+def backward_kernels(dev, batch=256, layers=None, mode="ste", tensor_cores=True, packed=True):
     """grad_x and grad_w of the image-space STE / LRE backward per layer shape; flop = 2 * B*OH*OW * C*k*k * O (the
     useful fp32-equivalent work, whatever number of bf16 products the tensor-core path spends on it)."""
     layers = layers or RESNET18_CIFAR_LAYERS
     rows, tot = [], {"gx_ms": 0.0, "gw_ms": 0.0, "flop": 0.0}
     table = ops.decode_table(dev, 128) if mode == "ste" else torch.randn(256, device=dev)
     exact = mode == "ste"
-    saved = ops.TENSOR_CORE_BACKWARD
-    ops.TENSOR_CORE_BACKWARD = tensor_cores
+    saved, saved_packed = ops.TENSOR_CORE_BACKWARD, ops.PACKED_BACKWARD
+    ops.TENSOR_CORE_BACKWARD, ops.PACKED_BACKWARD = tensor_cores, packed
     try:
         for (C, H, O, k, s, p, count) in layers:
             x8 = torch.randint(-127, 128, (batch, C, H, H), dtype=torch.int8, device=dev)
@@ -162,9 +162,10 @@ def backward_kernels(dev, batch=256, layers=None, mode="ste", tensor_cores=True)
             tot["gw_ms"] += gw_ms * count
             tot["flop"] += flop * count
     finally:
-        ops.TENSOR_CORE_BACKWARD = saved
+        ops.TENSOR_CORE_BACKWARD, ops.PACKED_BACKWARD = saved, saved_packed
     return {"batch": batch, "mode": mode,
-            "path": "tcgen05 (bf16 x3 split, fp32 TMEM accumulator)" if tensor_cores else "fp32 SIMT",
+            "path": ("tcgen05 (bf16 x3 split, fp32 TMEM accumulator), " + ("operands packed ahead by one pass over the gradient (included in the times)"
+                                                                        if packed else "operands built inside the kernel")) if tensor_cores else "fp32 SIMT",
             "layers": rows, "total_grad_x_ms": tot["gx_ms"], "total_grad_w_ms": tot["gw_ms"],
             "total_grad_x_tflops": tot["flop"] / tot["gx_ms"] / 1e9, "total_grad_w_tflops": tot["flop"] / tot["gw_ms"] / 1e9,
             "fp32_fma_peak_tflops": 74.4}
@@ -350,6 +351,7 @@ def run_all(dev, which=("lds", "stream", "backward", "custom", "fp32", "layers")
             elif name == "backward":
                 out["backward_ste_resnet18_cifar_b256"] = backward_kernels(dev)
                 out["backward_lre_resnet18_cifar_b256"] = backward_kernels(dev, mode="lre")
+                out["backward_ste_resnet18_cifar_b256_operands_in_kernel"] = backward_kernels(dev, packed=False)
                 out["backward_ste_resnet18_cifar_b256_simt"] = backward_kernels(dev, tensor_cores=False)
             elif name == "custom":
                 out["custom"] = custom_kernels(dev, pk)

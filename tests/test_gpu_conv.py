@@ -276,18 +276,21 @@ def test_tensor_core_backward_against_fp64_and_the_simt_kernels(dev, geom):
         rgcols, rgw = lo.lre_backward(g64, cols, widx, tx, tw)
         rgx = lo.fold(rgcols, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw_)
         outs = {}
-        for tc in (True, False):                                       # tensor cores, SIMT
-            ops.TENSOR_CORE_BACKWARD = tc
+        for tc in ("packed", "in-kernel", False):                      # tensor cores (operands packed ahead / built in the kernel), SIMT
+            ops.TENSOR_CORE_BACKWARD = bool(tc)
+            ops.PACKED_BACKWARD = tc == "packed"
             try:
                 gx, gw = ops.lre_conv_backward(_t(go, dev).view(B, O, OH, OW), _t(x8, dev), _t(widx, dev), _t(tx, dev), _t(tw, dev),
                                                g4, 128, go_scale=_t(gs, dev), exact_tables=exact)
             finally:
                 ops.TENSOR_CORE_BACKWARD = True
+                ops.PACKED_BACKWARD = True
             _close(gx, rgx)
             _close(gw, rgw)
             outs[tc] = (gx, gw)
-        _close(outs[True][0], outs[False][0].double().cpu().numpy())
-        _close(outs[True][1], outs[False][1].double().cpu().numpy())
+        for tc in ("packed", "in-kernel"):
+            _close(outs[tc][0], outs[False][0].double().cpu().numpy())
+            _close(outs[tc][1], outs[False][1].double().cpu().numpy())
     status = ctypes.c_int(-1)
     torch.cuda.synchronize()
     assert _C.lib.atb_tensor_core_status(ctypes.byref(status)) == 0 and status.value == 0
