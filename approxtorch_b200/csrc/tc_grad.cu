@@ -560,23 +560,38 @@ int tc_conv_grad_x(const float* go, const uint8_t* widx, const float* dx, const 
 }
 
 // =====================================================================================================================
-// Second form: operands packed ahead of the contraction
+// Second form: operands packed ahead of the contraction, persistent warp-specialised kernel
 // =====================================================================================================================
 // The kernels above rebuild the three bf16 terms of every gradient value once per tap that reads it and store them two
 // bytes at a time: they are bound by the instructions that produce the operands, not by the tensor cores.  When the
 // caller provides scratch memory the gradient is instead split ONCE by a streaming pass into bf16 planes laid out the
 // way each contraction reads them,
-//   GX[term][pixel p = (n, oh, ow)][o]   (o padded to a multiple of 32)     for grad_x: 8 consecutive o = 16 bytes
-//   GW[term][o][p]                       (row pitch a multiple of 8)        for grad_w: 8 consecutive p = 16 bytes
-// and the mapped weights of grad_x into WT[term][tap][c][o]; a 16-byte piece of those planes is exactly one row of a
-// core matrix, so an operand tile is filled by asynchronous 16-byte copies (cp.async, zero fill outside the image)
-// with no arithmetic at all.  Only grad_w's image operand (the table map of the saved 8-bit activations under the
-// window shift) is still produced by the threads, 8 consecutive pixels per thread and slice.
-// Pipeline: STAGES shared-memory stages; in iteration t the block waits for the MMAs of slice t-2 (long finished),
-// refills their stage with slice t+STAGES-2, waits for its own copies of slice t, fences, synchronises, and thread 0
-// issues slice t's MMAs - so the tensor core always has the next slice's MMAs queued behind the running ones.
+//   GX[term][pixel p = (n, oh, ow)][o]   (o padded to a multiple of 64)     for grad_x: 64 consecutive o = one 128-byte row
+//   GW[term][o][p]                       (row pitch a multiple of 8)        for grad_w: 64 consecutive p = one 128-byte row
+// and the mapped weights of grad_x into WT[term][tap][c][o].  A 64-element slice of the reduction is then one
+// 128-byte row per tile row, which is the K-major layout with 128-byte swizzle that tcgen05.mma reads (8-row atoms of
+// 1024 bytes, the 16-byte chunk c of row r stored at chunk c ^ (r & 7)): a warp's asynchronous 16-byte copies
+// (cp.async, zero fill outside the image) read whole 128-byte lines and write whole 128-byte shared-memory rows.
+// Only grad_w's image operand (the table map of the saved 8-bit activations under the window shift) is still
+// produced by the threads, 8 consecutive pixels per item.
+//
+// One block per SM walks over the output tiles (tile t = blockIdx.x + i * gridDim.x).  Roles by warp:
+//   warps 0-3   epilogue: read a finished accumulator out of TMEM (tcgen05.ld) and store / atomically add it;
+//   warp  4     one thread issues the MMAs of a slice as soon as its stage is full, and commits to the stage's
+//               "empty" barrier (and, after a tile's last slice, to the accumulator's "full" barrier);
+//   warps 5-20  producers: wait until a stage is empty, fill it, and - one slice later, when their own copies have
+//               landed and are fenced for the asynchronous proxy - arrive on the stage's "full" barrier.
+// Two accumulators (2 x 128 TMEM columns) let the epilogue of one tile run under the MMAs of the next; no block-wide
+// barrier sits in the loop.  Every wait is bounded: a role that gives up raises a block-wide abort flag (all other
+// waits poll it), the status word is set, and the block leaves through the common exit.
 // grad_w is computed transposed (rows = (c, tap), columns = o) so that rows fill 128-row tiles whatever O is and the
 // atomics of a warp fall on consecutive addresses; N is 64 instead of 128 when the column operand has at most 64 rows.
+
+constexpr int PkK = 64;                              // reduction slice: one 128-byte swizzle row of bf16
+constexpr int PkTermBytes = 128 * 128;               // one bf16 term of one 128-row operand tile
+constexpr int PkEpiWarps = 4, PkProdWarps = 16;
+constexpr int PkThreads = 32 * (PkEpiWarps + 1 + PkProdWarps);     // 672
+// producer thread p (0 .. 511) fills chunk p & 7 of rows p >> 3 and (p >> 3) + 64 of every operand tile
 
 __device__ __forceinline__ void tc_mma_n(uint32_t tmem, uint64_t da, uint64_t db, uint32_t idesc, bool accumulate)
 {
@@ -584,11 +599,33 @@ __device__ __forceinline__ void tc_mma_n(uint32_t tmem, uint64_t da, uint64_t db
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
 }
-
+// K-major operand with 128-byte swizzle: 8-row atoms 1024 bytes apart (the leading-dimension field is unused)
+__device__ __forceinline__ uint64_t tc_desc_sw128(uint32_t saddr)
+{
+    return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(1) << 16) |
+           (static_cast<uint64_t>(1024 >> 4) << 32) | (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
+}
 // 16 bytes global -> shared, asynchronously; `bytes` < 16 zero-fills the rest (0: nothing is read)
 __device__ __forceinline__ void tc_copy16(uint32_t dst, const void* src, int bytes)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tc_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// bounded wait that also gives up when another role of the block has
+__device__ __forceinline__ bool tc_wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+    for (int i = 0; i < (1 << 21); ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((i & 63) == 63 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
 }
 
 // ---- the packing pass over the gradient ------------------------------------------------------------------------------------
@@ -599,12 +636,12 @@ __device__ __forceinline__ void tc_copy16(uint32_t dst, const void* src, int byt
 template <bool VEC>
 __global__ void __launch_bounds__(256) tc_pack_go_kernel(const float* __restrict__ go, const float* __restrict__ gs,
                                                          uint16_t* __restrict__ gx_planes, uint16_t* __restrict__ gw_planes,
-                                                         int O, int L, int O32, long long P, long long Ppad)
+                                                         int O, int L, int Opad, long long P, long long Ppad)
 {
     __shared__ __align__(8) uint16_t tile[3][32][36];               // [term][pixel][channel], 8-byte aligned rows
     const int l0 = blockIdx.x * 32, o0 = blockIdx.y * 32, n = blockIdx.z;
     const int t = threadIdx.x;
-    const long long gx_plane = P * O32, gw_plane = static_cast<long long>(O) * Ppad;
+    const long long gx_plane = P * Opad, gw_plane = static_cast<long long>(O) * Ppad;
     {
         const int o = o0 + (t >> 3), l = l0 + 4 * (t & 7);
         float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -651,7 +688,7 @@ __global__ void __launch_bounds__(256) tc_pack_go_kernel(const float* __restrict
     {
         const int l = l0 + (t >> 3), oq = 4 * (t & 7);              // four consecutive channels of one pixel: 8 bytes per term
         if (l < L) {
-            const long long at = (static_cast<long long>(n) * L + l) * O32 + o0 + oq;
+            const long long at = (static_cast<long long>(n) * L + l) * Opad + o0 + oq;
 #pragma unroll
             for (int term = 0; term < 3; ++term)
                 *reinterpret_cast<uint2*>(gx_planes + term * gx_plane + at) = *reinterpret_cast<const uint2*>(&tile[term][t >> 3][oq]);
@@ -661,13 +698,13 @@ __global__ void __launch_bounds__(256) tc_pack_go_kernel(const float* __restrict
 
 // WT[term][tap][c][o] = split(dx[widx[o, c, tap]] - wz[o]); zero for o >= O.  One thread per (tap, c, o).
 __global__ void tc_pack_w_kernel(const uint8_t* __restrict__ widx, const float* __restrict__ dx, const float* __restrict__ wz,
-                                 uint16_t* __restrict__ wt, int O, int C, int KK, int O32, int terms)
+                                 uint16_t* __restrict__ wt, int O, int C, int KK, int Opad, int terms)
 {
-    const long long total = static_cast<long long>(KK) * C * O32;
+    const long long total = static_cast<long long>(KK) * C * Opad;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int o = static_cast<int>(i % O32);
-        const long long tc = i / O32;
+        const int o = static_cast<int>(i % Opad);
+        const long long tc = i / Opad;
         const int c = static_cast<int>(tc % C), tap = static_cast<int>(tc / C);
         uint16_t hi = 0, mid = 0, lo = 0;
         if (o < O) {
@@ -681,95 +718,130 @@ __global__ void tc_pack_w_kernel(const uint8_t* __restrict__ widx, const float* 
 }
 
 // ---- problem: grad_x from packed planes ----------------------------------------------------------------------------------
-// rows: the pixels of one stride class; columns: c; reduction index r = tap * O32 + o.  Thread t fills the 16-byte
-// piece (row t / 4, k-group t % 4) of every term of both operand tiles.
-struct TcPackedGradX {
+// rows: the pixels of one stride class z; columns: c; reduction index r = tap * Opad + o over the class's taps.
+struct PkGradX {
     const uint16_t* gxp; const uint16_t* wt; float* gx;
-    int Nb, O32; ConvGeom g;
+    int Nb, Opad, classes; ConvGeom g;
     TcFastDiv divSH, divSW;
     const uint8_t* xmask; const float* xscale;
     long long gx_plane, wt_plane;
+    int mt, nt;                                  // tiles along the rows (of the largest class) and along c
     static constexpr bool kAtomic = false;
-    int Mc, Hc, Wc, h0, w0, ntaps;
-    const int* tap_dh; const int* tap_dw; const int* tap_ij;
-    // thread state
-    int hp, wp, c_row; long long pix_base; uint32_t soff;
-    __device__ int M() const { return Mc; }
-    __device__ int N() const { return g.C; }
-    __device__ void setup(int z, int, int& rbeg, int& rend)
+    // block state (shared memory): the taps of every class
+    const int* cls_start; const int* tap_dh; const int* tap_dw; const int* tap_ij;
+    __device__ void block_setup()
     {
-        __shared__ int s_dh[TcMaxTaps], s_dw[TcMaxTaps], s_ij[TcMaxTaps], s_n;
-        const int a = z / g.SW, b = z - a * g.SW;
-        h0 = ((a - g.PH) % g.SH + g.SH) % g.SH;
-        w0 = ((b - g.PW) % g.SW + g.SW) % g.SW;
-        Hc = h0 < g.H ? (g.H - h0 + g.SH - 1) / g.SH : 0;
-        Wc = w0 < g.W ? (g.W - w0 + g.SW - 1) / g.SW : 0;
-        Mc = Nb * Hc * Wc;
+        __shared__ int s_start[65], s_dh[TcMaxTaps], s_dw[TcMaxTaps], s_ij[TcMaxTaps];
         if (threadIdx.x == 0) {
             int n = 0;
-            for (int i = 0; i < g.KH; ++i) {
-                if (((a - i * g.DH) % g.SH + g.SH) % g.SH != 0) continue;
-                for (int j = 0; j < g.KW; ++j) {
-                    if (((b - j * g.DW) % g.SW + g.SW) % g.SW != 0) continue;
-                    s_dh[n] = i * g.DH; s_dw[n] = j * g.DW; s_ij[n] = i * g.KW + j; ++n;
+            for (int z = 0; z < classes; ++z) {
+                s_start[z] = n;
+                const int a = z / g.SW, b = z - a * g.SW;
+                for (int i = 0; i < g.KH; ++i) {
+                    if (((a - i * g.DH) % g.SH + g.SH) % g.SH != 0) continue;
+                    for (int j = 0; j < g.KW; ++j) {
+                        if (((b - j * g.DW) % g.SW + g.SW) % g.SW != 0) continue;
+                        s_dh[n] = i * g.DH; s_dw[n] = j * g.DW; s_ij[n] = i * g.KW + j; ++n;
+                    }
                 }
             }
-            s_n = n;
+            s_start[classes] = n;
         }
-        __syncthreads();
-        ntaps = s_n;
-        tap_dh = s_dh; tap_dw = s_dw; tap_ij = s_ij;
-        rbeg = 0; rend = ntaps * O32;
+        cls_start = s_start; tap_dh = s_dh; tap_dw = s_dw; tap_ij = s_ij;
     }
-    __device__ void pixel_of(int m, int& n, int& h, int& w) const
+    __device__ long long tiles() const { return static_cast<long long>(mt) * nt * classes; }
+    struct Tile { int m0, n0, z, rbeg, rend, M, h0, w0, Hc, Wc; };
+    __device__ Tile tile(long long t, int ncols) const
     {
-        const int hw = Hc * Wc;
+        Tile T;
+        const int per = mt * nt;
+        T.z = static_cast<int>(t / per);
+        const int rem = static_cast<int>(t - static_cast<long long>(T.z) * per);
+        const int ni = rem / mt;
+        T.m0 = (rem - ni * mt) * TcM; T.n0 = ni * ncols;
+        const int a = T.z / g.SW, b = T.z - a * g.SW;
+        T.h0 = ((a - g.PH) % g.SH + g.SH) % g.SH;
+        T.w0 = ((b - g.PW) % g.SW + g.SW) % g.SW;
+        T.Hc = T.h0 < g.H ? (g.H - T.h0 + g.SH - 1) / g.SH : 0;
+        T.Wc = T.w0 < g.W ? (g.W - T.w0 + g.SW - 1) / g.SW : 0;
+        T.M = Nb * T.Hc * T.Wc;
+        T.rbeg = 0; T.rend = (cls_start[T.z + 1] - cls_start[T.z]) * Opad;
+        return T;
+    }
+    __device__ int N() const { return g.C; }
+    __device__ void pixel_of(const Tile& T, int m, int& n, int& h, int& w) const
+    {
+        const int hw = T.Hc * T.Wc;
         n = m / hw;
         const int rem = m - n * hw;
-        const int t = rem / Wc;
-        h = h0 + g.SH * t;
-        w = w0 + g.SW * (rem - t * Wc);
+        const int t = rem / T.Wc;
+        h = T.h0 + g.SH * t;
+        w = T.w0 + g.SW * (rem - t * T.Wc);
     }
-    __device__ void prep(int tid, int m0, int n0)
+    // per-thread producer state of a tile: two rows (row0, row0 + 64)
+    struct Rows { int hp[2], wp[2]; long long pix_base[2]; int c_row[2]; };
+    __device__ Rows rows(const Tile& T, int p) const
     {
-        const int row = tid >> 2, j = tid & 3;
-        const int m = m0 + row;
-        hp = wp = -(1 << 28);
-        pix_base = 0;
-        if (m < Mc) {
-            int n, h, w;
-            pixel_of(m, n, h, w);
-            hp = h + g.PH; wp = w + g.PW;
-            pix_base = static_cast<long long>(n) * g.OH * g.OW;
+        Rows R;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int row = (p >> 3) + 64 * i;
+            const int m = T.m0 + row;
+            R.hp[i] = R.wp[i] = -(1 << 28);
+            R.pix_base[i] = 0;
+            if (m < T.M) {
+                int n, h, w;
+                pixel_of(T, m, n, h, w);
+                R.hp[i] = h + g.PH; R.wp[i] = w + g.PW;
+                R.pix_base[i] = static_cast<long long>(n) * g.OH * g.OW;
+            }
+            R.c_row[i] = T.n0 + row < g.C ? T.n0 + row : -1;
         }
-        c_row = n0 + row < g.C ? n0 + row : -1;
-        soff = static_cast<uint32_t>(row >> 3) * TcSBO + static_cast<uint32_t>(j) * TcLBO + static_cast<uint32_t>(row & 7) * 16u;
+        return R;
     }
     template <int NA, int NB>
-    __device__ void produce(uint32_t stage, int r0, int, int tid, int ncols) const
+    __device__ void produce(uint32_t stage, const Tile& T, const Rows& R, int r0, int p, int ncols) const
     {
-        const int tap = r0 / O32;
-        const int o0 = r0 - tap * O32 + 8 * (tid & 3);
-        const int th = hp - tap_dh[tap], tw = wp - tap_dw[tap];
-        unsigned oh = th, ow = tw;
-        if (g.SH != 1) oh = tc_div(th < 0 ? 0 : th, divSH);
-        if (g.SW != 1) ow = tc_div(tw < 0 ? 0 : tw, divSW);
-        const bool hit = th >= 0 && tw >= 0 && oh < static_cast<unsigned>(g.OH) && ow < static_cast<unsigned>(g.OW);
-        const uint16_t* a = gxp + (hit ? (pix_base + oh * g.OW + ow) * O32 + o0 : 0LL);
+        const int tap_l = r0 / Opad;
+        const int tap = cls_start[T.z] + tap_l;
+        const int o0 = r0 - tap_l * Opad + 8 * (p & 7);
+        const int dh = tap_dh[tap], dw_ = tap_dw[tap];
+        const long long b_tap = static_cast<long long>(tap_ij[tap]) * g.C;
 #pragma unroll
-        for (int t = 0; t < NA; ++t) tc_copy16(stage + t * TcSplitBytes + soff, a + t * gx_plane, hit ? 16 : 0);
-        if ((tid >> 2) < ncols) {
-            const bool ok = c_row >= 0;
-            const uint16_t* b = wt + (ok ? (static_cast<long long>(tap_ij[tap]) * g.C + c_row) * O32 + o0 : 0LL);
+        for (int i = 0; i < 2; ++i) {
+            const int row = (p >> 3) + 64 * i;
+            const uint32_t dst = stage + static_cast<uint32_t>(row) * 128u + static_cast<uint32_t>(((p & 7) ^ (row & 7)) << 4);
+            const int th = R.hp[i] - dh, tw = R.wp[i] - dw_;
+            unsigned oh = th, ow = tw;
+            if (g.SH != 1) oh = tc_div(th < 0 ? 0 : th, divSH);
+            if (g.SW != 1) ow = tc_div(tw < 0 ? 0 : tw, divSW);
+            const bool hit = th >= 0 && tw >= 0 && oh < static_cast<unsigned>(g.OH) && ow < static_cast<unsigned>(g.OW);
+            const uint16_t* a = gxp + (hit ? (R.pix_base[i] + oh * g.OW + ow) * Opad + o0 : 0LL);
 #pragma unroll
-            for (int t = 0; t < NB; ++t) tc_copy16(stage + (NA + t) * TcSplitBytes + soff, b + t * wt_plane, ok ? 16 : 0);
+            for (int t = 0; t < NA; ++t) tc_copy16(dst + t * PkTermBytes, a + t * gx_plane, hit ? 16 : 0);
+            if (row < ncols) {
+                const bool ok = R.c_row[i] >= 0;
+                const uint16_t* b = wt + (ok ? (b_tap + R.c_row[i]) * Opad + o0 : 0LL);
+#pragma unroll
+                for (int t = 0; t < NB; ++t) tc_copy16(dst + (NA + t) * PkTermBytes, b + t * wt_plane, ok ? 16 : 0);
+            }
         }
     }
-    __device__ void finish(int m, int c, float v) const
+    // epilogue state of a thread (its row) and the store of one element
+    struct Out { int base; bool ok; };
+    __device__ Out out_row(const Tile& T, int m) const
     {
-        int n, h, w;
-        pixel_of(m, n, h, w);
-        const int at = ((n * g.C + c) * g.H + h) * g.W + w;
+        Out o{0, m < T.M};
+        if (o.ok) {
+            int n, h, w;
+            pixel_of(T, m, n, h, w);
+            o.base = (n * g.C * g.H + h) * g.W + w;
+        }
+        return o;
+    }
+    __device__ void finish(const Out& o, int c, float v) const
+    {
+        const int at = o.base + c * g.H * g.W;
         if (xmask != nullptr) v = (xmask[at] ? v : 0.0f) / fmaxf(__ldg(xscale), 1e-12f);
         gx[at] = v;
     }
@@ -777,19 +849,16 @@ struct TcPackedGradX {
 
 // ---- problem: grad_w (transposed) from the packed gradient -------------------------------------------------------------------
 // rows: k = (c, tap), produced by the threads from the saved 8-bit image through the table; columns: o, copied from
-// GW; reduction over the pixels p of this block's share.  Result element (k, o) is added to grad_w[o, k].
+// GW; reduction over the pixels of slice z of the pixel axis.  Result element (k, o) is added to grad_w[o, k].
 template <int XDT>
-struct TcPackedGradW {
+struct PkGradW {
     const void* x; const float* dw; const uint16_t* gwp; float* gw;
-    int O, K, pad_index; long long P, Ppad, gw_plane; ConvGeom g;
+    int O, K, pad_index, gz; long long P, Ppad, gw_plane; ConvGeom g;
     TcFastDiv divL, divOW, divKK, divKW;
+    int mt, nt;
     static constexpr bool kAtomic = true;
     const uint16_t* t_hi; const uint16_t* t_mid; const uint16_t* t_lo;      // the table's bf16 terms in shared memory
-    // thread state
-    int k_c, k_dh, k_dw, o_row; uint32_t soff;
-    __device__ int M() const { return K; }
-    __device__ int N() const { return O; }
-    __device__ void setup(int z, int nz, int& rbeg, int& rend)
+    __device__ void block_setup()
     {
         __shared__ uint16_t s_hi[257], s_mid[257], s_lo[257];
         for (int i = threadIdx.x; i < 257; i += blockDim.x) {
@@ -797,99 +866,130 @@ struct TcPackedGradW {
             tc_split1(__ldg(dw + (i < 256 || pad_index == 256 ? i : 255)), hi, mid, lo);
             s_hi[i] = hi; s_mid[i] = mid; s_lo[i] = lo;
         }
-        __syncthreads();
         t_hi = s_hi; t_mid = s_mid; t_lo = s_lo;
-        const long long per = ((P + nz - 1) / nz + TcK - 1) / TcK * TcK;
-        const long long b0 = per * z;
-        rbeg = static_cast<int>(b0 < P ? b0 : P);
-        rend = static_cast<int>(b0 + per < P ? b0 + per : P);
     }
-    __device__ void prep(int tid, int m0, int n0)
+    __device__ long long tiles() const { return static_cast<long long>(mt) * nt * gz; }
+    struct Tile { int m0, n0, z, rbeg, rend, M; };
+    __device__ Tile tile(long long t, int ncols) const
     {
-        const int row = tid >> 2, j = tid & 3;
-        const int k = m0 + row;
-        k_c = -1; k_dh = k_dw = 0;
-        if (k < K) {
-            const unsigned c = tc_div(k, divKK);
-            const unsigned ij = k - c * (g.KH * g.KW);
-            const unsigned ti = tc_div(ij, divKW);
-            k_c = static_cast<int>(c);
-            k_dh = static_cast<int>(ti) * g.DH - g.PH;
-            k_dw = static_cast<int>(ij - ti * g.KW) * g.DW - g.PW;
+        Tile T;
+        const int per = mt * nt;
+        T.z = static_cast<int>(t / per);
+        const int rem = static_cast<int>(t - static_cast<long long>(T.z) * per);
+        const int ni = rem / mt;
+        T.m0 = (rem - ni * mt) * TcM; T.n0 = ni * ncols;
+        T.M = K;
+        const long long per_z = ((P + gz - 1) / gz + PkK - 1) / PkK * PkK;
+        const long long b0 = per_z * T.z;
+        T.rbeg = static_cast<int>(b0 < P ? b0 : P);
+        T.rend = static_cast<int>(b0 + per_z < P ? b0 + per_z : P);
+        return T;
+    }
+    __device__ int N() const { return O; }
+    struct Rows { int k_c[2], k_dh[2], k_dw[2], o_row[2]; };
+    __device__ Rows rows(const Tile& T, int p) const
+    {
+        Rows R;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int row = (p >> 3) + 64 * i;
+            const int k = T.m0 + row;
+            R.k_c[i] = -1; R.k_dh[i] = R.k_dw[i] = 0;
+            if (k < K) {
+                const unsigned c = tc_div(k, divKK);
+                const unsigned ij = k - c * (g.KH * g.KW);
+                const unsigned ti = tc_div(ij, divKW);
+                R.k_c[i] = static_cast<int>(c);
+                R.k_dh[i] = static_cast<int>(ti) * g.DH - g.PH;
+                R.k_dw[i] = static_cast<int>(ij - ti * g.KW) * g.DW - g.PW;
+            }
+            R.o_row[i] = T.n0 + row < O ? T.n0 + row : -1;
         }
-        o_row = n0 + row < O ? n0 + row : -1;
-        soff = static_cast<uint32_t>(row >> 3) * TcSBO + static_cast<uint32_t>(j) * TcLBO + static_cast<uint32_t>(row & 7) * 16u;
+        return R;
     }
     template <int NA, int NB>
-    __device__ void produce(uint32_t stage, int r0, int rend, int tid, int ncols) const
+    __device__ void produce(uint32_t stage, const Tile& T, const Rows& R, int r0, int p, int ncols) const
     {
-        const int p0 = r0 + 8 * (tid & 3);
-        // columns: 16 bytes of each plane of GW (clipped at the end of this block's share)
-        if ((tid >> 2) < ncols) {
-            const int left = rend - p0;
-            const int bytes = (o_row >= 0 && left > 0) ? (left >= 8 ? 16 : 2 * left) : 0;
-            const uint16_t* b = gwp + (bytes > 0 ? o_row * Ppad + p0 : 0LL);
+        const int p0 = r0 + 8 * (p & 7);
+        const int left = T.rend - p0;
+        // where the chunk's first pixel lies (the same for both rows)
+        const int L = g.OH * g.OW;
+        const int pc = left > 0 ? p0 : 0;
+        const unsigned n0 = tc_div(pc, divL);
+        const int l0 = pc - static_cast<int>(n0) * L;
+        const int oh0 = static_cast<int>(tc_div(l0, divOW));
+        const int ow0 = l0 - oh0 * g.OW;
 #pragma unroll
-            for (int t = 0; t < NB; ++t) tc_copy16(stage + (NA + t) * TcSplitBytes + soff, b + t * gw_plane, bytes);
-        }
-        // rows: eight consecutive pixels of tap (k_dh, k_dw) of channel k_c through the table
-        uint32_t hi[4] = {0u, 0u, 0u, 0u}, mid[4] = {0u, 0u, 0u, 0u}, lo[4] = {0u, 0u, 0u, 0u};
-        if (k_c >= 0 && p0 < rend) {
-            const int L = g.OH * g.OW;
-            unsigned n = tc_div(p0, divL);
-            const int l = p0 - static_cast<int>(n) * L;
-            int oh = static_cast<int>(tc_div(l, divOW));
-            int ow = l - oh * g.OW;
+        for (int i = 0; i < 2; ++i) {
+            const int row = (p >> 3) + 64 * i;
+            const uint32_t dst = stage + static_cast<uint32_t>(row) * 128u + static_cast<uint32_t>(((p & 7) ^ (row & 7)) << 4);
+            // columns: 16 bytes of each plane of GW (clipped at the end of this tile's share of the pixels)
+            if (row < ncols) {
+                const int bytes = (R.o_row[i] >= 0 && left > 0) ? (left >= 8 ? 16 : 2 * left) : 0;
+                const uint16_t* b = gwp + (bytes > 0 ? R.o_row[i] * Ppad + p0 : 0LL);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                if (p0 + e < rend) {
-                    const int ih = oh * g.SH + k_dh, iw = ow * g.SW + k_dw;
-                    int idx = pad_index;
-                    if (static_cast<unsigned>(ih) < static_cast<unsigned>(g.H) && static_cast<unsigned>(iw) < static_cast<unsigned>(g.W))
-                        idx = index_of<XDT>(x, ((static_cast<int>(n) * g.C + k_c) * g.H + ih) * g.W + iw);
-                    hi[e >> 1] |= static_cast<uint32_t>(t_hi[idx]) << (16 * (e & 1));
-                    if (NA == 3) {
-                        mid[e >> 1] |= static_cast<uint32_t>(t_mid[idx]) << (16 * (e & 1));
-                        lo[e >> 1] |= static_cast<uint32_t>(t_lo[idx]) << (16 * (e & 1));
+                for (int t = 0; t < NB; ++t) tc_copy16(dst + (NA + t) * PkTermBytes, b + t * gw_plane, bytes);
+            }
+            // rows: eight consecutive pixels of tap (k_dh, k_dw) of channel k_c through the table
+            uint32_t hi[4] = {0u, 0u, 0u, 0u}, mid[4] = {0u, 0u, 0u, 0u}, lo[4] = {0u, 0u, 0u, 0u};
+            if (R.k_c[i] >= 0 && left > 0) {
+                unsigned n = n0;
+                int oh = oh0, ow = ow0;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    if (e < left) {
+                        const int ih = oh * g.SH + R.k_dh[i], iw = ow * g.SW + R.k_dw[i];
+                        int idx = pad_index;
+                        if (static_cast<unsigned>(ih) < static_cast<unsigned>(g.H) && static_cast<unsigned>(iw) < static_cast<unsigned>(g.W))
+                            idx = index_of<XDT>(x, ((static_cast<int>(n) * g.C + R.k_c[i]) * g.H + ih) * g.W + iw);
+                        hi[e >> 1] |= static_cast<uint32_t>(t_hi[idx]) << (16 * (e & 1));
+                        if (NA == 3) {
+                            mid[e >> 1] |= static_cast<uint32_t>(t_mid[idx]) << (16 * (e & 1));
+                            lo[e >> 1] |= static_cast<uint32_t>(t_lo[idx]) << (16 * (e & 1));
+                        }
                     }
+                    if (++ow == g.OW) { ow = 0; if (++oh == g.OH) { oh = 0; ++n; } }
                 }
-                if (++ow == g.OW) { ow = 0; if (++oh == g.OH) { oh = 0; ++n; } }
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
+            if (NA == 3) {
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + PkTermBytes), "r"(mid[0]), "r"(mid[1]), "r"(mid[2]), "r"(mid[3]) : "memory");
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 2 * PkTermBytes), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
             }
         }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + soff), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
-        if (NA == 3) {
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + TcSplitBytes + soff), "r"(mid[0]), "r"(mid[1]), "r"(mid[2]), "r"(mid[3]) : "memory");
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage + 2 * TcSplitBytes + soff), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
-        }
     }
-    __device__ void finish(int k, int o, float v) const { atomicAdd(gw + o * K + k, v); }
+    struct Out { int k; bool ok; };
+    __device__ Out out_row(const Tile& T, int m) const { return Out{m, m < K}; }
+    __device__ void finish(const Out& o, int col, float v) const { atomicAdd(gw + col * K + o.k, v); }
 };
 
 // NA, NB: bf16 terms of the row and of the column operand (3: hi + mid + lo of an fp32 value, 1: exact in bf16);
 // the products (i, j) with i + j <= 2 are issued - lo * mid and smaller fall below fp32 rounding.
 template <class Prob, int NA, int NB, int STAGES>
-__global__ void __launch_bounds__(TcThreads, (NA + NB) * STAGES * TcSplitBytes <= 112 * 1024 ? 2 : 1)
-tc_packed_kernel(const Prob prob_in, const int ncols)
+__global__ void __launch_bounds__(PkThreads, 1) tc_packed_kernel(const Prob prob_in, const int ncols)
 {
-    extern __shared__ __align__(1024) uint8_t smem[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     __shared__ uint32_t s_tmem;
-    __shared__ __align__(8) uint64_t s_bar[STAGES];
-    constexpr int kStage = (NA + NB) * TcSplitBytes;
+    __shared__ int s_abort;
+    __shared__ __align__(8) uint64_t s_full[STAGES], s_empty[STAGES], s_acc_full[2], s_acc_empty[2];
+    constexpr int kStage = (NA + NB) * PkTermBytes;
     Prob p = prob_in;
-    int rbeg, rend;
-    p.setup(blockIdx.z, gridDim.z, rbeg, rend);
-    const int M = p.M(), N = p.N();
-    const int m0 = blockIdx.x * TcM, n0 = blockIdx.y * ncols;
-    if (m0 >= M) return;
-    if (Prob::kAtomic && rbeg >= rend) return;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t bar0 = static_cast<uint32_t>(__cvta_generic_to_shared(&s_bar[0]));
+    p.block_setup();
     if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar0 + 8 * s) : "memory");
+        s_abort = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(&s_full[s]))), "r"(PkProdWarps) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(&s_empty[s]))) : "memory");
+        }
+        for (int a = 0; a < 2; ++a) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(&s_acc_full[a]))) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(&s_acc_empty[a]))), "r"(PkEpiWarps) : "memory");
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 128;"
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 256;"
                      ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(&s_tmem))) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -897,89 +997,146 @@ tc_packed_kernel(const Prob prob_in, const int ncols)
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
-    const uint32_t smem_a = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-    // D fp32, A and B bf16, both K-major, M = 128, N = ncols
-    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((static_cast<uint32_t>(ncols) >> 3) << 17) | ((128u >> 4) << 24);
+    // the dynamic area starts on a 1024-byte boundary of the shared window (the swizzle atoms are address based)
+    const uint32_t smem_a = (static_cast<uint32_t>(__cvta_generic_to_shared(smem_raw)) + 1023u) & ~1023u;
+    const uint32_t full0 = static_cast<uint32_t>(__cvta_generic_to_shared(&s_full[0]));
+    const uint32_t empty0 = static_cast<uint32_t>(__cvta_generic_to_shared(&s_empty[0]));
+    const uint32_t accf0 = static_cast<uint32_t>(__cvta_generic_to_shared(&s_acc_full[0]));
+    const uint32_t acce0 = static_cast<uint32_t>(__cvta_generic_to_shared(&s_acc_empty[0]));
+    volatile int* abort_flag = &s_abort;
+    const long long ntiles = p.tiles();
 
-    p.prep(tid, m0, n0);
-    const int ntiles = (rend - rbeg + TcK - 1) / TcK;
-    bool healthy = true;
-    for (int t = 0; t < STAGES - 2; ++t) {
-        if (t < ntiles) p.template produce<NA, NB>(smem_a + t * kStage, rbeg + t * TcK, rend, tid, ncols);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
-    for (int t = 0; t < ntiles; ++t) {
-        const int tn = t + STAGES - 2;                     // refills the stage of slice t - 2
-        if (tn < ntiles) {
-            if (t >= 2 && !tc_wait(bar0 + 8 * ((t - 2) % STAGES), ((t - 2) / STAGES) & 1)) healthy = false;
-            p.template produce<NA, NB>(smem_a + (tn % STAGES) * kStage, rbeg + tn * TcK, rend, tid, ncols);
+    if (warp >= PkEpiWarps + 1) {
+        // ---------------------------------------------------------------- producers
+        const int pid = tid - 32 * (PkEpiWarps + 1);
+        int stage = 0; uint32_t phase = 0;
+        int pend_stage[STAGES]; int npend = 0;                   // stages filled by this thread and not yet announced
+        bool ok = true;
+        for (long long t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+            const typename Prob::Tile T = p.tile(t, ncols);
+            if (T.m0 >= T.M || (Prob::kAtomic && T.rbeg >= T.rend)) continue;
+            const typename Prob::Rows R = p.rows(T, pid);
+            for (int r0 = T.rbeg; r0 < T.rend; r0 += PkK) {
+                if (!tc_wait_or_abort(empty0 + 8 * stage, phase ^ 1u, abort_flag)) { ok = false; break; }
+                p.template produce<NA, NB>(smem_a + stage * kStage, T, R, r0, pid, ncols);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                pend_stage[npend++] = stage;
+                if (npend == STAGES - 1) {
+                    // the oldest slice: its copies have landed once at most STAGES - 2 newer groups are pending
+                    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) tc_arrive(full0 + 8 * pend_stage[0]);
+#pragma unroll
+                    for (int i = 0; i + 1 < STAGES - 1; ++i) pend_stage[i] = pend_stage[i + 1];
+                    --npend;
+                }
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");     // this thread's copies of slice t have landed
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
-        if (tid == 0) {
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t sa = smem_a + (t % STAGES) * kStage;
+        __syncwarp();
+        for (int i = 0; i < npend; ++i)
+            if (lane == 0) tc_arrive(full0 + 8 * pend_stage[i]);
+    } else if (warp == PkEpiWarps) {
+        // ---------------------------------------------------------------- MMA issue (one thread)
+        if (lane == 0) {
+            // D fp32, A and B bf16, both K-major, M = 128, N = ncols
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((static_cast<uint32_t>(ncols) >> 3) << 17) | ((128u >> 4) << 24);
+            int stage = 0; uint32_t phase = 0;
+            int acc = 0; uint32_t acc_phase = 0;
+            bool ok = true;
+            for (long long t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+                const typename Prob::Tile T = p.tile(t, ncols);
+                if (T.m0 >= T.M || (Prob::kAtomic && T.rbeg >= T.rend)) continue;
+                if (T.rbeg < T.rend) {
+                    if (!tc_wait_or_abort(acce0 + 8 * acc, acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t d = tmem + static_cast<uint32_t>(acc * 128);
+                    bool first = true;
+                    for (int r0 = T.rbeg; r0 < T.rend; r0 += PkK) {
+                        if (!tc_wait_or_abort(full0 + 8 * stage, phase, abort_flag)) { ok = false; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t sa = smem_a + stage * kStage;
 #pragma unroll
-            for (int ks = 0; ks < TcK / 16; ++ks) {
-                const uint32_t kstep = ks * 2 * TcLBO;
-                bool first = (t == 0 && ks == 0);
+                        for (int ks = 0; ks < PkK / 16; ++ks) {
 #pragma unroll
-                for (int i = 0; i < NA; ++i)
+                            for (int i = 0; i < NA; ++i)
 #pragma unroll
-                    for (int j = 0; j < NB; ++j)
-                        if (i + j <= 2) {
-                            tc_mma_n(tmem, tc_desc(sa + i * TcSplitBytes + kstep), tc_desc(sa + (NA + j) * TcSplitBytes + kstep),
-                                     idesc, !first);
-                            first = false;
+                                for (int j = 0; j < NB; ++j)
+                                    if (i + j <= 2) {
+                                        tc_mma_n(d, tc_desc_sw128(sa + i * PkTermBytes + ks * 32), tc_desc_sw128(sa + (NA + j) * PkTermBytes + ks * 32),
+                                                 idesc, !first);
+                                        first = false;
+                                    }
                         }
+                        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                                     ::"r"(empty0 + 8 * stage) : "memory");
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                    }
+                    if (!ok) break;
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                                 ::"r"(accf0 + 8 * acc) : "memory");
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+                }
             }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                         ::"r"(bar0 + 8 * (t % STAGES)) : "memory");
         }
-    }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    // the commit of the last slice covers every MMA issued before it
-    if (ntiles > 0 && !tc_wait(bar0 + 8 * ((ntiles - 1) % STAGES), ((ntiles - 1) / STAGES) & 1)) healthy = false;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (!healthy) atomicExch(&g_tc_status, 1);
-    const int q = warp & 3, chunk = warp >> 2;
-    if (ntiles > 0 && healthy && chunk * 32 < ncols) {
-        uint32_t r[32];
-        const uint32_t taddr = tmem + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(chunk * 32);
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                       "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                       "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                       "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                     : "r"(taddr) : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int m = m0 + q * 32 + lane;
-        if (m < M) {
+    } else {
+        // ---------------------------------------------------------------- epilogue (warp w: TMEM lanes 32 w .. 32 w + 31)
+        int acc = 0; uint32_t acc_phase = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
+            const typename Prob::Tile T = p.tile(t, ncols);
+            if (T.m0 >= T.M || (Prob::kAtomic && T.rbeg >= T.rend)) continue;
+            const typename Prob::Out out = p.out_row(T, T.m0 + warp * 32 + lane);
+            const int N = p.N();
+            if (T.rbeg >= T.rend) {
+                // empty reduction: the tile is zero
+                if (out.ok)
+                    for (int j = 0; j < ncols; ++j)
+                        if (T.n0 + j < N) p.finish(out, T.n0 + j, 0.0f);
+                continue;
+            }
+            if (!tc_wait_or_abort(accf0 + 8 * acc, acc_phase, abort_flag)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int c0 = 0; c0 < ncols; c0 += 32) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(acc * 128 + c0);
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                               "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                               "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                             : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (out.ok) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int n = n0 + chunk * 32 + j;
-                if (n < N) p.finish(m, n, __uint_as_float(r[j]));
+                    for (int j = 0; j < 32; ++j) {
+                        const int n = T.n0 + c0 + j;
+                        if (n < N) p.finish(out, n, __uint_as_float(r[j]));
+                    }
+                }
             }
+            // this warp is done with the accumulator
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc_arrive(acce0 + 8 * acc);
+            if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
         }
-    } else if (ntiles == 0 && !Prob::kAtomic && chunk * 32 < ncols) {
-        const int m = m0 + q * 32 + lane;
-        if (m < M)
-            for (int j = 0; j < 32; ++j) {
-                const int n = n0 + chunk * 32 + j;
-                if (n < N) p.finish(m, n, 0.0f);
-            }
     }
+    // common exit: nothing of this block is in flight any more (every MMA was committed to a barrier somebody waited
+    // on, unless the block aborted), the TMEM columns go back
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 128;" ::"r"(tmem) : "memory");
+    if (tid == 0 && s_abort) atomicExch(&g_tc_status, 1);
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 256;" ::"r"(tmem) : "memory");
 }
 
 template <class Prob, int NA, int NB, int STAGES>
-static int tc_packed_launch(const Prob& p, long long M, long long N, int ncols, unsigned gz, cudaStream_t s)
+static int tc_packed_launch(const Prob& p, long long tiles, int ncols, cudaStream_t s)
 {
-    constexpr int kBytes = (NA + NB) * STAGES * TcSplitBytes;
+    constexpr int kBytes = (NA + NB) * STAGES * PkTermBytes + 1024;       // + room to round the start up to 1024
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -992,9 +1149,10 @@ static int tc_packed_launch(const Prob& p, long long M, long long N, int ncols, 
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
         attr_set[dev] = true;
     }
-    const dim3 grid(ceil_div(M, TcM), ceil_div(N, ncols), gz);
-    if (grid.y > 65535 || grid.z > 65535) return fail_invalid("problem too large for the tensor-core backward");
-    tc_packed_kernel<Prob, NA, NB, STAGES><<<grid, TcThreads, kBytes, s>>>(p, ncols);
+    const long long sms = sm_count();
+    const int grid = static_cast<int>(tiles < sms ? tiles : sms);
+    if (grid <= 0) return ATB_OK;
+    tc_packed_kernel<Prob, NA, NB, STAGES><<<grid, PkThreads, kBytes, s>>>(p, ncols);
     return check_launch("tc_packed_kernel");
 }
 
@@ -1002,17 +1160,17 @@ static size_t tc_round256(size_t b) { return (b + 255u) / 256u * 256u; }
 
 // Scratch layout: GX planes | GW planes | WT planes, each 256-byte aligned.
 struct TcPackedSizes {
-    int O32; long long P, Ppad; size_t gx_bytes, gw_bytes, wt_bytes;
+    int Opad; long long P, Ppad; size_t gx_bytes, gw_bytes, wt_bytes;
 };
 static TcPackedSizes tc_packed_sizes(int N, int O, const ConvGeom& g, bool need_x, bool need_w, bool exact_tables)
 {
     TcPackedSizes z{};
-    z.O32 = (O + 31) / 32 * 32;
+    z.Opad = (O + PkK - 1) / PkK * PkK;
     z.P = static_cast<long long>(N) * g.OH * g.OW;
     z.Ppad = (z.P + 7) / 8 * 8;
-    z.gx_bytes = need_x ? tc_round256(static_cast<size_t>(3) * z.P * z.O32 * 2u) : 0u;
+    z.gx_bytes = need_x ? tc_round256(static_cast<size_t>(3) * z.P * z.Opad * 2u) : 0u;
     z.gw_bytes = need_w ? tc_round256(static_cast<size_t>(3) * O * z.Ppad * 2u) : 0u;
-    z.wt_bytes = need_x ? tc_round256(static_cast<size_t>(exact_tables ? 1 : 3) * g.KH * g.KW * g.C * z.O32 * 2u) : 0u;
+    z.wt_bytes = need_x ? tc_round256(static_cast<size_t>(exact_tables ? 1 : 3) * g.KH * g.KW * g.C * z.Opad * 2u) : 0u;
     return z;
 }
 
@@ -1020,7 +1178,7 @@ size_t tc_packed_scratch_bytes(int N, int O, const ConvGeom& g, bool need_x, boo
 {
     const TcPackedSizes z = tc_packed_sizes(N, O, g, need_x, need_w, exact_tables);
     // 32-bit element offsets inside a plane: larger problems stay on the kernels that build their operands in place
-    if (z.P * z.O32 >= 2147483647LL || static_cast<long long>(O) * z.Ppad >= 2147483647LL) return 0;
+    if (z.P * z.Opad >= 2147483647LL || static_cast<long long>(O) * z.Ppad >= 2147483647LL) return 0;
     return z.gx_bytes + z.gw_bytes + z.wt_bytes;
 }
 
@@ -1037,46 +1195,49 @@ int tc_packed_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_
     uint16_t* gwp = need_w ? reinterpret_cast<uint16_t*>(static_cast<char*>(scratch) + z.gx_bytes) : nullptr;
     uint16_t* wt = need_x ? reinterpret_cast<uint16_t*>(static_cast<char*>(scratch) + z.gx_bytes + z.gw_bytes) : nullptr;
     {
-        const dim3 grid(ceil_div(L, 32), z.O32 / 32, N);
+        const dim3 grid(ceil_div(L, 32), z.Opad / 32, N);
         if (grid.y > 65535 || grid.z > 65535) return fail_invalid("problem too large for the tensor-core backward");
-        if (L % 4 == 0 && aligned_to(go, 16)) tc_pack_go_kernel<true><<<grid, 256, 0, s>>>(go, go_scale, gxp, gwp, O, L, z.O32, z.P, z.Ppad);
-        else tc_pack_go_kernel<false><<<grid, 256, 0, s>>>(go, go_scale, gxp, gwp, O, L, z.O32, z.P, z.Ppad);
+        if (L % 4 == 0 && aligned_to(go, 16)) tc_pack_go_kernel<true><<<grid, 256, 0, s>>>(go, go_scale, gxp, gwp, O, L, z.Opad, z.P, z.Ppad);
+        else tc_pack_go_kernel<false><<<grid, 256, 0, s>>>(go, go_scale, gxp, gwp, O, L, z.Opad, z.P, z.Ppad);
         int rc = check_launch("tc_pack_go_kernel");
         if (rc != ATB_OK) return rc;
     }
     if (need_x) {
         const int terms = exact_tables ? 1 : 3;
-        const long long total = static_cast<long long>(KK) * g.C * z.O32;
-        tc_pack_w_kernel<<<grid_for(total, 256, 4096), 256, 0, s>>>(widx, dx, w_zero, wt, O, g.C, KK, z.O32, terms);
+        const long long total = static_cast<long long>(KK) * g.C * z.Opad;
+        tc_pack_w_kernel<<<grid_for(total, 256, 4096), 256, 0, s>>>(widx, dx, w_zero, wt, O, g.C, KK, z.Opad, terms);
         int rc = check_launch("tc_pack_w_kernel");
         if (rc != ATB_OK) return rc;
-        TcPackedGradX p{};
-        p.gxp = gxp; p.wt = wt; p.gx = grad_x; p.Nb = N; p.O32 = z.O32; p.g = g;
-        p.divSH = tc_fastdiv(g.SH); p.divSW = tc_fastdiv(g.SW); p.xmask = x_mask; p.xscale = x_scale;
-        p.gx_plane = z.P * z.O32; p.wt_plane = total;
-        const long long max_class = static_cast<long long>(N) * ((g.H + g.SH - 1) / g.SH) * ((g.W + g.SW - 1) / g.SW);
         const int ncols = g.C <= 64 ? 64 : 128;
-        rc = exact_tables ? tc_packed_launch<TcPackedGradX, 3, 1, 3>(p, max_class, g.C, ncols, g.SH * g.SW, s)
-                          : tc_packed_launch<TcPackedGradX, 3, 3, 4>(p, max_class, g.C, ncols, g.SH * g.SW, s);
+        PkGradX p{};
+        p.gxp = gxp; p.wt = wt; p.gx = grad_x; p.Nb = N; p.Opad = z.Opad; p.classes = g.SH * g.SW; p.g = g;
+        p.divSH = tc_fastdiv(g.SH); p.divSW = tc_fastdiv(g.SW); p.xmask = x_mask; p.xscale = x_scale;
+        p.gx_plane = z.P * z.Opad; p.wt_plane = total;
+        const long long max_class = static_cast<long long>(N) * ((g.H + g.SH - 1) / g.SH) * ((g.W + g.SW - 1) / g.SW);
+        p.mt = ceil_div(max_class, TcM); p.nt = ceil_div(g.C, ncols);
+        const long long tiles = static_cast<long long>(p.mt) * p.nt * p.classes;
+        rc = exact_tables ? tc_packed_launch<PkGradX, 3, 1, 3>(p, tiles, ncols, s) : tc_packed_launch<PkGradX, 3, 3, 2>(p, tiles, ncols, s);
         if (rc != ATB_OK) return rc;
     }
     if (need_w) {
         const int ncols = O <= 64 ? 64 : 128;
-        const long long tiles = static_cast<long long>(ceil_div(K, TcM)) * ceil_div(O, ncols);
-        const long long slots = (exact_tables ? 2LL : 1LL) * sm_count();
-        long long gz = tiles >= slots ? 1 : slots / tiles;
-        const long long maxs = (z.P + 8 * TcK - 1) / (8 * TcK);
+        const int mt = ceil_div(K, TcM), nt = ceil_div(O, ncols);
+        // slices of the pixel axis: about two tiles per SM, none shorter than eight 64-pixel steps
+        const long long tiles_mn = static_cast<long long>(mt) * nt;
+        long long gz = (2LL * sm_count() + tiles_mn - 1) / tiles_mn;
+        const long long maxs = (z.P + 8 * PkK - 1) / (8 * PkK);
         if (gz > maxs) gz = maxs;
-        if (gz > 1024) gz = 1024;
+        if (gz > 4096) gz = 4096;
         if (gz < 1) gz = 1;
 #define ATB_TC_PW(DT)                                                                                                     \
     {                                                                                                                     \
-        TcPackedGradW<DT> p{};                                                                                            \
-        p.x = x; p.dw = dw; p.gwp = gwp; p.gw = grad_w; p.O = O; p.K = K; p.pad_index = pad_index;                        \
+        PkGradW<DT> p{};                                                                                                  \
+        p.x = x; p.dw = dw; p.gwp = gwp; p.gw = grad_w; p.O = O; p.K = K; p.pad_index = pad_index; p.gz = static_cast<int>(gz); \
         p.P = z.P; p.Ppad = z.Ppad; p.gw_plane = static_cast<long long>(O) * z.Ppad; p.g = g;                             \
         p.divL = tc_fastdiv(L); p.divOW = tc_fastdiv(g.OW); p.divKK = tc_fastdiv(KK); p.divKW = tc_fastdiv(g.KW);          \
-        return exact_tables ? tc_packed_launch<TcPackedGradW<DT>, 1, 3, 3>(p, K, O, ncols, static_cast<unsigned>(gz), s)  \
-                            : tc_packed_launch<TcPackedGradW<DT>, 3, 3, 4>(p, K, O, ncols, static_cast<unsigned>(gz), s); \
+        p.mt = mt; p.nt = nt;                                                                                             \
+        return exact_tables ? tc_packed_launch<PkGradW<DT>, 1, 3, 3>(p, tiles_mn * gz, ncols, s)                          \
+                            : tc_packed_launch<PkGradW<DT>, 3, 3, 2>(p, tiles_mn * gz, ncols, s);                          \
     }
         if (x_dtype == ATB_U8) ATB_TC_PW(ATB_U8)
         if (x_dtype == ATB_I8) ATB_TC_PW(ATB_I8)
