@@ -854,8 +854,8 @@ template <int XDT>
 struct PkGradW {
     const void* x; const float* dw; const uint16_t* gwp; float* gw;
     int O, K, pad_index, gz; long long P, Ppad, gw_plane; ConvGeom g;
-    TcFastDiv divL, divOW, divKK, divKW;
-    int mt, nt;
+    TcFastDiv divL, divOW, divKK, divKW, divKH;
+    int mt, nt, window;
     static constexpr bool kAtomic = true;
     const uint16_t* t_hi; const uint16_t* t_mid; const uint16_t* t_lo;      // the table's bf16 terms in shared memory
     __device__ void block_setup()
@@ -886,7 +886,11 @@ struct PkGradW {
         return T;
     }
     __device__ int N() const { return O; }
-    struct Rows { int k_c[2], k_dh[2], k_dw[2], o_row[2]; };
+    // per-thread producer state of a tile.  Generic mapping: two rows (row0, row0 + 64), one 8-pixel chunk each.
+    // Window mapping (stride and dilation 1 along w, 2 or 3 taps per kernel row): thread p owns the KW rows of
+    // group (c, i) number p >> 3 of the tile and one chunk - the taps of a kernel row read the same stretch of the
+    // image shifted by one, so 8 + KW - 1 table lookups feed 8 * KW elements.
+    struct Rows { int k_c[2], k_dh[2], k_dw[2], o_row[2]; int w_c, w_dh, w_row0; };
     __device__ Rows rows(const Tile& T, int p) const
     {
         Rows R;
@@ -905,14 +909,54 @@ struct PkGradW {
             }
             R.o_row[i] = T.n0 + row < O ? T.n0 + row : -1;
         }
+        R.w_c = -1; R.w_dh = 0; R.w_row0 = 0;
+        if (window) {
+            const int grp = static_cast<int>(tc_div(T.m0, divKW)) + (p >> 3);          // (c, i) pair number
+            const int k0 = grp * g.KW;
+            if (k0 < T.m0 + TcM && k0 < K) {
+                const unsigned c = tc_div(grp, divKH);
+                R.w_c = static_cast<int>(c);
+                R.w_dh = (grp - static_cast<int>(c) * g.KH) * g.DH - g.PH;
+                R.w_row0 = k0 - T.m0;                                                   // may be negative: rows of the tile before
+            }
+        }
         return R;
+    }
+    // eight consecutive pixels of tap (kdh, kdw) of channel kc through the table, into chunk `dst` of the row's terms
+    template <int NA>
+    __device__ void row_generic(uint32_t dst, int kc, int kdh, int kdw, unsigned n, int oh, int ow, int left) const
+    {
+        uint32_t hi[4] = {0u, 0u, 0u, 0u}, mid[4] = {0u, 0u, 0u, 0u}, lo[4] = {0u, 0u, 0u, 0u};
+        if (kc >= 0 && left > 0) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                if (e < left) {
+                    const int ih = oh * g.SH + kdh, iw = ow * g.SW + kdw;
+                    int idx = pad_index;
+                    if (static_cast<unsigned>(ih) < static_cast<unsigned>(g.H) && static_cast<unsigned>(iw) < static_cast<unsigned>(g.W))
+                        idx = index_of<XDT>(x, ((static_cast<int>(n) * g.C + kc) * g.H + ih) * g.W + iw);
+                    hi[e >> 1] |= static_cast<uint32_t>(t_hi[idx]) << (16 * (e & 1));
+                    if (NA == 3) {
+                        mid[e >> 1] |= static_cast<uint32_t>(t_mid[idx]) << (16 * (e & 1));
+                        lo[e >> 1] |= static_cast<uint32_t>(t_lo[idx]) << (16 * (e & 1));
+                    }
+                }
+                if (++ow == g.OW) { ow = 0; if (++oh == g.OH) { oh = 0; ++n; } }
+            }
+        }
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
+        if (NA == 3) {
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + PkTermBytes), "r"(mid[0]), "r"(mid[1]), "r"(mid[2]), "r"(mid[3]) : "memory");
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 2 * PkTermBytes), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
+        }
     }
     template <int NA, int NB>
     __device__ void produce(uint32_t stage, const Tile& T, const Rows& R, int r0, int p, int ncols) const
     {
-        const int p0 = r0 + 8 * (p & 7);
+        const int chunk = p & 7;
+        const int p0 = r0 + 8 * chunk;
         const int left = T.rend - p0;
-        // where the chunk's first pixel lies (the same for both rows)
+        // where the chunk's first pixel lies
         const int L = g.OH * g.OW;
         const int pc = left > 0 ? p0 : 0;
         const unsigned n0 = tc_div(pc, divL);
@@ -922,7 +966,7 @@ struct PkGradW {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int row = (p >> 3) + 64 * i;
-            const uint32_t dst = stage + static_cast<uint32_t>(row) * 128u + static_cast<uint32_t>(((p & 7) ^ (row & 7)) << 4);
+            const uint32_t dst = stage + static_cast<uint32_t>(row) * 128u + static_cast<uint32_t>((chunk ^ (row & 7)) << 4);
             // columns: 16 bytes of each plane of GW (clipped at the end of this tile's share of the pixels)
             if (row < ncols) {
                 const int bytes = (R.o_row[i] >= 0 && left > 0) ? (left >= 8 ? 16 : 2 * left) : 0;
@@ -930,31 +974,51 @@ struct PkGradW {
 #pragma unroll
                 for (int t = 0; t < NB; ++t) tc_copy16(dst + (NA + t) * PkTermBytes, b + t * gw_plane, bytes);
             }
-            // rows: eight consecutive pixels of tap (k_dh, k_dw) of channel k_c through the table
-            uint32_t hi[4] = {0u, 0u, 0u, 0u}, mid[4] = {0u, 0u, 0u, 0u}, lo[4] = {0u, 0u, 0u, 0u};
-            if (R.k_c[i] >= 0 && left > 0) {
-                unsigned n = n0;
-                int oh = oh0, ow = ow0;
+            if (!window) row_generic<NA>(dst, R.k_c[i], R.k_dh[i], R.k_dw[i], n0, oh0, ow0, left);
+        }
+        if (!window || R.w_c < 0) return;
+        const int kw = g.KW;
+        if (left >= 8 && ow0 + 8 <= g.OW) {
+            // one stretch of 8 + kw - 1 image bytes serves the kw taps of the kernel row
+            const int ih = oh0 * g.SH + R.w_dh;
+            const bool row_ok = static_cast<unsigned>(ih) < static_cast<unsigned>(g.H);
+            const int base = ((static_cast<int>(n0) * g.C + R.w_c) * g.H + (row_ok ? ih : 0)) * g.W;
+            const int iw0 = ow0 - g.PW;
+            uint32_t vh[10], vm[10], vl[10];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    if (e < left) {
-                        const int ih = oh * g.SH + R.k_dh[i], iw = ow * g.SW + R.k_dw[i];
-                        int idx = pad_index;
-                        if (static_cast<unsigned>(ih) < static_cast<unsigned>(g.H) && static_cast<unsigned>(iw) < static_cast<unsigned>(g.W))
-                            idx = index_of<XDT>(x, ((static_cast<int>(n) * g.C + R.k_c[i]) * g.H + ih) * g.W + iw);
-                        hi[e >> 1] |= static_cast<uint32_t>(t_hi[idx]) << (16 * (e & 1));
-                        if (NA == 3) {
-                            mid[e >> 1] |= static_cast<uint32_t>(t_mid[idx]) << (16 * (e & 1));
-                            lo[e >> 1] |= static_cast<uint32_t>(t_lo[idx]) << (16 * (e & 1));
-                        }
-                    }
-                    if (++ow == g.OW) { ow = 0; if (++oh == g.OH) { oh = 0; ++n; } }
+            for (int q = 0; q < 10; ++q) {
+                vh[q] = vm[q] = vl[q] = 0u;
+                if (q < 8 + kw - 1) {
+                    const int iw = iw0 + q;
+                    int idx = pad_index;
+                    if (row_ok && static_cast<unsigned>(iw) < static_cast<unsigned>(g.W)) idx = index_of<XDT>(x, base + iw);
+                    vh[q] = t_hi[idx];
+                    if (NA == 3) { vm[q] = t_mid[idx]; vl[q] = t_lo[idx]; }
                 }
             }
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
-            if (NA == 3) {
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + PkTermBytes), "r"(mid[0]), "r"(mid[1]), "r"(mid[2]), "r"(mid[3]) : "memory");
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 2 * PkTermBytes), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+                const int row = R.w_row0 + j;
+                if (j < kw && row >= 0 && row < TcM) {
+                    const uint32_t dst = stage + static_cast<uint32_t>(row) * 128u + static_cast<uint32_t>((chunk ^ (row & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(vh[j] | (vh[j + 1] << 16)), "r"(vh[j + 2] | (vh[j + 3] << 16)),
+                                 "r"(vh[j + 4] | (vh[j + 5] << 16)), "r"(vh[j + 6] | (vh[j + 7] << 16)) : "memory");
+                    if (NA == 3) {
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + PkTermBytes), "r"(vm[j] | (vm[j + 1] << 16)),
+                                     "r"(vm[j + 2] | (vm[j + 3] << 16)), "r"(vm[j + 4] | (vm[j + 5] << 16)), "r"(vm[j + 6] | (vm[j + 7] << 16)) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 2 * PkTermBytes), "r"(vl[j] | (vl[j + 1] << 16)),
+                                     "r"(vl[j + 2] | (vl[j + 3] << 16)), "r"(vl[j + 4] | (vl[j + 5] << 16)), "r"(vl[j + 6] | (vl[j + 7] << 16)) : "memory");
+                    }
+                }
+            }
+        } else {
+            // a chunk that crosses the end of an image row or of this tile's share: tap by tap
+            for (int j = 0; j < kw; ++j) {
+                const int row = R.w_row0 + j;
+                if (row >= 0 && row < TcM) {
+                    const uint32_t dst = stage + static_cast<uint32_t>(row) * 128u + static_cast<uint32_t>((chunk ^ (row & 7)) << 4);
+                    row_generic<NA>(dst, R.w_c, R.w_dh, j * g.DW - g.PW, n0, oh0, ow0, left);
+                }
             }
         }
     }
@@ -1235,7 +1299,8 @@ int tc_packed_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_
         p.x = x; p.dw = dw; p.gwp = gwp; p.gw = grad_w; p.O = O; p.K = K; p.pad_index = pad_index; p.gz = static_cast<int>(gz); \
         p.P = z.P; p.Ppad = z.Ppad; p.gw_plane = static_cast<long long>(O) * z.Ppad; p.g = g;                             \
         p.divL = tc_fastdiv(L); p.divOW = tc_fastdiv(g.OW); p.divKK = tc_fastdiv(KK); p.divKW = tc_fastdiv(g.KW);          \
-        p.mt = mt; p.nt = nt;                                                                                             \
+        p.mt = mt; p.nt = nt; p.divKH = tc_fastdiv(g.KH);                                                                 \
+        p.window = (g.SW == 1 && g.DW == 1 && (g.KW == 2 || g.KW == 3)) ? 1 : 0;                                          \
         return exact_tables ? tc_packed_launch<PkGradW<DT>, 1, 3, 3>(p, tiles_mn * gz, ncols, s)                          \
                             : tc_packed_launch<PkGradW<DT>, 3, 3, 2>(p, tiles_mn * gz, ncols, s);                          \
     }

@@ -250,7 +250,7 @@ def test_lre_backward_im2col_operator(dev):
 
 
 @pytest.mark.parametrize("geom", [(4, 70, 20, 20, 150, 3, 1, 1, 1), (3, 40, 17, 19, 130, 3, 2, 1, 1), (2, 200, 9, 9, 260, 1, 1, 0, 1),
-                                  (2, 33, 14, 14, 40, (3, 2), (2, 1), (1, 2), (1, 2))])
+                                  (2, 33, 14, 14, 40, (3, 2), (2, 1), (1, 2), (1, 2)), (3, 20, 12, 17, 24, (3, 2), 1, (1, 0), 1)])
 def test_tensor_core_backward_against_fp64_and_the_simt_kernels(dev, geom):
     """Image-space STE / LRE backward on the tensor cores (three-term bf16 split, fp32 accumulation): several output
     tiles, a reduction split over the grid, stride classes, ragged edges - against the fp64 oracle at rel 1e-5 and
