@@ -1012,12 +1012,52 @@ struct PkGradW {
                 }
             }
         } else {
-            // a chunk that crosses the end of an image row or of this tile's share: tap by tap
-            for (int j = 0; j < kw; ++j) {
+            // a chunk that crosses the end of an image row (or of this tile's share): pixel by pixel with a sliding
+            // window over the kernel row's taps - one new lookup per pixel, kw at the start of an image row
+            uint32_t th[3][4] = {}, tm[3][4] = {}, tl[3][4] = {};
+            uint32_t wh[3] = {0u, 0u, 0u}, wm[3] = {0u, 0u, 0u}, wl[3] = {0u, 0u, 0u};
+            unsigned n = n0;
+            int oh = oh0, ow = ow0, base = 0;
+            bool fresh = true, row_ok = false;
+            auto look = [&](int iw, int slot) {
+                int idx = pad_index;
+                if (row_ok && static_cast<unsigned>(iw) < static_cast<unsigned>(g.W)) idx = index_of<XDT>(x, base + iw);
+                wh[slot] = t_hi[idx];
+                if (NA == 3) { wm[slot] = t_mid[idx]; wl[slot] = t_lo[idx]; }
+            };
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                if (e < left) {
+                    if (fresh) {
+                        const int ih = oh * g.SH + R.w_dh;
+                        row_ok = static_cast<unsigned>(ih) < static_cast<unsigned>(g.H);
+                        base = ((static_cast<int>(n) * g.C + R.w_c) * g.H + (row_ok ? ih : 0)) * g.W;
+                        look(ow - g.PW, 0);
+                        if (kw == 3) look(ow - g.PW + 1, 1);
+                    }
+                    if (kw == 3) look(ow - g.PW + 2, 2); else look(ow - g.PW + 1, 1);
+#pragma unroll
+                    for (int j = 0; j < 3; ++j)
+                        if (j < kw) {
+                            th[j][e >> 1] |= wh[j] << (16 * (e & 1));
+                            if (NA == 3) { tm[j][e >> 1] |= wm[j] << (16 * (e & 1)); tl[j][e >> 1] |= wl[j] << (16 * (e & 1)); }
+                        }
+                    wh[0] = wh[1]; wm[0] = wm[1]; wl[0] = wl[1];
+                    if (kw == 3) { wh[1] = wh[2]; wm[1] = wm[2]; wl[1] = wl[2]; }
+                }
+                fresh = false;
+                if (++ow == g.OW) { ow = 0; fresh = true; if (++oh == g.OH) { oh = 0; ++n; } }
+            }
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
                 const int row = R.w_row0 + j;
-                if (row >= 0 && row < TcM) {
+                if (j < kw && row >= 0 && row < TcM) {
                     const uint32_t dst = stage + static_cast<uint32_t>(row) * 128u + static_cast<uint32_t>((chunk ^ (row & 7)) << 4);
-                    row_generic<NA>(dst, R.w_c, R.w_dh, j * g.DW - g.PW, n0, oh0, ow0, left);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(th[j][0]), "r"(th[j][1]), "r"(th[j][2]), "r"(th[j][3]) : "memory");
+                    if (NA == 3) {
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + PkTermBytes), "r"(tm[j][0]), "r"(tm[j][1]), "r"(tm[j][2]), "r"(tm[j][3]) : "memory");
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + 2 * PkTermBytes), "r"(tl[j][0]), "r"(tl[j][1]), "r"(tl[j][2]), "r"(tl[j][3]) : "memory");
+                    }
                 }
             }
         }
