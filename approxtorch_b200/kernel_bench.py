@@ -324,6 +324,12 @@ def profile_once(dev):
     go = torch.randn(256, 128, 16, 16, device=dev)
     dec = ops.decode_table(dev, 128)
     ops.lre_conv_backward(go, x8, wi, dec, dec, ((3, 3), (1, 1), (1, 1), (1, 1)), 128, exact_tables=True)
+    saved = ops.PACKED_BACKWARD
+    ops.PACKED_BACKWARD = False                            # the same layer with the operands built inside the kernel
+    try:
+        ops.lre_conv_backward(go, x8, wi, dec, dec, ((3, 3), (1, 1), (1, 1), (1, 1)), 128, exact_tables=True)
+    finally:
+        ops.PACKED_BACKWARD = saved
     # custom-pair backward and a table of the fp32 class on the single-layer configuration's GEMM shape
     N, K, L, O = 8, 576, 1024, 64
     xc = torch.randint(0, 256, (N, K, L), dtype=torch.uint8, device=dev)
@@ -336,7 +342,8 @@ def profile_once(dev):
     y = torch.empty((N, O, L), dtype=torch.float32, device=dev)
     ops.lut_gemm_launch(xc, wc, ops.lut_image(half), y, N, K, L, O)
     torch.cuda.synchronize()
-    return {"launched": "stats, quantize_image, fakequant_bwd, lut_gemm (1x1 conv), tc_gemm (grad_x, grad_w), pair_grad (dx, dw), pair_fwd"}
+    return {"launched": "stats, quantize_image, fakequant_bwd, lut_gemm (1x1 conv), tc_pack_go, tc_pack_w, tc_packed (grad_x, grad_w), "
+                        "tc_gemm (grad_x, grad_w), pair_grad (dx, dw), pair_fwd"}
 
 
 def run_all(dev, which=("lds", "stream", "backward", "custom", "fp32", "layers"), batches=(128, 16)):
