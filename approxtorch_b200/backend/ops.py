@@ -278,6 +278,7 @@ def quantize_weight(w: Tensor, scale: Tensor, zero_point: Tensor | None, qmin: i
 
 TENSOR_CORE_BACKWARD = True   # False: keep the STE / LRE image-space backward on the fp32 SIMT kernels
 PACKED_BACKWARD = True        # False: the tensor-core backward builds its operands inside the contraction kernels
+DETERMINISTIC_GRAD_W = False  # True: the packed backward adds grad_w's partial sums in a fixed order (no atomics)
 
 
 def lre_conv_backward(go: Tensor, x8: Tensor, w_idx: Tensor | None, dx: Tensor | None, dw: Tensor | None,
@@ -295,7 +296,8 @@ def lre_conv_backward(go: Tensor, x8: Tensor, w_idx: Tensor | None, dx: Tensor |
     O = go.shape[1]
     gx = torch.empty((B, C, H, W), dtype=torch.float32, device=go.device) if need_x else None
     gw = torch.empty((O, C * kh * kw), dtype=torch.float32, device=go.device) if need_w else None
-    flags = (1 if exact_tables else 0) | (0 if TENSOR_CORE_BACKWARD else 2) | (0 if PACKED_BACKWARD else 4)
+    flags = ((1 if exact_tables else 0) | (0 if TENSOR_CORE_BACKWARD else 2) | (0 if PACKED_BACKWARD else 4) |
+             (8 if DETERMINISTIC_GRAD_W else 0))
     with _Guard(go):
         # scratch for the packed bf16 planes of the gradient (0: the problem does not qualify or packing is off)
         nbytes = int(_lib.atb_lre_conv_bwd_scratch_bytes(B, C, H, W, O, kh, kw, sh, sw, ph, pw, dh, dw_, flags,

@@ -139,11 +139,11 @@ int tc_conv_grad_x(const float* go, const uint8_t* widx, const float* dx, const 
                    const uint8_t* x_mask, const float* x_scale, float* grad_x, int N, int O, const ConvGeom& g,
                    bool exact_tables, cudaStream_t s);
 int tc_status_read(int* status);
-size_t tc_packed_scratch_bytes(int N, int O, const ConvGeom& g, bool need_x, bool need_w, bool exact_tables);
+size_t tc_packed_scratch_bytes(int N, int O, const ConvGeom& g, bool need_x, bool need_w, bool exact_tables, bool deterministic);
 int tc_packed_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t* widx, const float* dx, const float* dw,
                        const float* go_scale, const float* w_zero, const uint8_t* x_mask, const float* x_scale,
                        float* grad_x, float* grad_w, int N, int O, const ConvGeom& g, int pad_index, bool exact_tables,
-                       void* scratch, cudaStream_t s);
+                       bool deterministic, void* scratch, cudaStream_t s);
 
 inline int grid_for(long long work, int threads, int cap)
 {

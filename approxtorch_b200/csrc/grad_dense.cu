@@ -651,7 +651,7 @@ extern "C" size_t atb_lre_conv_bwd_scratch_bytes(int N, int C, int H, int W, int
     if (!conv_out_shape(H, W, kh, kw, sh, sw, ph, pw, dh, dw_, &OH, &OW)) return 0;
     if (static_cast<long long>(sh) * sw > 64 || static_cast<long long>(kh) * kw > 128) return 0;
     const ConvGeom g{C, H, W, kh, kw, sh, sw, ph, pw, dh, dw_, OH, OW};
-    return tc_packed_scratch_bytes(N, O, g, need_x != 0, need_w != 0, (flags & 1) != 0);
+    return tc_packed_scratch_bytes(N, O, g, need_x != 0, need_w != 0, (flags & 1) != 0, (flags & 8) != 0);
 }
 
 extern "C" int atb_tensor_core_status(int* status /*host*/)
@@ -732,7 +732,8 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
     const bool want_x = grad_x != nullptr && Mx * C > 0, want_w = grad_w != nullptr && O * K > 0;
     if (lean && !simt_only && (flags & 4) == 0 && scratch != nullptr && O > 0 && P > 0 && N <= 65535 && (want_x || want_w) &&
         sh * sw <= 64 && kh * kw <= 128) {
-        const size_t need = tc_packed_scratch_bytes(N, O, g, want_x, want_w, exact_tables);
+        const bool deterministic = (flags & 8) != 0;
+        const size_t need = tc_packed_scratch_bytes(N, O, g, want_x, want_w, exact_tables, deterministic);
         if (need > 0 && scratch_bytes >= need) {
             ATB_REQUIRE(aligned_to(scratch, 16), "scratch must be 16-byte aligned");
             ATB_REQUIRE(go && (!want_x || (widx && dx)) && (!want_w || (x && dw)), "null pointer");
@@ -742,7 +743,7 @@ extern "C" int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, con
                 if (rc != ATB_OK) return rc;
             }
             return tc_packed_conv_bwd(go, x, x_dtype, widx, dx, dw, go_scale, w_zero, x_mask, x_scale, want_x ? grad_x : nullptr,
-                                      want_w ? grad_w : nullptr, N, O, g, pad_index, exact_tables, scratch, s);
+                                      want_w ? grad_w : nullptr, N, O, g, pad_index, exact_tables, deterministic, scratch, s);
         }
     }
     if (grad_x != nullptr && Mx * C > 0) {

@@ -852,7 +852,7 @@ struct PkGradX {
 // GW; reduction over the pixels of slice z of the pixel axis.  Result element (k, o) is added to grad_w[o, k].
 template <int XDT>
 struct PkGradW {
-    const void* x; const float* dw; const uint16_t* gwp; float* gw;
+    const void* x; const float* dw; const uint16_t* gwp; float* gw; float* part;
     int O, K, pad_index, gz; long long P, Ppad, gw_plane; ConvGeom g;
     TcFastDiv divL, divOW, divKK, divKW, divKH;
     int mt, nt, window;
@@ -1062,10 +1062,27 @@ struct PkGradW {
             }
         }
     }
-    struct Out { int k; bool ok; };
-    __device__ Out out_row(const Tile& T, int m) const { return Out{m, m < K}; }
-    __device__ void finish(const Out& o, int col, float v) const { atomicAdd(gw + col * K + o.k, v); }
+    // `part` null: fp32 atomics into the zeroed grad_w (the order of the slices' contributions varies from run to
+    // run); otherwise slice z stores its tile into part[z][o][k] and a second pass adds the slices in ascending order
+    struct Out { int k; bool ok; int z; };
+    __device__ Out out_row(const Tile& T, int m) const { return Out{m, m < K, T.z}; }
+    __device__ void finish(const Out& o, int col, float v) const
+    {
+        if (part != nullptr) part[(static_cast<long long>(o.z) * O + col) * K + o.k] = v;
+        else atomicAdd(gw + col * K + o.k, v);
+    }
 };
+
+// grad_w[i] = sum over the slices z < nz of part[z][i], in ascending z
+__global__ void tc_sum_slices_kernel(const float* __restrict__ part, float* __restrict__ gw, int nz, long long n)
+{
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float acc = 0.0f;
+        for (int z = 0; z < nz; ++z) acc += __ldcs(part + z * n + i);
+        gw[i] = acc;
+    }
+}
 
 // NA, NB: bf16 terms of the row and of the column operand (3: hi + mid + lo of an fp32 value, 1: exact in bf16);
 // the products (i, j) with i + j <= 2 are issued - lo * mid and smaller fall below fp32 rounding.
@@ -1264,9 +1281,25 @@ static size_t tc_round256(size_t b) { return (b + 255u) / 256u * 256u; }
 
 // Scratch layout: GX planes | GW planes | WT planes, each 256-byte aligned.
 struct TcPackedSizes {
-    int Opad; long long P, Ppad; size_t gx_bytes, gw_bytes, wt_bytes;
+    int Opad; long long P, Ppad; size_t gx_bytes, gw_bytes, wt_bytes, part_bytes;
+    int gz, gz_used;           // slices of grad_w's pixel axis, and how many of them are not empty
 };
-static TcPackedSizes tc_packed_sizes(int N, int O, const ConvGeom& g, bool need_x, bool need_w, bool exact_tables)
+// slices of the pixel axis for grad_w: about two tiles per SM, none shorter than eight 64-pixel steps
+static void tc_grad_w_slices(long long K, int O, long long P, int* gz_out, int* used_out)
+{
+    const int ncols = O <= 64 ? 64 : 128;
+    const long long tiles_mn = static_cast<long long>(ceil_div(K, TcM)) * ceil_div(O, ncols);
+    long long gz = (2LL * sm_count() + tiles_mn - 1) / tiles_mn;
+    const long long maxs = (P + 8 * PkK - 1) / (8 * PkK);
+    if (gz > maxs) gz = maxs;
+    if (gz > 4096) gz = 4096;
+    if (gz < 1) gz = 1;
+    const long long per_z = ((P + gz - 1) / gz + PkK - 1) / PkK * PkK;       // as PkGradW::tile cuts the axis
+    *gz_out = static_cast<int>(gz);
+    *used_out = static_cast<int>(per_z > 0 ? (P + per_z - 1) / per_z : 0);
+}
+static TcPackedSizes tc_packed_sizes(int N, int O, const ConvGeom& g, bool need_x, bool need_w, bool exact_tables,
+                                     bool deterministic)
 {
     TcPackedSizes z{};
     z.Opad = (O + PkK - 1) / PkK * PkK;
@@ -1275,29 +1308,33 @@ static TcPackedSizes tc_packed_sizes(int N, int O, const ConvGeom& g, bool need_
     z.gx_bytes = need_x ? tc_round256(static_cast<size_t>(3) * z.P * z.Opad * 2u) : 0u;
     z.gw_bytes = need_w ? tc_round256(static_cast<size_t>(3) * O * z.Ppad * 2u) : 0u;
     z.wt_bytes = need_x ? tc_round256(static_cast<size_t>(exact_tables ? 1 : 3) * g.KH * g.KW * g.C * z.Opad * 2u) : 0u;
+    const long long K = static_cast<long long>(g.C) * g.KH * g.KW;
+    tc_grad_w_slices(K, O, z.P, &z.gz, &z.gz_used);
+    z.part_bytes = (need_w && deterministic) ? tc_round256(static_cast<size_t>(z.gz_used) * O * K * 4u) : 0u;
     return z;
 }
 
-size_t tc_packed_scratch_bytes(int N, int O, const ConvGeom& g, bool need_x, bool need_w, bool exact_tables)
+size_t tc_packed_scratch_bytes(int N, int O, const ConvGeom& g, bool need_x, bool need_w, bool exact_tables, bool deterministic)
 {
-    const TcPackedSizes z = tc_packed_sizes(N, O, g, need_x, need_w, exact_tables);
+    const TcPackedSizes z = tc_packed_sizes(N, O, g, need_x, need_w, exact_tables, deterministic);
     // 32-bit element offsets inside a plane: larger problems stay on the kernels that build their operands in place
     if (z.P * z.Opad >= 2147483647LL || static_cast<long long>(O) * z.Ppad >= 2147483647LL) return 0;
-    return z.gx_bytes + z.gw_bytes + z.wt_bytes;
+    return z.gx_bytes + z.gw_bytes + z.wt_bytes + z.part_bytes;
 }
 
 // Both gradients (either may be null) from one packing pass.  grad_w must have been zeroed by the caller.
 int tc_packed_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t* widx, const float* dx, const float* dw,
                        const float* go_scale, const float* w_zero, const uint8_t* x_mask, const float* x_scale,
                        float* grad_x, float* grad_w, int N, int O, const ConvGeom& g, int pad_index, bool exact_tables,
-                       void* scratch, cudaStream_t s)
+                       bool deterministic, void* scratch, cudaStream_t s)
 {
     const bool need_x = grad_x != nullptr, need_w = grad_w != nullptr;
-    const TcPackedSizes z = tc_packed_sizes(N, O, g, need_x, need_w, exact_tables);
+    const TcPackedSizes z = tc_packed_sizes(N, O, g, need_x, need_w, exact_tables, deterministic);
     const int L = g.OH * g.OW, KK = g.KH * g.KW, K = g.C * KK;
     uint16_t* gxp = need_x ? static_cast<uint16_t*>(scratch) : nullptr;
     uint16_t* gwp = need_w ? reinterpret_cast<uint16_t*>(static_cast<char*>(scratch) + z.gx_bytes) : nullptr;
     uint16_t* wt = need_x ? reinterpret_cast<uint16_t*>(static_cast<char*>(scratch) + z.gx_bytes + z.gw_bytes) : nullptr;
+    float* part = z.part_bytes ? reinterpret_cast<float*>(static_cast<char*>(scratch) + z.gx_bytes + z.gw_bytes + z.wt_bytes) : nullptr;
     {
         const dim3 grid(ceil_div(L, 32), z.Opad / 32, N);
         if (grid.y > 65535 || grid.z > 65535) return fail_invalid("problem too large for the tensor-core backward");
@@ -1326,28 +1363,31 @@ int tc_packed_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_
     if (need_w) {
         const int ncols = O <= 64 ? 64 : 128;
         const int mt = ceil_div(K, TcM), nt = ceil_div(O, ncols);
-        // slices of the pixel axis: about two tiles per SM, none shorter than eight 64-pixel steps
         const long long tiles_mn = static_cast<long long>(mt) * nt;
-        long long gz = (2LL * sm_count() + tiles_mn - 1) / tiles_mn;
-        const long long maxs = (z.P + 8 * PkK - 1) / (8 * PkK);
-        if (gz > maxs) gz = maxs;
-        if (gz > 4096) gz = 4096;
-        if (gz < 1) gz = 1;
+        const long long gz = z.gz;
 #define ATB_TC_PW(DT)                                                                                                     \
     {                                                                                                                     \
         PkGradW<DT> p{};                                                                                                  \
-        p.x = x; p.dw = dw; p.gwp = gwp; p.gw = grad_w; p.O = O; p.K = K; p.pad_index = pad_index; p.gz = static_cast<int>(gz); \
+        p.x = x; p.dw = dw; p.gwp = gwp; p.gw = grad_w; p.part = part; p.O = O; p.K = K; p.pad_index = pad_index;         \
+        p.gz = static_cast<int>(gz);                                                                                      \
         p.P = z.P; p.Ppad = z.Ppad; p.gw_plane = static_cast<long long>(O) * z.Ppad; p.g = g;                             \
         p.divL = tc_fastdiv(L); p.divOW = tc_fastdiv(g.OW); p.divKK = tc_fastdiv(KK); p.divKW = tc_fastdiv(g.KW);          \
         p.mt = mt; p.nt = nt; p.divKH = tc_fastdiv(g.KH);                                                                 \
         p.window = (g.SW == 1 && g.DW == 1 && (g.KW == 2 || g.KW == 3)) ? 1 : 0;                                          \
-        return exact_tables ? tc_packed_launch<PkGradW<DT>, 1, 3, 3>(p, tiles_mn * gz, ncols, s)                          \
-                            : tc_packed_launch<PkGradW<DT>, 3, 3, 2>(p, tiles_mn * gz, ncols, s);                          \
+        rc = exact_tables ? tc_packed_launch<PkGradW<DT>, 1, 3, 3>(p, tiles_mn * gz, ncols, s)                            \
+                          : tc_packed_launch<PkGradW<DT>, 3, 3, 2>(p, tiles_mn * gz, ncols, s);                            \
     }
+        int rc = ATB_OK;
         if (x_dtype == ATB_U8) ATB_TC_PW(ATB_U8)
-        if (x_dtype == ATB_I8) ATB_TC_PW(ATB_I8)
-        ATB_TC_PW(ATB_F32)
+        else if (x_dtype == ATB_I8) ATB_TC_PW(ATB_I8)
+        else ATB_TC_PW(ATB_F32)
 #undef ATB_TC_PW
+        if (rc != ATB_OK) return rc;
+        if (part != nullptr) {
+            const long long n = static_cast<long long>(O) * K;
+            tc_sum_slices_kernel<<<grid_for(n, 256, 4096), 256, 0, s>>>(part, grad_w, z.gz_used, n);
+            return check_launch("tc_sum_slices_kernel");
+        }
     }
     return ATB_OK;
 }

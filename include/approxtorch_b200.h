@@ -201,7 +201,9 @@ int atb_lre_bwd(const float* go, const void* x, int x_dtype, const void* w, int 
  * grad_x = (x_mask ? g : 0) / max(*x_scale, 1e-12) (fakequant_per_tensor_backward_claude,
  * approxtorch/backend/csrc/claude/quantization.cu:113-143, without its separate 9-byte-per-element pass).
  * flags: bit 0 = dx, dw and w_zero hold integers of magnitude <= 256 (the STE decode tables): half the tensor-core
- * work; bit 1 = use the SIMT kernels; bit 2 = never pack the operands into scratch.
+ * work; bit 1 = use the SIMT kernels; bit 2 = never pack the operands into scratch; bit 3 = with packed operands,
+ * grad_w's slices of the pixel axis are stored separately and added in a fixed order by a second pass (bit-identical
+ * from run to run; the default adds them with fp32 atomics in whatever order the blocks finish).
  * scratch / scratch_bytes: optional device memory of atb_lre_conv_bwd_scratch_bytes() bytes (16-byte aligned).
  * Replaces the cuDNN convolution_backward calls of approxtorch/nn/bgemm_int8.py:165-212, 259-295. */
 int atb_lre_conv_bwd(const float* go, const void* x, int x_dtype, const uint8_t* widx /*[O,K]*/,

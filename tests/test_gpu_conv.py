@@ -296,6 +296,29 @@ def test_tensor_core_backward_against_fp64_and_the_simt_kernels(dev, geom):
     assert _C.lib.atb_tensor_core_status(ctypes.byref(status)) == 0 and status.value == 0
 
 
+def test_packed_backward_grad_w_in_fixed_order_is_reproducible(dev):
+    """With the fixed-order option the slices of grad_w's pixel axis are stored and added by a second pass: two runs
+    give the same bits, and the result stays within rel 1e-5 of the fp64 oracle."""
+    from approxtorch_b200.backend import ops
+    rng = np.random.default_rng(77)
+    B, C, H, W, O = 6, 40, 24, 24, 72
+    g4 = ((3, 3), (1, 1), (1, 1), (1, 1))
+    x8 = rng.integers(-127, 128, (B, C, H, W), dtype=np.int8)
+    widx = rng.integers(0, 256, (O, C * 9), dtype=np.uint8)
+    cols = lo.im2col_index(lo.index_of(x8, True), 3, 3, 1, 1, 1, 1, 1, 1, 128)
+    go = rng.standard_normal((B, O, cols.shape[2])).astype(np.float32)
+    tab = (rng.standard_normal(256) * 3).astype(np.float32)
+    _, rgw = lo.lre_backward(go.astype(np.float64), cols, widx, tab, tab)
+    ops.DETERMINISTIC_GRAD_W = True
+    try:
+        runs = [ops.lre_conv_backward(_t(go, dev).view(B, O, H, W), _t(x8, dev), _t(widx, dev), _t(tab, dev), _t(tab, dev),
+                                      g4, 128, need_x=False)[1] for _ in range(3)]
+    finally:
+        ops.DETERMINISTIC_GRAD_W = False
+    assert torch.equal(runs[0], runs[1]) and torch.equal(runs[0], runs[2])
+    _close(runs[0], rgw)
+
+
 def _uint8_layer_truth(x, w, bias, lut, sx, zx, sw, zw, geom):
     (kh, kw), (sh, sw_), (ph, pw), (dh, dw_) = geom
     O = w.shape[0]
