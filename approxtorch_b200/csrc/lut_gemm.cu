@@ -446,30 +446,47 @@ __device__ __forceinline__ bool park_or_finish(const GemmArgs& a, const volatile
                 xsum += __ldcg(reinterpret_cast<const int*>(slot + 16 * kThreads) + tid);
             }
         }
-#pragma unroll
-        for (int e = 0; e < 16; ++e) {
-            uint4 own = get(e);
-            uint4 sum = FLOAT ? make_uint4(0u, 0u, 0u, 0u) : own;
+        if (!FLOAT) {
+            // integer sums (modulo 2^32, any order): one segment at a time, eight of its 16-byte pieces requested
+            // together so that their latencies overlap instead of adding up
             for (int s = 0; s < nsegs; ++s) {
-                uint4 p;
-                if (s == mine) {
-                    if (!FLOAT) continue;
-                    p = own;
-                } else {
-                    const long long b = first + s;
-                    const uint4* slot = a.slots + (2LL * b + (tile_u0 > b * a.units_per_cta ? 1 : 0)) * kSlotVecs;
-                    p = __ldcg(slot + e * kThreads + tid);
+                if (s == mine) continue;
+                const long long b = first + s;
+                const uint4* slot = a.slots + (2LL * b + (tile_u0 > b * a.units_per_cta ? 1 : 0)) * kSlotVecs + tid;
+#pragma unroll
+                for (int e0 = 0; e0 < 16; e0 += 8) {
+                    uint4 p[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) p[i] = __ldcg(slot + (e0 + i) * kThreads);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        uint4 sum = get(e0 + i);
+                        sum.x += p[i].x; sum.y += p[i].y; sum.z += p[i].z; sum.w += p[i].w;
+                        set(e0 + i, sum);
+                    }
                 }
-                if (FLOAT) {
+            }
+        } else {
+            // fp32 sums in ascending segment order whoever finishes (a rarely taken path: tables of the fp32 class
+            // normally run on the kernel that keeps the table on chip)
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                const uint4 own = get(e);
+                uint4 sum = make_uint4(0u, 0u, 0u, 0u);
+                for (int s = 0; s < nsegs; ++s) {
+                    uint4 p = own;
+                    if (s != mine) {
+                        const long long b = first + s;
+                        const uint4* slot = a.slots + (2LL * b + (tile_u0 > b * a.units_per_cta ? 1 : 0)) * kSlotVecs;
+                        p = __ldcg(slot + e * kThreads + tid);
+                    }
                     sum.x = __float_as_uint(__uint_as_float(sum.x) + __uint_as_float(p.x));
                     sum.y = __float_as_uint(__uint_as_float(sum.y) + __uint_as_float(p.y));
                     sum.z = __float_as_uint(__uint_as_float(sum.z) + __uint_as_float(p.z));
                     sum.w = __float_as_uint(__uint_as_float(sum.w) + __uint_as_float(p.w));
-                } else {
-                    sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
                 }
+                set(e, sum);
             }
-            set(e, sum);
         }
     }
     return true;

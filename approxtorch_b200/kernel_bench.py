@@ -52,11 +52,12 @@ RESNET18_CIFAR_LAYERS = [
 
 def peaks(dev):
     """Roofline denominators: measured HBM copy bandwidth and max SM clock when the measurement file is present."""
-    out = {"hbm_gbs": 6650.0, "sm_max_mhz": 1965.0, "source": "fallback"}
+    out = {"hbm_gbs": 6650.0, "sm_max_mhz": 1965.0, "bf16_tflops": 1590.0, "source": "fallback"}
     try:
         with open(os.path.join(_REPO, "MEASURED_PEAKS.json")) as f:
             m = json.load(f)
-        out.update(hbm_gbs=float(m["hbm_gbs"]), sm_max_mhz=float(m["sm_max_mhz"]), source="MEASURED_PEAKS.json")
+        out.update(hbm_gbs=float(m["hbm_gbs"]), sm_max_mhz=float(m["sm_max_mhz"]), bf16_tflops=float(m["bf16_tflops"]),
+                   source="MEASURED_PEAKS.json")
     except Exception:
         pass
     out["sms"] = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -138,6 +139,7 @@ def backward_kernels(dev, batch=256, layers=None, mode="ste", tensor_cores=True,
     """grad_x and grad_w of the image-space STE / LRE backward per layer shape; flop = 2 * B*OH*OW * C*k*k * O (the
     useful fp32-equivalent work, whatever number of bf16 products the tensor-core path spends on it)."""
     layers = layers or RESNET18_CIFAR_LAYERS
+    pk = peaks(dev)
     rows, tot = [], {"gx_ms": 0.0, "gw_ms": 0.0, "flop": 0.0}
     table = ops.decode_table(dev, 128) if mode == "ste" else torch.randn(256, device=dev)
     exact = mode == "ste"
@@ -168,7 +170,13 @@ def backward_kernels(dev, batch=256, layers=None, mode="ste", tensor_cores=True,
                                                                         if packed else "operands built inside the kernel")) if tensor_cores else "fp32 SIMT",
             "layers": rows, "total_grad_x_ms": tot["gx_ms"], "total_grad_w_ms": tot["gw_ms"],
             "total_grad_x_tflops": tot["flop"] / tot["gx_ms"] / 1e9, "total_grad_w_tflops": tot["flop"] / tot["gw_ms"] / 1e9,
-            "fp32_fma_peak_tflops": 74.4}
+            "fp32_fma_peak_tflops": 74.4,
+            # tensor-core roofline: every useful product costs 3 (exact table) or 6 bf16 products
+            "bf16_products_per_product": (3 if exact else 6) if tensor_cores else None,
+            "frac_of_measured_bf16_peak": ({"grad_x": (3 if exact else 6) * tot["flop"] / tot["gx_ms"] / 1e9 / pk["bf16_tflops"],
+                                            "grad_w": (3 if exact else 6) * tot["flop"] / tot["gw_ms"] / 1e9 / pk["bf16_tflops"],
+                                            "peak_tflops": pk["bf16_tflops"], "peak_source": pk["source"]}
+                                           if tensor_cores else None)}
 
 
 # ----------------------------------------------------------------------------------------------- custom pair / depthwise
