@@ -266,11 +266,24 @@ __device__ __forceinline__ void load_chunk(const GemmArgs& a, const RowCursor& r
         // when the tap lies outside the image or past the last k) and the pad value is selected afterwards, so
         // that the 16 loads are independent and their latencies overlap.
         const int khw = a.g.KH * a.g.KW;
+        uint32_t v[kChunk];
+        if (khw == 1) {
+            // a 1x1 kernel: the reduction index is the channel, the sixteen taps lie one image plane apart
+            const bool inside_px = static_cast<unsigned>(rc.ih0) < static_cast<unsigned>(a.g.H) &&
+                                   static_cast<unsigned>(rc.iw0) < static_cast<unsigned>(a.g.W);
+            const long long plane = static_cast<long long>(a.g.H) * a.g.W;
+            const uint8_t* px = rc.base + (inside_px ? rc.ih0 * a.g.W + rc.iw0 : 0);
+#pragma unroll
+            for (int kk = 0; kk < kChunk; ++kk) {
+                const bool inside = inside_px && (k0 + kk < kend);
+                const uint32_t b = static_cast<uint32_t>(__ldg(px + (inside ? (k0 + kk) * plane : 0LL))) ^ static_cast<uint32_t>(a.x_xor);
+                v[kk] = inside ? b : static_cast<uint32_t>(pad);
+            }
+        } else {
         int c = k0 / khw;
         const int rem = k0 - c * khw;
         int i = rem / a.g.KW;
         int j = rem - i * a.g.KW;
-        uint32_t v[kChunk];
 #pragma unroll
         for (int kk = 0; kk < kChunk; ++kk) {
             const int ih = rc.ih0 + i * a.g.DH;
@@ -286,6 +299,7 @@ __device__ __forceinline__ void load_chunk(const GemmArgs& a, const RowCursor& r
             const bool wrap_i = i == a.g.KH;
             i = wrap_i ? 0 : i;
             c += wrap_i ? 1 : 0;
+        }
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q)
@@ -320,6 +334,22 @@ __device__ __forceinline__ void load_chunk(const GemmArgs& a, const RowCursor& r
             }
         }
     }
+}
+
+// Sum of the first `kc` of the sixteen operand bytes a thread holds for its pixel row (the zero-point correction
+// needs the row sums; taking them here costs a dozen instructions per chunk instead of a shared-memory byte load per
+// k-step)
+__device__ __forceinline__ int chunk_sum(const uint32_t (&xr)[4], int kc)
+{
+    int s = 0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int nv = kc - 4 * q;
+        uint32_t w = xr[q];
+        if (nv < 4) w = nv <= 0 ? 0u : (w & ((1u << (8 * nv)) - 1u));
+        s = static_cast<int>(__dp4a(w, 0x01010101u, static_cast<unsigned>(s)));
+    }
+    return s;
 }
 
 __device__ __forceinline__ void store_chunk(uint8_t* s_x, uint8_t* s_w, int buf, int tid,
@@ -554,6 +584,9 @@ __device__ __forceinline__ bool gemm_body_int(const GemmArgs& a, uint8_t* smem, 
 
     uint32_t xr[4], wr[4];
     load_chunk(a, rc, wcol, vec_x, vec_w, kbeg, kend, tid, pad, xr, wr, bm);
+    // thread t loads pixel row t of the tile, which is also the row whose operand sum the epilogue asks it for
+    const bool sum_rows = want_xsum && tid < bm;
+    if (sum_rows) xsum += chunk_sum(xr, min(kChunk, kend - kbeg));
     store_chunk(s_x, s_w, 0, tid, xr, wr, bm);
     if (wait_table) {
         const bool ok = table_copy_wait(bar);
@@ -598,7 +631,10 @@ __device__ __forceinline__ bool gemm_body_int(const GemmArgs& a, uint8_t* smem, 
             const int kc = min(kChunk, kend - k0);
             const int cur = ci & 1;
             const bool has_next = ci + 1 < nch;
-            if (has_next) load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr, bm);
+            if (has_next) {
+                load_chunk(a, rc, wcol, vec_x, vec_w, k0 + kChunk, kend, tid, pad, xr, wr, bm);
+                if (sum_rows) xsum += chunk_sum(xr, min(kChunk, kend - k0 - kChunk));
+            }
             for (int kk = 0; kk < kc; ++kk, ++step) {
                 if (has_next && kk == 4) store_chunk(s_x, s_w, cur ^ 1, tid, xr, wr, bm);
                 const uint8_t* xrow = s_x + (cur * kChunk + kk) * kMaxBlockRows + warp * TM;
@@ -608,7 +644,6 @@ __device__ __forceinline__ bool gemm_body_int(const GemmArgs& a, uint8_t* smem, 
                 else if (has_next) wnext = s_w + ((cur ^ 1) * kChunk) * kStagedCols;
                 uint8_t* stage_next = s_stage + ((step + 1) & 1) * kStageBytes;
                 const uint8_t* stage_cur = s_stage + (step & 1) * kStageBytes;
-                if (want_xsum) xsum += static_cast<int>(xrow[lane]);
 
                 QuadWords v;
                 if (wnext != nullptr) fetch_quad(s_tab, wnext, warp, lane, v);
