@@ -58,6 +58,9 @@ _SIGNATURES = {
                                        _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "atb_lut_conv2d_fwd": (_i, [_vp, _i, _vp, _vp, _vp] + [_i] * 13 + [_i]
                            + [_vp] * 5 + [_i, _vp, _sz, _vp]),
+    "atb_pixel_rows_u8": (_i, [_vp, _i] + [_i] * 12 + [_i, _vp, _vp, _vp, _vp]),
+    "atb_lut_gemm_rows_plan": (_i, [_i, _i, _ll, _i, ctypes.POINTER(GemmPlan)]),
+    "atb_lut_conv2d_rows_fwd": (_i, [_vp, _vp, _vp, _vp, _i, _i, _ll, _i] + [_vp] * 5 + [_i, _vp, _sz, _vp]),
     "atb_absmax": (_i, [_vp, _ll, _i, _vp, _vp]),
     "atb_fakequant_fwd": (_i, [_vp, _vp, _vp, _i, _i, _vp, _vp, _ll, _vp]),
     "atb_fakequant_bwd": (_i, [_vp, _vp, _vp, _vp, _ll, _vp]),

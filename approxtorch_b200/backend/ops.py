@@ -95,7 +95,42 @@ def lut_image(lut: Tensor) -> Tensor:
         _check(_lib.atb_lut_prepare(_ptr(src), _ptr(img), _stream(lut)), "atb_lut_prepare")
     _images[key] = (weakref.ref(lut, lambda _r, k=key: _images.pop(k, None)), (lut._version, lut.data_ptr()), img)
     _image_class.pop(img.data_ptr(), None)
+    _image_owner[img.data_ptr()] = weakref.ref(lut)
     return img
+
+
+_image_owner: dict = {}    # image data_ptr -> weakref of the table tensor it was built from
+_transposed: dict = {}     # id(table) -> ((version, data_ptr), transposed table tensor)
+
+
+def _transposed_image(image: Tensor):
+    """Image of the transposed table (lut_t[a][b] = lut[b][a]) for the channels-as-rows orientation, or None when the
+    table this image was built from is not known any more."""
+    ref = _image_owner.get(image.data_ptr())
+    lut = ref() if ref is not None else None
+    if lut is None:
+        return None
+    hit = _transposed.get(id(lut))
+    stamp = (lut._version, lut.data_ptr())
+    if hit is None or hit[0] != stamp:
+        lut_t = lut.detach().reshape(256, 256).t().contiguous().reshape(-1)
+        _transposed[id(lut)] = hit = (stamp, lut_t)
+        weakref.finalize(lut, _transposed.pop, id(lut), None)
+    return lut_image(hit[1])
+
+
+def _image_class_known(image: Tensor):
+    """Table class of an image (0 int16, 1 uint16, 2 fp32) or None while it cannot be asked for (stream capture)."""
+    key = image.data_ptr()
+    cls = _image_class.get(key)
+    if cls is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        out = ctypes.c_int(-1)
+        with _Guard(image):
+            _check(_lib.atb_lut_image_class(_ptr(image), ctypes.byref(out), _stream(image)), "atb_lut_image_class")
+        cls = _image_class[key] = out.value
+    return cls
 
 
 _image_class: dict = {}   # image data_ptr -> table class (0 int16, 1 uint16, 2 fp32), asked for once per image build
@@ -108,16 +143,7 @@ def _class_flag(image: Tensor) -> int:
     and an unknown class takes the generic kernel."""
     if not FP32_TABLE_ON_CHIP:
         return 0
-    key = image.data_ptr()
-    cls = _image_class.get(key)
-    if cls is None:
-        if torch.cuda.is_current_stream_capturing():
-            return 0
-        out = ctypes.c_int(-1)
-        with _Guard(image):
-            _check(_lib.atb_lut_image_class(_ptr(image), ctypes.byref(out), _stream(image)), "atb_lut_image_class")
-        cls = _image_class[key] = out.value
-    return (1 << 24) if cls == 2 else 0
+    return (1 << 24) if _image_class_known(image) == 2 else 0
 
 
 _PAIR_BYTES = int(_lib.atb_pair_table_bytes())
@@ -219,6 +245,11 @@ def lut_conv2d_launch(img8: Tensor, w_idx: Tensor, image: Tensor, geom, pad_inde
     _require(OH >= 1 and OW >= 1, "conv geometry yields empty output")
     y = torch.empty((B, O, OH, OW), dtype=torch.float32, device=img8.device)
     cfg = _normalise_cfg(int(cfg))
+    if (ROWS_ORIENTATION and cfg < 0 and _rows_orientation_wins(B * OH * OW, C * kh * kw, O)
+            and _image_class_known(image) in (0, 1)):
+        image_t = _transposed_image(image)
+        if image_t is not None and _image_class_known(image_t) in (0, 1):
+            return _lut_conv2d_rows(img8, w_idx, image_t, y, geom, pad_index, alpha, beta, zero_x, zero_w)
     flag = _class_flag(image)
     if flag:
         cfg = max(cfg, 0) | flag
@@ -233,6 +264,54 @@ def lut_conv2d_launch(img8: Tensor, w_idx: Tensor, image: Tensor, geom, pad_inde
                                        _ptr(alpha), _ptr(beta), _ptr(zero_x), _ptr(zero_w), _ptr(wsum),
                                        cfg, _ptr(scratch), plan.scratch_bytes, _stream(y)),
                "atb_lut_conv2d_fwd")
+    return y
+
+
+ROWS_ORIENTATION = True    # layers with few pixel rows and many channels run with the channels as tile rows
+
+
+def _rows_orientation_wins(R: int, K: int, O: int) -> bool:
+    """Cost model of the two tile orientations (SM-microseconds; a k-step of a tile costs 0.43 us + 0.0226 us per 32
+    rows, the image-space loader 10 % more than the matrix loader; the pixel-matrix pass is charged to the
+    channels-as-rows side)."""
+    if R >= 2 ** 31 or R * K > (256 << 20) or K < 16:
+        return False
+
+    def step_us(rows):
+        return 0.43 + 0.0226 * (-(-rows // 32))
+
+    def tiles(rows, cols):
+        bm = 512 if rows >= 512 else -(-rows // 32) * 32
+        return -(-rows // bm) * -(-cols // 64), bm
+
+    tn, bmn = tiles(R, O)
+    tt, bmt = tiles(O, R)
+    cost_pixels_as_rows = tn * K * 1.10 * step_us(bmn)
+    cost_channels_as_rows = tt * K * step_us(bmt) + 148.0 * (6.0 + R * K / 1.0e6)
+    return cost_channels_as_rows < 0.92 * cost_pixels_as_rows
+
+
+def _lut_conv2d_rows(img8, w_idx, image_t, y, geom, pad_index, alpha, beta, zero_x, zero_w):
+    """The convolution with the output channels as tile rows: pixel matrix [P, K] (+ its row sums when the layer
+    has zero points), then the GEMM kernel with the weights as the row operand and the transposed table."""
+    (kh, kw), (sh, sw), (ph, pw), (dh, dw) = geom
+    B, C, H, W = img8.shape
+    O = w_idx.shape[0]
+    L = y.shape[2] * y.shape[3]
+    P, K = B * L, C * kh * kw
+    dev = img8.device
+    pix = torch.empty((P, K), dtype=torch.uint8, device=dev)
+    pixsum = torch.empty(P, dtype=torch.int32, device=dev) if zero_x is not None else None
+    plan = _C.GemmPlan()
+    with _Guard(y):
+        st = _stream(y)
+        _check(_lib.atb_pixel_rows_u8(_ptr(img8), _DTYPE_CODE[img8.dtype], B, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw,
+                                      pad_index, _ptr(zero_x), _ptr(pix), _ptr(pixsum), st), "atb_pixel_rows_u8")
+        _check(_lib.atb_lut_gemm_rows_plan(O, K, P, -1, ctypes.byref(plan)), "atb_lut_gemm_rows_plan")
+        scratch = torch.empty(plan.scratch_bytes, dtype=torch.uint8, device=dev) if plan.scratch_bytes else None
+        _check(_lib.atb_lut_conv2d_rows_fwd(_ptr(w_idx), _ptr(pix), _ptr(image_t), _ptr(y), O, K, P, L,
+                                            _ptr(alpha), _ptr(beta), _ptr(zero_x), _ptr(zero_w), _ptr(pixsum),
+                                            -1, _ptr(scratch), plan.scratch_bytes, st), "atb_lut_conv2d_rows_fwd")
     return y
 
 

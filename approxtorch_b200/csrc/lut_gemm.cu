@@ -72,6 +72,7 @@ constexpr int kSlotVecs = 16 * kThreads + kThreads / 4;  // in 16-byte vectors: 
 // device-side error word of the library (0 = none); see atb_device_status
 __device__ int g_device_status = 0;
 constexpr int kStatusTableCopyTimeout = 1;
+constexpr int kStatusRowsOrientationNeedsIntegerTable = 2;
 
 struct GemmArgs {
     const uint8_t* x;
@@ -97,6 +98,11 @@ struct GemmArgs {
     const float* zero_x;
     const float* zero_w;
     const int* wsum;
+    // Channels-as-rows orientation (atb_lut_conv2d_rows_fwd): the row operand is the weight matrix [channels, K], the
+    // column operand the pixel matrix [pixels, K]; alpha, beta and zero_w are then indexed by ROW, wsum holds the
+    // pixels' operand sums (indexed by column), and element (row, column) lands at y[n][row][l] with column = n * out_L + l.
+    int rows_are_channels;
+    int out_L;
 };
 
 // description of the segment a block is working on, kept in shared memory (the main loop has no register to spare)
@@ -389,6 +395,44 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
     const int col_base = QUAD ? (lane & 15) : lane;          // first of this thread's columns within the 64
     constexpr int col_step = QUAD ? 16 : 32;
     if (!active) return;
+    if constexpr (QUAD) {
+        if (a.rows_are_channels) {
+            long long col_off[NT];
+            long long col_sum[NT];
+            bool col_ok[NT];
+            const bool zp = a.zero_x != nullptr;
+            const long long zc = zp ? llrintf(__ldg(a.zero_x)) : 0LL;       // the column operand's (activations') zero point
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const int o = c0 + col_base + col_step * t;
+                col_ok[t] = o < a.O;
+                const int oc = col_ok[t] ? o : 0;
+                const int n = oc / a.out_L;
+                col_off[t] = static_cast<long long>(n) * a.R * a.out_L + (oc - n * a.out_L);
+                col_sum[t] = zp ? static_cast<long long>(__ldg(a.wsum + oc)) : 0LL;
+            }
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) {
+                const long long r = r0 + warp * 32 + row_base + j;
+                const long long xs = __shfl_sync(0xffffffffu, xsum, row_base + j);
+                if (r >= r_end) continue;
+                const long long zr = zp ? llrintf(__ldg(a.zero_w + r)) : 0LL;  // the row operand's (this channel's) zero point
+                const float al = a.alpha != nullptr ? __ldg(a.alpha + r) : 1.0f;
+                const float be = a.beta != nullptr ? __ldg(a.beta + r) : 0.0f;
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    if (!col_ok[t]) continue;
+                    long long v = total(j, t);
+                    if (zp) v = v - zc * xs - zr * col_sum[t] + static_cast<long long>(a.K) * zr * zc;
+                    float f = __ll2float_rn(v);
+                    if (a.alpha != nullptr) f = f * al;
+                    if (a.beta != nullptr) f = f + be;
+                    a.y[col_off[t] + r * a.out_L] = f;
+                }
+            }
+            return;
+        }
+    }
     if (a.L == 1) {
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
@@ -793,6 +837,12 @@ __device__ __forceinline__ bool run_segment(const GemmArgs& a, uint8_t* smem, in
                        ((a.w_batch_stride & 15) == 0);
     // pad_index < 0: taps outside the image take the activation zero point (an integer-valued device scalar)
     const int pad = a.pad_index >= 0 ? a.pad_index : min(255, max(0, static_cast<int>(llrintf(__ldg(a.zero_x)))));
+    if (cls == LUT_F32 && a.rows_are_channels) {
+        // the channels-as-rows epilogue exists for the integer classes only: refuse loudly instead of writing a
+        // differently laid out result
+        if (tid == 0) atomicExch(&g_device_status, kStatusRowsOrientationNeedsIntegerTable);
+        return false;
+    }
     if (cls != LUT_F32)
         return gemm_body_int<RAGGED>(a, smem, rc, wcol, vec_x, vec_w, pad, cls == LUT_I16 ? 32768 : 0, r_end, kbeg, kend,
                                      desc, s_flag, bar, wait_table);
@@ -1166,5 +1216,96 @@ extern "C" int atb_lut_conv2d_fwd(const void* x, int dtype, const uint8_t* w, co
         a.image_mode = 0; a.L = 1; a.R = N;
     }
     a.alpha = alpha; a.beta = beta; a.zero_x = zero_x; a.zero_w = zero_w; a.wsum = wsum;
+    return launch_gemm(a, cfg, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+// ---- channels as rows ------------------------------------------------------------------------------------------
+// pix[(n * L + l) * K + k]: the operand index of tap k of output pixel (n, l), or the pad value; pixsum[p] = sum_k pix[p, k]
+template <int DT>
+__global__ void pixel_rows_kernel(const void* __restrict__ x, uint8_t* __restrict__ pix, int* __restrict__ pixsum,
+                                  ConvGeom g, int pad_index, const float* __restrict__ zero_x)
+{
+    const int L = g.OH * g.OW, K = g.C * g.KH * g.KW, khw = g.KH * g.KW;
+    const long long p = blockIdx.x;
+    const int n = static_cast<int>(p / L);
+    const int l = static_cast<int>(p - static_cast<long long>(n) * L);
+    const int oh = l / g.OW, ow = l - oh * g.OW;
+    const int pad = pad_index >= 0 ? pad_index : min(255, max(0, static_cast<int>(llrintf(__ldg(zero_x)))));
+    const long long base = static_cast<long long>(n) * g.C * g.H * g.W;
+    int sum = 0;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        const int c = k / khw, rem = k - c * khw;
+        const int i = rem / g.KW, j = rem - i * g.KW;
+        const int ih = oh * g.SH - g.PH + i * g.DH, iw = ow * g.SW - g.PW + j * g.DW;
+        int idx = pad;
+        if (static_cast<unsigned>(ih) < static_cast<unsigned>(g.H) && static_cast<unsigned>(iw) < static_cast<unsigned>(g.W))
+            idx = index_of<DT>(x, base + (static_cast<long long>(c) * g.H + ih) * g.W + iw);
+        pix[p * K + k] = static_cast<uint8_t>(idx);
+        sum += idx;
+    }
+    if (pixsum != nullptr) {
+        __shared__ int part[32];
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, off);
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = sum;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            int v = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0;
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
+            if (threadIdx.x == 0) pixsum[p] = v;
+        }
+    }
+}
+
+extern "C" int atb_pixel_rows_u8(const void* x, int dtype, int N, int C, int H, int W, int kh, int kw, int sh, int sw,
+                                 int ph, int pw, int dh, int dw, int pad_index, const float* zero_x,
+                                 uint8_t* pix, int* pixsum, void* stream)
+{
+    ATB_REQUIRE(N >= 0 && C >= 0 && H >= 0 && W >= 0, "negative dimension");
+    ATB_REQUIRE(dtype == ATB_I8 || dtype == ATB_U8, "image must be int8 values or uint8 indices");
+    ATB_REQUIRE(pad_index >= -1 && pad_index <= 255, "pad_index out of range");
+    ATB_REQUIRE(pad_index >= 0 || zero_x != nullptr, "pad_index -1 takes the pad value from zero_x, which is null");
+    int OH = 0, OW = 0;
+    ATB_REQUIRE(conv_out_shape(H, W, kh, kw, sh, sw, ph, pw, dh, dw, &OH, &OW), "conv geometry yields empty output");
+    const long long P = static_cast<long long>(N) * OH * OW;
+    const long long K = static_cast<long long>(C) * kh * kw;
+    if (P == 0 || K == 0) return ATB_OK;
+    ATB_REQUIRE(x != nullptr && pix != nullptr, "null pointer");
+    ATB_REQUIRE(P <= 2147483647LL && K <= kMaxK, "dimensions too large");
+    const ConvGeom g{C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, OH, OW};
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int threads = K >= 256 ? 256 : 128;
+    if (dtype == ATB_I8) pixel_rows_kernel<ATB_I8><<<static_cast<unsigned>(P), threads, 0, s>>>(x, pix, pixsum, g, pad_index, zero_x);
+    else pixel_rows_kernel<ATB_U8><<<static_cast<unsigned>(P), threads, 0, s>>>(x, pix, pixsum, g, pad_index, zero_x);
+    return check_launch("pixel_rows_kernel");
+}
+
+extern "C" int atb_lut_gemm_rows_plan(int O, int K, long long P, int cfg, atb_gemm_plan* plan)
+{
+    ATB_REQUIRE(P >= 0 && P <= 2147483647LL, "pixel count out of range");
+    return atb_lut_gemm_plan(O, K, static_cast<int>(P), 0, cfg, plan);
+}
+
+extern "C" int atb_lut_conv2d_rows_fwd(const uint8_t* w, const uint8_t* pix, const void* lut_image_t, float* y,
+                                       int O, int K, long long P, int L,
+                                       const float* alpha, const float* beta, const float* zero_x,
+                                       const float* zero_w, const int* pixsum,
+                                       int cfg, void* scratch, size_t scratch_bytes, void* stream)
+{
+    ATB_REQUIRE(O >= 0 && K >= 1 && P >= 0 && L >= 1, "negative dimension or empty reduction");
+    ATB_REQUIRE(P <= 2147483647LL && P % L == 0, "pixel count must be a multiple of L below 2^31");
+    ATB_REQUIRE(K <= kMaxK, "reductions longer than 65536 steps are not supported");
+    ATB_REQUIRE(lut_image_t != nullptr, "lut_image is null");
+    ATB_REQUIRE(cfg < 0 || ((cfg >> 24) & 1) == 0, "tables of the fp32 class are not served in this orientation");
+    if (O == 0 || P == 0) return ATB_OK;
+    ATB_REQUIRE(y != nullptr && (K == 0 || (w != nullptr && pix != nullptr)), "null operand");
+    int rc = check_epilogue(zero_x, zero_w, pixsum);
+    if (rc != ATB_OK) return rc;
+    GemmArgs a{};
+    a.x = w; a.w = pix; a.img = static_cast<const LutImage*>(lut_image_t); a.y = y;
+    a.R = O; a.K = K; a.L = 1; a.O = static_cast<int>(P);
+    a.wb_rows = 0; a.w_batch_stride = 0;
+    a.image_mode = 0; a.x_xor = 0; a.pad_index = 0;
+    a.alpha = alpha; a.beta = beta; a.zero_x = zero_x; a.zero_w = zero_w; a.wsum = pixsum;
+    a.rows_are_channels = 1; a.out_L = L;
     return launch_gemm(a, cfg, scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
 }

@@ -38,7 +38,8 @@ extern "C" {
 const char* atb_last_error(void);
 int atb_version(void);
 /* Device-side error word of the current device (host pointer out; synchronises).  0 = none; 1 = a LUT GEMM block
- * gave up waiting for its table copy and left its tiles unwritten.  (No counterpart in the reference.) */
+ * gave up waiting for its table copy and left its tiles unwritten; 2 = atb_lut_conv2d_rows_fwd was given a table of
+ * the fp32 class and wrote nothing.  (No counterpart in the reference.) */
 int atb_device_status(int* status /*host*/);
 
 /* ---- LUT image --------------------------------------------------------------------------
@@ -147,6 +148,26 @@ int atb_lut_conv2d_fwd(const void* x, int dtype, const uint8_t* w /*[O, C*kh*kw]
                        int sh, int sw, int ph, int pw, int dh, int dw, int pad_index,
                        const float* alpha, const float* beta, const float* zero_x, const float* zero_w, const int* wsum,
                        int cfg, void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- the same convolution with the output channels as tile rows ----------------------------------
+ * For operands with few pixel rows and many channels (late layers at small batch) the 512-row tiles of
+ * atb_lut_conv2d_fwd are badly filled (784 pixels = 1.5 tiles).  Here the tile rows are the output channels and the
+ * 64 tile columns are pixels: the row operand is the weight matrix w [O,K], the column operand the pixel matrix
+ * pix [P,K] (P = N*L output pixels; pix[p,k] = operand index of tap k of pixel p, written by atb_pixel_rows_u8, which
+ * also returns pixsum[p] = sum_k pix[p,k] for the zero-point correction), and the table image is the image of the
+ * TRANSPOSED table (lut_t[a][b] = lut[b][a], prepared like any other).  Integer table classes only
+ * (atb_lut_image_class; an fp32-class image raises device status 2 and writes nothing).  Same results bit for bit as
+ * atb_lut_conv2d_fwd: y [N,O,L] fp32, alpha/beta/zero_w [O], zero_x scalar.  atb_lut_gemm_rows_plan gives the scratch
+ * need (cfg as for atb_lut_gemm_plan).  (No counterpart in the reference: its kernels have one orientation.) */
+int atb_pixel_rows_u8(const void* x, int dtype, int N, int C, int H, int W, int kh, int kw, int sh, int sw,
+                      int ph, int pw, int dh, int dw, int pad_index, const float* zero_x /*scalar or NULL*/,
+                      uint8_t* pix /*[N*OH*OW, C*kh*kw]*/, int* pixsum /*[N*OH*OW] or NULL*/, void* stream);
+int atb_lut_gemm_rows_plan(int O, int K, long long P, int cfg, atb_gemm_plan* plan);
+int atb_lut_conv2d_rows_fwd(const uint8_t* w /*[O,K]*/, const uint8_t* pix /*[P,K]*/, const void* lut_image_t, float* y,
+                            int O, int K, long long P, int L,
+                            const float* alpha, const float* beta, const float* zero_x,
+                            const float* zero_w, const int* pixsum,
+                            int cfg, void* scratch, size_t scratch_bytes, void* stream);
 
 /* ---- fake quantisation -------------------------------------------------------------------- */
 /* result[0] = max|x| (result[1] = min x, result[2] = max x when want_minmax).  `result` must hold 3 floats;

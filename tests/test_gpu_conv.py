@@ -59,6 +59,64 @@ def test_conv_forward_is_bit_exact(dev, geom):
     assert torch.equal(y.flatten(2), y3)
 
 
+ROWS_GEOMS = [  # (B, C, H, W, O, k, s, p, d): few pixels, many channels - the shapes the channels-as-rows orientation serves
+    (3, 64, 7, 7, 600, 1, 1, 0, 1), (2, 48, 7, 7, 520, 3, 1, 1, 1), (5, 32, 9, 8, 130, 3, 2, 1, 1), (1, 16, 5, 5, 64, 1, 1, 0, 1),
+    (2, 20, 6, 7, 1100, (3, 2), 1, (1, 0), 1),
+]
+
+
+@pytest.mark.parametrize("geom", ROWS_GEOMS)
+def test_channels_as_rows_orientation_is_bit_identical(dev, geom, monkeypatch):
+    """The convolution with the output channels as tile rows (pixel matrix + transposed table) gives the same bits
+    as the pixels-as-rows kernel and the int64 oracle: signed table without zero points, unsigned table with the
+    zero-point correction, per-channel scale and shift."""
+    from approxtorch_b200.backend import ops
+    B, C, H, W, O, k, s, p, d = geom
+    (kh, kw), (sh, sw), (ph, pw), (dh, dw) = _pair(k), _pair(s), _pair(p), _pair(d)
+    g4 = ((kh, kw), (sh, sw), (ph, pw), (dh, dw))
+    rng = np.random.default_rng(abs(hash(geom)) & 0xffff)
+    K = C * kh * kw
+    widx = rng.integers(0, 256, (O, K), dtype=np.uint8)
+    alpha = _t(rng.uniform(0.5, 2.0, O).astype(np.float32), dev)
+    beta = _t(rng.standard_normal(O).astype(np.float32), dev)
+
+    def both(x8, image, pad, **kw_):
+        monkeypatch.setattr(ops, "ROWS_ORIENTATION", False)
+        a = ops.lut_conv2d_launch(x8, _t(widx, dev), image, g4, pad, **kw_)
+        monkeypatch.setattr(ops, "ROWS_ORIENTATION", True)
+        monkeypatch.setattr(ops, "_rows_orientation_wins", lambda R, K_, O_: True)
+        calls = []
+        real = ops._lut_conv2d_rows
+        monkeypatch.setattr(ops, "_lut_conv2d_rows", lambda *a_, **k_: (calls.append(1), real(*a_, **k_))[1])
+        b = ops.lut_conv2d_launch(x8, _t(widx, dev), image, g4, pad, **kw_)
+        assert calls, "the channels-as-rows path was not taken"
+        assert torch.equal(a, b)
+        return b
+
+    # signed table, int8 image, plain sums against the oracle
+    x8 = rng.integers(-127, 128, (B, C, H, W)).astype(np.int8)
+    lut = lo.lut_signed_noisy(64, seed=9)
+    lut_dev = _t(lut.reshape(-1), dev)             # kept alive: the transposed image is built from the table tensor
+    img = ops.lut_image(lut_dev)
+    y = both(_t(x8, dev), img, 128)
+    cols = lo.im2col_index(lo.index_of(x8, True), kh, kw, sh, sw, ph, pw, dh, dw, 128)
+    np.testing.assert_array_equal(y.flatten(2).cpu().numpy().astype(np.int64), lo.bgemm_exact(cols, widx, lut))
+    both(_t(x8, dev), img, 128, alpha=alpha, beta=beta)
+    # unsigned table, uint8 image, zero points (the pad value is the activation zero point)
+    xu = rng.integers(0, 256, (B, C, H, W), dtype=np.uint8)
+    lutu = lo.lut_unsigned_truncated(6)
+    lutu_dev = _t(lutu.reshape(-1), dev)
+    imgu = ops.lut_image(lutu_dev)
+    zx = torch.tensor(117.0, device=dev)
+    zw = _t(rng.integers(0, 256, O).astype(np.float32), dev)
+    ws = _t(widx.astype(np.int64).sum(axis=1).astype(np.int32), dev)
+    yu = both(_t(xu, dev), imgu, -1, alpha=alpha, beta=beta, zero_x=zx, zero_w=zw, wsum=ws)
+    colsu = lo.im2col_index(xu, kh, kw, sh, sw, ph, pw, dh, dw, 117)
+    t = lo.uint8_zero_point_correction(lo.bgemm_exact(colsu, widx, lutu), colsu, widx, 117, zw.cpu().numpy().astype(np.int64))
+    want = t.astype(np.float32) * alpha.cpu().numpy()[None, :, None] + beta.cpu().numpy()[None, :, None]
+    np.testing.assert_allclose(yu.flatten(2).cpu().numpy(), want, rtol=1e-6, atol=1e-3)
+
+
 def test_layer_matches_fixture_composed_from_reference_pieces(golden, dev):
     import approxtorch_b200 as at
     g = golden("conv_layer")
