@@ -112,10 +112,15 @@ def _transposed_image(image: Tensor):
         return None
     hit = _transposed.get(id(lut))
     stamp = (lut._version, lut.data_ptr())
-    if hit is None or hit[0] != stamp:
-        lut_t = lut.detach().reshape(256, 256).t().contiguous().reshape(-1)
-        _transposed[id(lut)] = hit = (stamp, lut_t)
+    if hit is None:
+        # one transposed tensor per table, rewritten in place when the table changes (so that its image is rebuilt
+        # in place too, and nothing accumulates when a table is re-broadcast before every forward)
+        lut_t = torch.empty(65536, dtype=torch.float32, device=lut.device)
+        _transposed[id(lut)] = hit = [None, lut_t]
         weakref.finalize(lut, _transposed.pop, id(lut), None)
+    if hit[0] != stamp:
+        hit[1].view(256, 256).copy_(lut.detach().reshape(256, 256).t())
+        hit[0] = stamp
     return lut_image(hit[1])
 
 

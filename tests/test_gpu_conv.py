@@ -102,6 +102,9 @@ def test_channels_as_rows_orientation_is_bit_identical(dev, geom, monkeypatch):
     cols = lo.im2col_index(lo.index_of(x8, True), kh, kw, sh, sw, ph, pw, dh, dw, 128)
     np.testing.assert_array_equal(y.flatten(2).cpu().numpy().astype(np.int64), lo.bgemm_exact(cols, widx, lut))
     both(_t(x8, dev), img, 128, alpha=alpha, beta=beta)
+    # a table rewritten in place (as a re-broadcast module buffer is): the transposed image follows it
+    lut_dev.view(256, 256)[3:40, 100:180] += 2.0
+    both(_t(x8, dev), ops.lut_image(lut_dev), 128)
     # unsigned table, uint8 image, zero points (the pad value is the activation zero point)
     xu = rng.integers(0, 256, (B, C, H, W), dtype=np.uint8)
     lutu = lo.lut_unsigned_truncated(6)
