@@ -234,7 +234,10 @@ def lut_conv_layers(dev, batch, pk=None, layers=None):
         ms = _time_ms(lambda: ops.lut_conv2d_launch(x, w, img, g4, -1, alpha=al, zero_x=zx, zero_w=zw, wsum=ws),
                       iters=3, warmup=2, reps=8)
         macs = float(R) * K * O
-        rows.append({"C": C, "H": H, "O": O, "k": k, "stride": s, "count": count, "R": R, "K": K, "plan": _plan_name(R, K, O),
+        by_channels = ops.ROWS_ORIENTATION and ops._rows_orientation_wins(R, K, O)
+        rows.append({"C": C, "H": H, "O": O, "k": k, "stride": s, "count": count, "R": R, "K": K,
+                     "tile_rows": "channels" if by_channels else "pixels",
+                     "plan": _plan_name(O, K, R) if by_channels else _plan_name(R, K, O),
                      "ms": ms, "lookups_per_s": macs / (ms * 1e-3), "frac_of_lookup_peak": macs / (ms * 1e-3) / pk["lookup_peak"]})
         tot_ms += ms * count
         tot_macs += macs * count
