@@ -71,6 +71,7 @@ constexpr int kSlotVecs = 16 * kThreads + kThreads / 4;  // in 16-byte vectors: 
 
 // device-side error word of the library (0 = none); see atb_device_status
 __device__ int g_device_status = 0;
+constexpr int kMaxK32 = 16384;                       // reductions whose zero-point corrected sums fit 32 bits
 constexpr int kStatusTableCopyTimeout = 1;
 constexpr int kStatusRowsOrientationNeedsIntegerTable = 2;
 
@@ -128,7 +129,17 @@ __device__ __forceinline__ float scale_shift(float v, int o, const GemmArgs& a)
 __device__ __forceinline__ float finalize_output(long long total, long long xsum, int o, const GemmArgs& a)
 {
     float v;
-    if (a.zero_x != nullptr) {
+    if (a.zero_x != nullptr && a.K <= kMaxK32) {
+        // up to 16384 steps every term is below 2^30 in magnitude and the corrected sum below 2^31: 32-bit arithmetic
+        // (wrapping on the way, exact at the end) instead of 64-bit multiplies and a 64-bit conversion
+        const int zx = __float2int_rn(__ldg(a.zero_x));
+        const int zw = __float2int_rn(__ldg(a.zero_w + o));
+        const int ws = __ldg(a.wsum + o);
+        const unsigned t32 = static_cast<unsigned>(total) - static_cast<unsigned>(zw) * static_cast<unsigned>(xsum) -
+                             static_cast<unsigned>(zx) * static_cast<unsigned>(ws) +
+                             static_cast<unsigned>(a.K) * static_cast<unsigned>(zx) * static_cast<unsigned>(zw);
+        v = __int2float_rn(static_cast<int>(t32));
+    } else if (a.zero_x != nullptr) {
         const long long zx = llrintf(__ldg(a.zero_x));
         const long long zw = llrintf(__ldg(a.zero_w + o));
         const long long ws = __ldg(a.wsum + o);
@@ -423,8 +434,16 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
                 for (int t = 0; t < NT; ++t) {
                     if (!col_ok[t]) continue;
                     long long v = total(j, t);
-                    if (zp) v = v - zc * xs - zr * col_sum[t] + static_cast<long long>(a.K) * zr * zc;
-                    float f = __ll2float_rn(v);
+                    float f;
+                    if (zp && a.K <= kMaxK32) {
+                        const unsigned t32 = static_cast<unsigned>(v) - static_cast<unsigned>(zc) * static_cast<unsigned>(xs) -
+                                             static_cast<unsigned>(zr) * static_cast<unsigned>(col_sum[t]) +
+                                             static_cast<unsigned>(a.K) * static_cast<unsigned>(zr) * static_cast<unsigned>(zc);
+                        f = __int2float_rn(static_cast<int>(t32));
+                    } else {
+                        if (zp) v = v - zc * xs - zr * col_sum[t] + static_cast<long long>(a.K) * zr * zc;
+                        f = __ll2float_rn(v);
+                    }
                     if (a.alpha != nullptr) f = f * al;
                     if (a.beta != nullptr) f = f + be;
                     a.y[col_off[t] + r * a.out_L] = f;
