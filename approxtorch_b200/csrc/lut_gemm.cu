@@ -144,6 +144,8 @@ __device__ __forceinline__ float finalize_output(long long total, long long xsum
         const long long zw = llrintf(__ldg(a.zero_w + o));
         const long long ws = __ldg(a.wsum + o);
         v = __ll2float_rn(total - zw * xsum - zx * ws + static_cast<long long>(a.K) * zx * zw);
+    } else if (a.K <= kMaxK32) {
+        v = __int2float_rn(static_cast<int>(static_cast<unsigned>(total)));     // |sum| < 2^30: one 32-bit conversion
     } else {
         v = __ll2float_rn(total);
     }
@@ -440,6 +442,8 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
                                              static_cast<unsigned>(zr) * static_cast<unsigned>(col_sum[t]) +
                                              static_cast<unsigned>(a.K) * static_cast<unsigned>(zr) * static_cast<unsigned>(zc);
                         f = __int2float_rn(static_cast<int>(t32));
+                    } else if (a.K <= kMaxK32) {
+                        f = __int2float_rn(static_cast<int>(static_cast<unsigned>(v)));
                     } else {
                         if (zp) v = v - zc * xs - zr * col_sum[t] + static_cast<long long>(a.K) * zr * zc;
                         f = __ll2float_rn(v);
