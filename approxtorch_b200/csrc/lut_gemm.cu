@@ -121,8 +121,10 @@ struct SegDesc {
 // unsigned table's 33, the zero-point terms need 64.
 __device__ __forceinline__ float scale_shift(float v, int o, const GemmArgs& a)
 {
-    if (a.alpha != nullptr) v = v * __ldg(a.alpha + o);
-    if (a.beta != nullptr) v = v + __ldg(a.beta + o);
+    // two roundings, like the separate multiply and add of the reference's dequantisation: never contracted into an
+    // FMA, so that every epilogue variant of this file gives the same bits
+    if (a.alpha != nullptr) v = __fmul_rn(v, __ldg(a.alpha + o));
+    if (a.beta != nullptr) v = __fadd_rn(v, __ldg(a.beta + o));
     return v;
 }
 
@@ -448,14 +450,46 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
                         if (zp) v = v - zc * xs - zr * col_sum[t] + static_cast<long long>(a.K) * zr * zc;
                         f = __ll2float_rn(v);
                     }
-                    if (a.alpha != nullptr) f = f * al;
-                    if (a.beta != nullptr) f = f + be;
+                    if (a.alpha != nullptr) f = __fmul_rn(f, al);
+                    if (a.beta != nullptr) f = __fadd_rn(f, be);
                     a.y[col_off[t] + r * a.out_L] = f;
                 }
             }
             return;
         }
     }
+    // Integer tables with sums that fit 32 bits: what depends on the column only (zero point, its products, scale,
+    // shift) is fetched once per thread and column instead of once per output element.
+    const bool fast = QUAD && a.K <= kMaxK32;
+    unsigned ce_zw[NT], ce_cc[NT];
+    float ce_al[NT], ce_be[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        ce_zw[t] = 0u; ce_cc[t] = 0u; ce_al[t] = 1.0f; ce_be[t] = 0.0f;
+        if (fast) {
+            const int o = min(c0 + col_base + col_step * t, a.O - 1);
+            if (a.zero_x != nullptr) {
+                const unsigned zx = static_cast<unsigned>(__float2int_rn(__ldg(a.zero_x)));
+                const unsigned zw = static_cast<unsigned>(__float2int_rn(__ldg(a.zero_w + o)));
+                ce_zw[t] = zw;
+                ce_cc[t] = static_cast<unsigned>(a.K) * zx * zw - zx * static_cast<unsigned>(__ldg(a.wsum + o));
+            }
+            if (a.alpha != nullptr) ce_al[t] = __ldg(a.alpha + o);
+            if (a.beta != nullptr) ce_be[t] = __ldg(a.beta + o);
+        }
+    }
+    auto fin = [&](int j, int t, int xs, int o) -> float {
+        if constexpr (QUAD) {
+            if (fast) {
+                const unsigned v = static_cast<unsigned>(total(j, t)) - ce_zw[t] * static_cast<unsigned>(xs) + ce_cc[t];
+                float f = __int2float_rn(static_cast<int>(v));
+                if (a.alpha != nullptr) f = __fmul_rn(f, ce_al[t]);
+                if (a.beta != nullptr) f = __fadd_rn(f, ce_be[t]);
+                return f;
+            }
+        }
+        return finalize_output(total(j, t), xs, o, a);
+    };
     if (a.L == 1) {
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
@@ -465,7 +499,7 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
 #pragma unroll
             for (int t = 0; t < NT; ++t) {
                 const int o = c0 + col_base + col_step * t;
-                if (o < a.O) a.y[r * a.O + o] = finalize_output(total(j, t), xs, o, a);
+                if (o < a.O) a.y[r * a.O + o] = fin(j, t, xs, o);
             }
         }
         return;
@@ -484,8 +518,7 @@ __device__ __forceinline__ void write_tile(const GemmArgs& a, uint8_t* smem, lon
             for (int tt = 0; tt < TH; ++tt) {
                 const int t = half * TH + tt;
                 const int oc = col_base + col_step * t;            // channel within the 64
-                tile[(oc - 32 * half) * kPitch + row_base + j] =
-                    (c0 + oc < a.O) ? finalize_output(total(j, t), xs, c0 + oc, a) : 0.0f;
+                tile[(oc - 32 * half) * kPitch + row_base + j] = (c0 + oc < a.O) ? fin(j, t, xs, c0 + oc) : 0.0f;
             }
         }
         __syncwarp();

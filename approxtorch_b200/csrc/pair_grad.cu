@@ -472,8 +472,9 @@ __device__ __forceinline__ float fwd_finalize(float total, int xsum, int o, int 
         v = static_cast<float>(static_cast<double>(total) +
                                static_cast<double>(-zw * xsum - zx * ws + static_cast<long long>(K) * zx * zw));
     }
-    if (ep.alpha != nullptr) v = v * __ldg(ep.alpha + o);
-    if (ep.beta != nullptr) v = v + __ldg(ep.beta + o);
+    // unfused, like every epilogue of the LUT GEMM (two roundings: the reference multiplies and adds separately)
+    if (ep.alpha != nullptr) v = __fmul_rn(v, __ldg(ep.alpha + o));
+    if (ep.beta != nullptr) v = __fadd_rn(v, __ldg(ep.beta + o));
     return v;
 }
 
