@@ -1312,6 +1312,60 @@ __global__ void pixel_rows_kernel(const void* __restrict__ x, uint8_t* __restric
     }
 }
 
+// The same for a 1x1 kernel without padding: a transposition [C][pixels] -> [pixels][C].  One block turns 32 pixels x
+// 256 channels around through shared memory (32 bytes read along the pixels, 32 bytes written along the channels) and
+// adds its share of the pixels' sums to pixsum, which the caller has zeroed.
+template <int DT>
+__global__ void __launch_bounds__(256) pixel_rows_1x1_kernel(const void* __restrict__ x, uint8_t* __restrict__ pix,
+                                                             int* __restrict__ pixsum, ConvGeom g, long long P)
+{
+    __shared__ uint8_t tile[32][33];
+    const int L = g.OH * g.OW, C = g.C;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;          // 32 x 8
+    const long long p0 = static_cast<long long>(blockIdx.x) * 32;
+    // the pixel this thread reads for
+    const long long pr = p0 + tx;
+    const bool pr_ok = pr < P;
+    long long src = 0;
+    if (pr_ok) {
+        const int n = static_cast<int>(pr / L);
+        const int l = static_cast<int>(pr - static_cast<long long>(n) * L);
+        const int oh = l / g.OW, ow = l - oh * g.OW;
+        src = (static_cast<long long>(n) * C * g.H + oh * g.SH) * g.W + ow * g.SW;
+    }
+    const long long plane = static_cast<long long>(g.H) * g.W;
+    int sums[4] = {0, 0, 0, 0};                                          // pixels ty + 8 i, this thread's channels
+    const int c_end = min(C, (static_cast<int>(blockIdx.y) + 1) * 256);
+    for (int c0 = blockIdx.y * 256; c0 < c_end; c0 += 32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int c = c0 + ty + 8 * i;
+            tile[ty + 8 * i][tx] = (pr_ok && c < C) ? static_cast<uint8_t>(index_of<DT>(x, src + c * plane)) : static_cast<uint8_t>(0);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const long long pw_ = p0 + ty + 8 * i;
+            const int c = c0 + tx;
+            if (pw_ < P && c < C) {
+                const uint8_t v = tile[tx][ty + 8 * i];
+                pix[pw_ * C + c] = v;
+                sums[i] += v;
+            }
+        }
+        __syncthreads();
+    }
+    if (pixsum != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int v = sums[i];
+            for (int off = 16; off > 0; off >>= 1) v += __shfl_down_sync(0xffffffffu, v, off);
+            const long long pw_ = p0 + ty + 8 * i;
+            if (tx == 0 && pw_ < P) atomicAdd(pixsum + pw_, v);
+        }
+    }
+}
+
 extern "C" int atb_pixel_rows_u8(const void* x, int dtype, int N, int C, int H, int W, int kh, int kw, int sh, int sw,
                                  int ph, int pw, int dh, int dw, int pad_index, const float* zero_x,
                                  uint8_t* pix, int* pixsum, void* stream)
@@ -1329,6 +1383,16 @@ extern "C" int atb_pixel_rows_u8(const void* x, int dtype, int N, int C, int H, 
     ATB_REQUIRE(P <= 2147483647LL && K <= kMaxK, "dimensions too large");
     const ConvGeom g{C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, OH, OW};
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (kh == 1 && kw == 1 && ph == 0 && pw == 0) {
+        if (pixsum != nullptr) {
+            cudaError_t e = cudaMemsetAsync(pixsum, 0, static_cast<size_t>(P) * sizeof(int), s);
+            if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return ATB_ERR_CUDA; }
+        }
+        const dim3 grid(static_cast<unsigned>((P + 31) / 32), static_cast<unsigned>((C + 255) / 256));
+        if (dtype == ATB_I8) pixel_rows_1x1_kernel<ATB_I8><<<grid, 256, 0, s>>>(x, pix, pixsum, g, P);
+        else pixel_rows_1x1_kernel<ATB_U8><<<grid, 256, 0, s>>>(x, pix, pixsum, g, P);
+        return check_launch("pixel_rows_1x1_kernel");
+    }
     const int threads = K >= 256 ? 256 : 128;
     if (dtype == ATB_I8) pixel_rows_kernel<ATB_I8><<<static_cast<unsigned>(P), threads, 0, s>>>(x, pix, pixsum, g, pad_index, zero_x);
     else pixel_rows_kernel<ATB_U8><<<static_cast<unsigned>(P), threads, 0, s>>>(x, pix, pixsum, g, pad_index, zero_x);

@@ -357,7 +357,40 @@ def profile_once(dev):
                         "tc_gemm (grad_x, grad_w), pair_grad (dx, dw), pair_fwd"}
 
 
-def run_all(dev, which=("lds", "stream", "backward", "custom", "fp32", "layers"), batches=(128, 16)):
+def orientation(dev, pk=None, batch=16):
+    """Two late ResNet-50 layers at a small batch with the pixels and with the output channels as tile rows (same
+    results bit for bit): the case the channels-as-rows orientation exists for."""
+    pk = pk or peaks(dev)
+    lut = unsigned_truncated_table(dev)
+    img = ops.lut_image(lut)
+    out = {"batch": batch, "table_kept_alive": lut.numel()}
+    real = ops._rows_orientation_wins
+    try:
+        for (C, H, O, k, s, p) in ((2048, 7, 512, 1, 1, 0), (512, 7, 512, 3, 1, 1)):
+            x = torch.randint(0, 256, (batch, C, H, H), dtype=torch.uint8, device=dev)
+            w = torch.randint(0, 256, (O, C * k * k), dtype=torch.uint8, device=dev)
+            g4 = ((k, k), (s, s), (p, p), (1, 1))
+            zx, zw = torch.tensor(117.0, device=dev), torch.full((O,), 120.0, device=dev)
+            ws = w.sum(dim=1, dtype=torch.int32)
+            al = torch.rand(O, device=dev)
+            OH = (H + 2 * p - k) // s + 1
+            macs = float(batch * OH * OH) * C * k * k * O
+            row = {}
+            ys = []
+            for name, force in (("pixels_as_rows", False), ("channels_as_rows", True)):
+                ops._rows_orientation_wins = (lambda R_, K_, O_, f=force: f)
+                ms = _time_ms(lambda: ops.lut_conv2d_launch(x, w, img, g4, -1, alpha=al, zero_x=zx, zero_w=zw, wsum=ws),
+                              iters=3, warmup=2, reps=8)
+                ys.append(ops.lut_conv2d_launch(x, w, img, g4, -1, alpha=al, zero_x=zx, zero_w=zw, wsum=ws))
+                row[name] = {"ms": ms, "lookups_per_s": macs / (ms * 1e-3), "frac_of_lookup_peak": macs / (ms * 1e-3) / pk["lookup_peak"]}
+            row["bit_identical"] = bool(torch.equal(ys[0], ys[1]))
+            out[f"C{C}_H{H}_O{O}_k{k}"] = row
+    finally:
+        ops._rows_orientation_wins = real
+    return out
+
+
+def run_all(dev, which=("lds", "stream", "backward", "custom", "fp32", "orientation", "layers"), batches=(128, 16)):
     pk = peaks(dev)
     out = {"peaks": pk}
     for name in which:
@@ -375,6 +408,8 @@ def run_all(dev, which=("lds", "stream", "backward", "custom", "fp32", "layers")
                 out["custom"] = custom_kernels(dev, pk)
             elif name == "profile":
                 out["profile"] = profile_once(dev)
+            elif name == "orientation":
+                out["orientation_b16"] = orientation(dev, pk)
             elif name == "fp32":
                 out["fp32_class_table"] = fp32_table(dev, pk)
             elif name == "model":
@@ -402,7 +437,7 @@ def _print_table(res):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", default="lds,stream,backward,custom,fp32,layers")
+    ap.add_argument("--only", default="lds,stream,backward,custom,fp32,orientation,layers")
     ap.add_argument("--batch", default="128,16")
     ap.add_argument("--json", action="store_true")
     a = ap.parse_args()
